@@ -1,0 +1,145 @@
+"""Builds the CUDA sources of this folder into one shared library for sm_100a.
+
+Plain `nvcc`, one object per source file (compiled in parallel), linked into
+`_build/libmynah_slm_b200.so` beside the sources. The sources include no
+PyTorch header, so a cold build takes seconds per file rather than minutes. A
+stamp of the sources' contents and the flags decides whether anything has to
+be rebuilt, so the library that travels with the tree is used as it is.
+
+When the folder is not writable (a checkout that belongs to someone else) the
+build goes to a per-user folder under the system's temporary directory.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "libmynah_slm_b200.so"
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
+]
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def sources() -> list[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+
+
+def _headers() -> list[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+
+
+def _stamp() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for f in sources() + _headers():
+        h.update(f.encode())
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
+def _writable(path: str) -> bool:
+    try:
+        os.makedirs(path, exist_ok=True)
+        probe = os.path.join(path, f".probe{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return True
+    except OSError:
+        return False
+
+
+def build_dir() -> str:
+    local = os.path.join(HERE, "_build")
+    if _writable(local):
+        return local
+    alt = os.path.join(tempfile.gettempdir(), f"mynah_slm_b200_build_{os.getuid()}")
+    if _writable(alt):
+        return alt
+    raise BuildError(f"neither {local} nor {alt} is writable")
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise BuildError("nvcc not found (looked at $NVCC, PATH and /usr/local/cuda/bin): "
+                     "the CUDA kernels of mynah_slm_b200 cannot be built")
+
+
+def library_path(verbose: bool = False) -> str:
+    """Path of an up-to-date library, building it first if need be."""
+    out = build_dir()
+    lib = os.path.join(out, LIB_NAME)
+    stamp_file = os.path.join(out, "stamp")
+    stamp = _stamp()
+    if os.path.isfile(lib) and os.path.isfile(stamp_file):
+        with open(stamp_file) as f:
+            if f.read().strip() == stamp:
+                return lib
+    _build(out, lib, verbose)
+    with open(stamp_file, "w") as f:
+        f.write(stamp)
+    return lib
+
+
+def _say(msg: str) -> None:
+    print(f"[mynah_slm_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _build(out: str, lib: str, verbose: bool) -> None:
+    nvcc = find_nvcc()
+    srcs = sources()
+    _say(f"building {len(srcs)} CUDA sources for sm_100a into {out} (first call only)")
+    t0 = time.time()
+    done = threading.Event()
+
+    def heartbeat():
+        while not done.wait(10.0):
+            _say(f"still compiling ... {time.time() - t0:.0f}s")
+
+    hb = threading.Thread(target=heartbeat, daemon=True)
+    hb.start()
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(out, src[:-3] + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise BuildError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+        if verbose and r.stderr:
+            _say(f"{src}:\n{r.stderr}")
+        _say(f"compiled {src} ({time.time() - t0:.0f}s)")
+        return obj
+
+    try:
+        with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as ex:
+            objs = list(ex.map(compile_one, srcs))
+        tmp = lib + f".tmp{os.getpid()}"
+        r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-lcudart"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise BuildError(f"linking {LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, lib)
+    finally:
+        done.set()
+    _say(f"built {LIB_NAME} in {time.time() - t0:.0f}s")
+
+
+if __name__ == "__main__":
+    print(library_path(verbose="-v" in sys.argv))

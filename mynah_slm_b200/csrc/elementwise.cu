@@ -1,0 +1,134 @@
+// Row-wise kernels around the matrix products: token embedding, RMSNorm with
+// the residual add folded in, SwiGLU, and the plain residual add.
+//
+// The residual stream is fp32 in both precisions. Sums of squares and the
+// scale are fp32; the order of every sum is fixed by the thread layout, so a
+// row's result does not depend on which other rows share the launch.
+#include "common.cuh"
+
+// ------------------------------------------------------------- embedding
+// x[t, :] = E[token_t, :]           (mynah-slm src/arch_qwen3.c:186: no scaling)
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                                    float* __restrict__ x, int D, int V) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* out = x + (size_t)t * D;
+    if (tok < 0 || tok >= V) {      // refused on the host already; never read out of range
+        for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = 0.f;
+        return;
+    }
+    const TW* row = table + (size_t)tok * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+MYNAH_API int mynah_embed_gather(const void* table, int table_dtype, const int* tokens, float* x,
+                                 int T, int D, int V, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && D > 0 && V > 0, "embed_gather: bad sizes T=%d D=%d V=%d", T, D, V);
+    const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
+    if (table_dtype == MYNAH_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, x, D, V);
+    else if (table_dtype == MYNAH_BF16)
+        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)table, tokens, x, D, V);
+    else
+        return mynah_fail("embed_gather: unsupported table dtype %d", table_dtype);
+    return mynah_check_launch("embed_gather");
+}
+
+// --------------------------------------------------------------- RMSNorm
+// v = x[r] (+ delta[r]);  x[r] = v when delta is given;
+// out[i] = (v * s) * w   with   s = 1 / sqrt(mean(v^2) + eps)
+// (mynah-slm src/kernels.c:118-128; plain gain, not 1+w). `rows`, when given,
+// selects the rows to normalise (the rows whose logits are wanted); out then
+// has one row per selected row.
+template <typename TA>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
+                               const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+    __shared__ float red[32];
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = x + (size_t)r * D;
+    const TA* dr = delta ? delta + (size_t)r * D : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = xr[i];
+        if (dr) {
+            v += to_f32(dr[i]);
+            xr[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)D + eps);
+    TA* o = out + (size_t)blockIdx.x * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TA>((xr[i] * s) * w.at(i));
+}
+
+MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, const int* rows,
+                            void* out, int act_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    MYNAH_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: bad sizes rows=%d D=%d", n_rows, D);
+    MYNAH_REQUIRE(w_dtype == MYNAH_F32 || w_dtype == MYNAH_BF16, "rmsnorm: unsupported gain dtype %d", w_dtype);
+    const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 32));
+    const VecRef wr{w, w_dtype};
+    if (act_dtype == MYNAH_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, (const float*)delta, wr, rows, (float*)out, D, eps);
+    else if (act_dtype == MYNAH_BF16)
+        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+    else
+        return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
+    return mynah_check_launch("rmsnorm");
+}
+
+// ----------------------------------------------------------- residual add
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += to_f32(delta[i]);          // mynah-slm src/kernels.c:222-224
+}
+
+MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
+    if (act_dtype == MYNAH_F32)
+        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+    else if (act_dtype == MYNAH_BF16)
+        residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n);
+    else
+        return mynah_fail("residual_add: unsupported activation dtype %d", act_dtype);
+    return mynah_check_launch("residual_add");
+}
+
+// ----------------------------------------------------------------- SwiGLU
+// a = (g * sigmoid(g)) * u with the sigmoid that never exponentiates a
+// positive argument (mynah-slm src/kernels.c:193-205). gate_up is [T, 2F]:
+// gate in columns [0, F), up in [F, 2F).
+__device__ __forceinline__ float stable_sigmoid(float v) {
+    if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
+    const float e = expf(v);
+    return e / (1.0f + e);
+}
+
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, int F) {
+    const int t = blockIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= F) return;
+    const TA* row = gate_up + (size_t)t * 2 * F;
+    const float g = to_f32(row[i]), u = to_f32(row[F + i]);
+    out[(size_t)t * F + i] = from_f32<TA>((g * stable_sigmoid(g)) * u);
+}
+
+MYNAH_API int mynah_swiglu(const void* gate_up, void* out, int act_dtype, int T, int F, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && F > 0, "swiglu: bad sizes T=%d F=%d", T, F);
+    MYNAH_REQUIRE(ceil_div(F, 256) <= 65535, "swiglu: width %d exceeds one launch", F);
+    const dim3 grid(T, ceil_div(F, 256));
+    if (act_dtype == MYNAH_F32)
+        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, F);
+    else if (act_dtype == MYNAH_BF16)
+        swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, F);
+    else
+        return mynah_fail("swiglu: unsupported activation dtype %d", act_dtype);
+    return mynah_check_launch("swiglu");
+}

@@ -1,0 +1,35 @@
+// Error reporting of the exported entry points: the message of the last
+// failure of the calling thread, returned as text. The library never prints
+// (the reference's rule for its public API, mynah-slm include/mynah_slm.h:4-8).
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+static thread_local char g_error[512] = "";
+
+int mynah_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return -1;
+}
+
+int mynah_check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return mynah_fail("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+MYNAH_API const char* mynah_last_error(void) { return g_error; }
+
+// Compute capability of the current device as major*10+minor, or a negative
+// code; the Python side refuses anything but 100 before the first launch.
+MYNAH_API int mynah_device_arch(void) {
+    int dev = 0, major = 0, minor = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return mynah_fail("no CUDA device is current");
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    return major * 10 + minor;
+}

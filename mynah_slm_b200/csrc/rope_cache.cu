@@ -1,0 +1,160 @@
+// Position encoding and the write into the cache, fused with the per-head
+// norm: one pass over the projected q/k/v of a step.
+//
+//   q head: RMSNorm over head_dim (optional) -> split-half rotation (optional)
+//           -> back in place, for the attention kernel
+//   k head: same norm and rotation -> the sequence's page at its position
+//   v head: copied to the sequence's page
+//
+// Norm before rotation, one gain vector of head_dim shared by all heads,
+// V neither normed nor rotated (mynah-slm src/arch_qwen3.c:208-218,
+// src/kernels.c:130-137, :173-189). Norm, angles and rotation are fp32; the
+// rotation table is built in double like the reference's
+// (src/kernels.c:154-162) and stored as float. Values are rounded to the
+// activation or cache type once, when stored.
+#include "layout.cuh"
+
+namespace {
+
+// cos/sin[p][i] = (float) cos/sin(p * theta^(-2i/rotary_dim)), in double.
+__global__ void rope_table_kernel(float* __restrict__ cos_t, float* __restrict__ sin_t,
+                                  int n_pos, int half, double theta, int rotary_dim) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)n_pos * half) return;
+    const int p = (int)(idx / half), i = (int)(idx % half);
+    const double inv = 1.0 / pow(theta, (2.0 * (double)i) / (double)rotary_dim);
+    const double a = (double)p * inv;
+    cos_t[idx] = (float)cos(a);
+    sin_t[idx] = (float)sin(a);
+}
+
+constexpr int MAX_HEAD_DIM = 256;
+constexpr int WARPS = 4;
+
+struct QkvArgs {
+    int T, H, KV, HD, ld;          // ld: row stride of qkv in elements
+    int rotary_dim, n_pos;         // rotation over the first rotary_dim dims; table rows
+    float eps;
+};
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                          PageTable pt, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                          QkvArgs a, int* __restrict__ status) {
+    __shared__ float stage[WARPS][MAX_HEAD_DIM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = k_cache != nullptr ? a.H + 2 * a.KV : a.H;   // without storage only q is touched
+    const long long unit = (long long)blockIdx.x * WARPS + warp;
+    if (unit >= (long long)a.T * heads) return;
+    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    const int seq = tok_seq[t];
+    if (seq < 0) return;                                   // padding token: nothing to do
+    const int pos = tok_pos[t];
+    const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
+    const int kvh = is_q ? 0 : (is_k ? h - a.H : h - a.H - a.KV);
+    TA* src = qkv + (size_t)t * a.ld + (size_t)h * a.HD;
+
+    TC* dst = nullptr;
+    if (!is_q) {
+        TC* cache = is_k ? k_cache : v_cache;
+        const int page = page_of(pt, seq, pos);
+        if (page < 0) {
+            if (lane == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+            return;
+        }
+        dst = cache + (((size_t)page * a.KV + kvh) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.HD;
+    }
+
+    if (!is_q && !is_k) {                                  // V: copy
+        for (int i = lane; i < a.HD; i += 32) dst[i] = from_f32<TC>(to_f32(src[i]));
+        return;
+    }
+
+    float* s = stage[warp];
+    const VecRef gain = is_q ? q_gain : k_gain;
+    float ss = 0.f;
+    for (int i = lane; i < a.HD; i += 32) {
+        const float v = to_f32(src[i]);
+        s[i] = v;
+        ss += v * v;
+    }
+    if (gain.p != nullptr) {
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)a.HD + a.eps);
+        for (int i = lane; i < a.HD; i += 32) s[i] = s[i] * (sc * gain.at(i));   // x *= s*w, kernels.c:135
+    }
+    __syncwarp();
+
+    const int half = a.rotary_dim / 2;
+    const bool rotate = cos_t != nullptr && half > 0;
+    if (rotate && (pos < 0 || pos >= a.n_pos)) {
+        if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+        return;
+    }
+    if (rotate) {
+        const float* c = cos_t + (size_t)pos * half;
+        const float* sn = sin_t + (size_t)pos * half;
+        for (int i = lane; i < half; i += 32) {
+            const float x0 = s[i], x1 = s[i + half];
+            const float o0 = x0 * c[i] - x1 * sn[i];       // kernels.c:181-187
+            const float o1 = x1 * c[i] + x0 * sn[i];
+            if (is_q) {
+                src[i] = from_f32<TA>(o0);
+                src[i + half] = from_f32<TA>(o1);
+            } else {
+                dst[i] = from_f32<TC>(o0);
+                dst[i + half] = from_f32<TC>(o1);
+            }
+        }
+    }
+    for (int i = (rotate ? a.rotary_dim : 0) + lane; i < a.HD; i += 32) {
+        if (is_q) src[i] = from_f32<TA>(s[i]);
+        else dst[i] = from_f32<TC>(s[i]);
+    }
+}
+
+}  // namespace
+
+MYNAH_API int mynah_rope_table(float* cos_t, float* sin_t, int n_pos, int rotary_dim, double theta,
+                               cudaStream_t stream) {
+    MYNAH_REQUIRE(n_pos > 0 && rotary_dim > 0 && rotary_dim % 2 == 0,
+                  "rope_table: rotary_dim %d must be positive and even", rotary_dim);
+    const int half = rotary_dim / 2;
+    const long long n = (long long)n_pos * half;
+    rope_table_kernel<<<(unsigned)ceil_div_ll(n, 256), 256, 0, stream>>>(cos_t, sin_t, n_pos, half, theta, rotary_dim);
+    return mynah_check_launch("rope_table");
+}
+
+// dtype: type of qkv and of the cache (the 32-bit path keeps both in fp32).
+MYNAH_API int mynah_qk_norm_rope_store(
+    void* qkv, int dtype, int T, int H, int KV, int HD, int ld,
+    const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+    const float* cos_t, const float* sin_t, int rotary_dim, int n_pos,
+    const int* tok_seq, const int* tok_pos,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    void* k_cache, void* v_cache, int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && H > 0 && KV > 0 && HD > 0, "qk_norm_rope_store: bad sizes");
+    MYNAH_REQUIRE(HD <= MAX_HEAD_DIM, "qk_norm_rope_store: head_dim %d exceeds %d", HD, MAX_HEAD_DIM);
+    MYNAH_REQUIRE(rotary_dim % 2 == 0 && rotary_dim <= HD, "qk_norm_rope_store: rotary_dim %d does not fit head_dim %d", rotary_dim, HD);
+    MYNAH_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "qk_norm_rope_store: K and V storage go together");
+    const int heads = k_cache != nullptr ? H + 2 * KV : H;     // a run that reads another run's cache brings q only
+    MYNAH_REQUIRE(ld >= heads * HD, "qk_norm_rope_store: row stride %d is smaller than the row", ld);
+    const QkvArgs a{T, H, KV, HD, ld, cos_t ? rotary_dim : 0, n_pos, eps};
+    const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    const PageTable pt{page_indptr, page_ids, page_base, n_pages};
+    const long long units = (long long)T * heads;
+    const unsigned blocks = (unsigned)ceil_div_ll(units, WARPS);
+    if (dtype == MYNAH_F32)
+        qk_norm_rope_store_kernel<float, float><<<blocks, WARPS * 32, 0, stream>>>(
+            (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status);
+    else if (dtype == MYNAH_BF16)
+        qk_norm_rope_store_kernel<bf16, bf16><<<blocks, WARPS * 32, 0, stream>>>(
+            (bf16*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status);
+    else
+        return mynah_fail("qk_norm_rope_store: unsupported dtype %d", dtype);
+    return mynah_check_launch("qk_norm_rope_store");
+}

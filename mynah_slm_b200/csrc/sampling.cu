@@ -1,0 +1,458 @@
+// From logits to a token, on the device: penalties, greedy argmax, and
+// temperature sampling with top-k, min-p and top-p, in the reference's order
+// (mynah-slm src/sampler.c:116-187; penalties :80-106; ring :73-78; the
+// generator is splitmix64, :40-46).
+//
+// The reference sorts the whole vocabulary by (probability descending, id
+// ascending) and works on prefixes of that order. Every filter keeps a prefix
+// and the draw walks a prefix, so no sort is needed here: a prefix is found by
+// a radix search over the bits of the probabilities (three passes of 11, 11
+// and 10 bits) with a histogram of counts and of probability mass per digit.
+// Mass is summed as 2^-60 fixed point in 64-bit integers: integer sums do not
+// depend on the order of the additions, so the same logits and the same
+// generator state give the same token in every run.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+constexpr int BINS = 2048;
+
+__device__ __forceinline__ unsigned long long mass_of(float p) {
+    return __double2ull_rd((double)p * 1152921504606846976.0);     // p * 2^60
+}
+
+struct Prefix {            // a prefix of the sorted order
+    unsigned int value;    // bits of the probability at which it ends
+    unsigned int above;    // elements with a larger probability
+    unsigned int ties;     // elements equal to `value` that belong to it (by ascending id)
+    unsigned long long mass;   // its total mass
+};
+
+struct Shared {
+    unsigned int count[BINS];
+    unsigned long long mass[BINS];
+    unsigned int warp_count[32];
+    unsigned long long warp_mass[32];
+    // results handed from the finding thread to the block
+    unsigned int found_digit, found_above;
+    unsigned long long found_mass;
+    float red_f[32];
+    int red_i[32];
+    double red_d[32];
+    unsigned int scan_u[32];
+};
+
+// Finds the digit where the running (count, mass), taken from the largest
+// digit down, first satisfies the target, among elements whose higher bits
+// equal `prefix_bits` under `prefix_mask`. by_mass: cum_mass >= target_mass;
+// else cum_count >= target_count. On return sh.found_digit is that digit and
+// sh.found_above / sh.found_mass are the count and mass of the elements in
+// larger digits (added to what the caller carries).
+__device__ void radix_pass(const float* __restrict__ p, int V, unsigned int prefix_bits, unsigned int prefix_mask,
+                           int shift, int n_bins, bool by_mass, unsigned int target_count,
+                           unsigned long long target_mass, unsigned int carry_count, unsigned long long carry_mass,
+                           Shared& sh) {
+    for (int i = threadIdx.x; i < BINS; i += THREADS) {
+        sh.count[i] = 0;
+        sh.mass[i] = 0;
+    }
+    if (threadIdx.x == 0) {
+        sh.found_digit = 0;                 // the smallest digit, when the target is never met
+        sh.found_above = 0xffffffffu;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        const float v = p[i];
+        const unsigned int bits = __float_as_uint(v);
+        if ((bits & prefix_mask) == prefix_bits) {
+            const unsigned int d = (bits >> shift) & (n_bins - 1);
+            atomicAdd(&sh.count[d], 1u);
+            atomicAdd(&sh.mass[d], mass_of(v));
+        }
+    }
+    __syncthreads();
+    // scan from the largest digit down: thread t owns digits n_bins-1-2t and n_bins-2-2t
+    const int d0 = n_bins - 1 - 2 * (int)threadIdx.x, d1 = d0 - 1;
+    const unsigned int c0 = d0 >= 0 ? sh.count[d0] : 0, c1 = d1 >= 0 ? sh.count[d1] : 0;
+    const unsigned long long m0 = d0 >= 0 ? sh.mass[d0] : 0, m1 = d1 >= 0 ? sh.mass[d1] : 0;
+    unsigned int cs = c0 + c1;
+    unsigned long long ms = m0 + m1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int c = __shfl_up_sync(0xffffffffu, cs, o);
+        const unsigned long long m = __shfl_up_sync(0xffffffffu, ms, o);
+        if (lane >= o) {
+            cs += c;
+            ms += m;
+        }
+    }
+    if (lane == 31) {
+        sh.warp_count[warp] = cs;
+        sh.warp_mass[warp] = ms;
+    }
+    __syncthreads();
+    unsigned int cbase = carry_count;
+    unsigned long long mbase = carry_mass;
+    for (int w = 0; w < warp; w++) {
+        cbase += sh.warp_count[w];
+        mbase += sh.warp_mass[w];
+    }
+    // exclusive values before this thread's first digit
+    const unsigned int c_before = cbase + cs - (c0 + c1);
+    const unsigned long long m_before = mbase + ms - (m0 + m1);
+    auto met = [&](unsigned int c, unsigned long long m) {
+        return by_mass ? (m >= target_mass) : (c >= target_count);
+    };
+    if (c0 > 0 && !met(c_before, m_before) && met(c_before + c0, m_before + m0)) {
+        sh.found_digit = (unsigned int)d0;
+        sh.found_above = c_before;
+        sh.found_mass = m_before;
+    } else if (c1 > 0 && !met(c_before + c0, m_before + m0) && met(c_before + c0 + c1, m_before + m0 + m1)) {
+        sh.found_digit = (unsigned int)d1;
+        sh.found_above = c_before + c0;
+        sh.found_mass = m_before + m0;
+    }
+    __syncthreads();
+    if (sh.found_above == 0xffffffffu) {
+        // target beyond everything (rounding): end at the smallest populated digit
+        if (threadIdx.x == 0) {
+            int d = 0;
+            while (d < n_bins - 1 && sh.count[d] == 0) d++;
+            unsigned int c = carry_count;
+            unsigned long long m = carry_mass;
+            for (int e = n_bins - 1; e > d; e--) {
+                c += sh.count[e];
+                m += sh.mass[e];
+            }
+            sh.found_digit = (unsigned int)d;
+            sh.found_above = c;
+            sh.found_mass = m;
+        }
+        __syncthreads();
+    }
+}
+
+// The smallest prefix of the sorted order whose count reaches target_count
+// (by_mass false) or whose mass reaches target_mass (by_mass true).
+__device__ Prefix find_prefix(const float* __restrict__ p, int V, bool by_mass, unsigned int target_count,
+                              unsigned long long target_mass, Shared& sh) {
+    unsigned int bits = 0, mask = 0, above = 0;
+    unsigned long long mass = 0;
+    if (by_mass && target_mass == 0) target_mass = 1;      // a draw of exactly 0 takes the first element
+    if (!by_mass && target_count == 0) target_count = 1;
+    const int shifts[3] = {21, 10, 0}, nb[3] = {2048, 2048, 1024};
+    for (int r = 0; r < 3; r++) {
+        radix_pass(p, V, bits, mask, shifts[r], nb[r], by_mass, target_count, target_mass, above, mass, sh);
+        bits |= sh.found_digit << shifts[r];
+        mask |= (unsigned int)(nb[r] - 1) << shifts[r];
+        above = sh.found_above;
+        mass = sh.found_mass;
+        __syncthreads();
+    }
+    // `bits` is the probability at which the prefix ends; sh.count/mass of its last digit are still valid
+    const unsigned int last = bits & 1023u;
+    const unsigned int n_eq = sh.count[last];
+    const unsigned long long pm = mass_of(__uint_as_float(bits));
+    unsigned int ties;
+    if (by_mass) {
+        if (pm == 0 || target_mass <= mass) ties = 1;
+        else {
+            const unsigned long long need = target_mass - mass;
+            const unsigned long long t = (need + pm - 1) / pm;
+            ties = (unsigned int)(t < 1 ? 1 : (t > n_eq ? n_eq : t));
+        }
+    } else {
+        ties = target_count > above ? target_count - above : 1;
+        if (ties > n_eq) ties = n_eq;
+    }
+    if (ties < 1) ties = 1;
+    Prefix out{bits, above, ties, mass + (unsigned long long)ties * pm};
+    __syncthreads();
+    return out;
+}
+
+// Id of the j-th (1-based) element, by ascending id, whose probability bits equal `value`.
+__device__ int nth_equal(const float* __restrict__ p, int V, unsigned int value, unsigned int j, Shared& sh) {
+    const int per = (V + THREADS - 1) / THREADS;
+    const int lo = threadIdx.x * per, hi = min(V, lo + per);
+    unsigned int c = 0;
+    for (int i = lo; i < hi; i++) c += __float_as_uint(p[i]) == value;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned int cs = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned int t = __shfl_up_sync(0xffffffffu, cs, o);
+        if (lane >= o) cs += t;
+    }
+    if (lane == 31) sh.scan_u[warp] = cs;
+    if (threadIdx.x == 0) sh.red_i[0] = -1;
+    __syncthreads();
+    unsigned int before = cs - c;
+    for (int w = 0; w < warp; w++) before += sh.scan_u[w];
+    if (c > 0 && before < j && j <= before + c) {
+        unsigned int seen = before;
+        for (int i = lo; i < hi; i++) {
+            if (__float_as_uint(p[i]) == value && ++seen == j) {
+                sh.red_i[0] = i;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const int r = sh.red_i[0];
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ double splitmix_uniform(unsigned long long* state) {
+    unsigned long long z = (*state += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (double)(z >> 11) * (1.0 / 9007199254740992.0);
+}
+
+struct SampleParams {
+    float temp, top_p, min_p;
+    int top_k;
+};
+
+// First maximum of a row (strict >, lowest index on ties: sampler.c:124-129).
+__device__ int block_argmax(const float* __restrict__ row, int V, Shared& sh, float* max_out) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        const float v = row[i];
+        if (v > bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (v2 > bv || (v2 == bv && i2 < bi)) {
+            bv = v2;
+            bi = i2;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) {
+        sh.red_f[warp] = bv;
+        sh.red_i[warp] = bi;
+    }
+    __syncthreads();
+    bv = sh.red_f[lane];
+    bi = sh.red_i[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (v2 > bv || (v2 == bv && i2 < bi)) {
+            bv = v2;
+            bi = i2;
+        }
+    }
+    __syncthreads();
+    *max_out = bv;
+    return bi == 0x7fffffff ? 0 : bi;
+}
+
+// One CTA per row. The row of logits is overwritten with probabilities when
+// the temperature is positive (the reference's sampler also works in place).
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict__ params,
+              unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out) {
+    __shared__ Shared sh;
+    const SampleParams sp{params[0], params[1], params[2], (int)params[3]};
+    const int b = blockIdx.x;
+    float* row = logits + (size_t)b * ld;
+    const int slot = slots ? slots[b] : b;
+    if (slot < 0) {                          // padding row
+        if (threadIdx.x == 0) out[b] = 0;
+        return;
+    }
+    float mx;
+    const int best = block_argmax(row, V, sh, &mx);
+    if (sp.temp <= 0.f) {
+        if (threadIdx.x == 0) out[b] = best;
+        return;
+    }
+    // p_i = expf((l_i - max) / temp) * (float)(1 / sum), the sum in double (sampler.c:132-143)
+    double part = 0.0;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        const float e = expf((row[i] - mx) / sp.temp);
+        row[i] = e;
+        part += (double)e;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) sh.red_d[warp] = part;
+    __syncthreads();
+    double sum = 0.0;
+    for (int w = 0; w < THREADS / 32; w++) sum += sh.red_d[w];
+    const float inv = (float)(1.0 / sum);
+    unsigned int n_floor = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += THREADS) row[i] = row[i] * inv;
+    __syncthreads();
+    const float p_best = row[best];
+
+    // the kept prefix: top-k, then min-p, then top-p (sampler.c:146-175)
+    unsigned int n = (unsigned int)V;
+    if (sp.top_k > 0 && (unsigned int)sp.top_k < n) n = (unsigned int)sp.top_k;
+    if (sp.min_p > 0.f) {
+        const float floor_p = sp.min_p * p_best;
+        unsigned int c = 0;
+        for (int i = threadIdx.x; i < V; i += THREADS) c += row[i] >= floor_p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) sh.scan_u[warp] = c;
+        __syncthreads();
+        for (int w = 0; w < THREADS / 32; w++) n_floor += sh.scan_u[w];
+        __syncthreads();
+        if (n_floor < 1) n_floor = 1;
+        if (n_floor < n) n = n_floor;
+    }
+    if (sp.top_p < 1.0f) {
+        const unsigned long long target = __double2ull_ru((double)sp.top_p * 1152921504606846976.0);
+        const Prefix pp = find_prefix(row, V, true, 0, target, sh);
+        const unsigned int np = pp.above + pp.ties;
+        if (np < n) n = np;
+    }
+    if (n < 1) n = 1;
+    // mass of the kept prefix, then the draw r = U * total and the walk (sampler.c:178-186)
+    const Prefix kept = find_prefix(row, V, false, n, 0, sh);
+    unsigned long long state = rng[slot];
+    const double u = splitmix_uniform(&state);
+    const double r = u * (double)kept.mass;
+    unsigned long long target = __double2ull_ru(r);
+    if (target > kept.mass) target = kept.mass;
+    Prefix hit = find_prefix(row, V, true, 0, target, sh);
+    unsigned int rank = hit.above + hit.ties;              // 1-based place in the sorted order
+    unsigned int value = hit.value, j = hit.ties;
+    if (rank > n) {                                        // only through rounding: the last kept one
+        value = kept.value;
+        j = kept.ties;
+    }
+    const int id = nth_equal(row, V, value, j, sh);
+    if (threadIdx.x == 0) {
+        out[b] = id >= 0 ? id : best;
+        rng[slot] = state;
+    }
+}
+
+// One thread per row: the reference's loop over the ring of recent tokens,
+// entry by entry (a token that sits in the ring c times is penalised c times).
+// The ring rows are `stride` apart; the window in use is params[7] <= stride.
+__global__ void penalties_kernel(float* __restrict__ logits, int B, int V, int ld, const int* __restrict__ ring,
+                                 const int* __restrict__ ring_n, int stride, const int* __restrict__ slots,
+                                 const float* __restrict__ params) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const float repeat = params[4], freq = params[5], presence = params[6];
+    const int window = min((int)params[7], stride);
+    if (window <= 0 || (repeat == 1.0f && freq == 0.0f && presence == 0.0f)) return;   // sampler.c:81-84
+    const int slot = slots ? slots[b] : b;
+    if (slot < 0) return;
+    const int n = min(ring_n[slot], window);
+    const int* r = ring + (size_t)slot * stride;
+    float* row = logits + (size_t)b * ld;
+    for (int i = 0; i < n; i++) {
+        const int tok = r[i];
+        if (tok < 0 || tok >= V) continue;
+        int count = 0;
+        for (int k = 0; k < n; k++) count += r[k] == tok;
+        float l = row[tok];
+        if (repeat != 1.0f) l = l > 0.f ? l / repeat : l * repeat;
+        l -= freq * (float)count;
+        l -= presence;
+        row[tok] = l;
+    }
+}
+
+// ring[slot][head] = token; head advances; the count saturates at the window.
+__global__ void accept_kernel(const int* __restrict__ tokens, int B, int* __restrict__ ring, int* __restrict__ ring_n,
+                              int* __restrict__ ring_head, int stride, const int* __restrict__ slots,
+                              const float* __restrict__ params) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    const int window = min((int)params[7], stride);
+    if (b >= B || window <= 0) return;
+    const int slot = slots ? slots[b] : b;
+    if (slot < 0) return;
+    const int head = ring_head[slot] % window;
+    ring[(size_t)slot * stride + head] = tokens[b];
+    ring_head[slot] = (head + 1) % window;
+    if (ring_n[slot] < window) ring_n[slot]++;
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
+    __shared__ Shared sh;
+    float mx;
+    const int best = block_argmax(logits + (size_t)blockIdx.x * ld, V, sh, &mx);
+    if (threadIdx.x == 0) out[blockIdx.x] = best;
+}
+
+}  // namespace
+
+MYNAH_API int mynah_argmax(const float* logits, int B, int V, int ld, int* out, cudaStream_t stream) {
+    if (B == 0) return 0;
+    MYNAH_REQUIRE(B > 0 && V > 0 && ld >= V, "argmax: bad sizes B=%d V=%d ld=%d", B, V, ld);
+    argmax_kernel<<<B, THREADS, 0, stream>>>(logits, V, ld, out);
+    return mynah_check_launch("argmax");
+}
+
+// logits [B, ld] are overwritten. params (device): temp, top_p, min_p, top_k,
+// repeat, freq, presence as floats; they are read on the device so that a
+// captured step serves every setting. rng: one 64-bit generator state per
+// slot; slots [B] maps rows to slots (null: row b is slot b; a negative slot
+// marks a padding row). out [B] receives the token ids.
+MYNAH_API int mynah_sample(float* logits, int B, int V, int ld, const float* params,
+                           unsigned long long* rng, const int* slots, int* out, cudaStream_t stream) {
+    if (B == 0) return 0;
+    MYNAH_REQUIRE(B > 0 && V > 0 && ld >= V, "sample: bad sizes B=%d V=%d ld=%d", B, V, ld);
+    MYNAH_REQUIRE(params != nullptr && rng != nullptr, "sample: parameters and generator states are required");
+    sample_kernel<<<B, THREADS, 0, stream>>>(logits, V, ld, params, rng, slots, out);
+    return mynah_check_launch("sample");
+}
+
+MYNAH_API int mynah_apply_penalties(float* logits, int B, int V, int ld, const int* ring, const int* ring_n,
+                                    int window, const int* slots, const float* params, cudaStream_t stream) {
+    if (B == 0 || window == 0) return 0;
+    penalties_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(logits, B, V, ld, ring, ring_n, window, slots, params);
+    return mynah_check_launch("apply_penalties");
+}
+
+namespace {
+// After a sampled decode step: the sampled token becomes the sequence's next
+// input, one position further on.
+__global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ sampled,
+                                      int* __restrict__ tok_pos, int* __restrict__ kv_len,
+                                      const int* __restrict__ slots, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B || slots[b] < 0) return;
+    tokens[b] = sampled[b];
+    tok_pos[b] += 1;
+    kv_len[b] += 1;
+}
+}  // namespace
+
+MYNAH_API int mynah_decode_advance(int* tokens, const int* sampled, int* tok_pos, int* kv_len, const int* slots,
+                                   int B, cudaStream_t stream) {
+    if (B == 0) return 0;
+    decode_advance_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(tokens, sampled, tok_pos, kv_len, slots, B);
+    return mynah_check_launch("decode_advance");
+}
+
+MYNAH_API int mynah_sampler_accept(const int* tokens, int B, int* ring, int* ring_n, int* ring_head, int window,
+                                   const int* slots, const float* params, cudaStream_t stream) {
+    if (B == 0 || window == 0) return 0;
+    accept_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(tokens, B, ring, ring_n, ring_head, window, slots, params);
+    return mynah_check_launch("sampler_accept");
+}

@@ -1,0 +1,90 @@
+"""The Python entry point: load a model folder, generate from token ids.
+
+    from mynah_slm_b200 import LLM
+    llm = LLM("path/to/folder", dtype="bfloat16", max_tokens=65536)
+    out = llm.generate([[1, 2, 3], [4, 5]], max_new=32, temp=0.0)
+    out[0].tokens
+
+Option names and meanings are those of the reference's `run` command
+(mynah-slm cli/main.c:335-356): max_new (-n), temp, top_k, top_p, min_p, seed,
+repeat_penalty. Prompts are token ids: the text side (tokenizer, chat
+template) is not part of this library.
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from ..sampling.sampler import SamplingParams, stream_state
+from .engine import Engine, StepEntry
+from .generate import Request, Result, Timing, generate
+
+
+class EngineBackend:
+    """`generate`'s view of an engine: prompts in one step, then one sampled
+    token per sequence per step, host token ids in and out."""
+
+    def __init__(self, engine: Engine, params: SamplingParams):
+        self.engine = engine
+        self.params = params
+        self.max_positions = engine.spec.max_positions
+        engine.sampler.set_params(params)
+
+    def free_tokens(self) -> int:
+        return self.engine.free_tokens()
+
+    def open(self, request_index: int, prompt: Sequence[int]) -> int:
+        slot = self.engine.open_sequence()
+        self.engine.sampler.start_sequences([slot], [stream_state(self.params.seed, request_index)], [prompt])
+        return slot
+
+    def close(self, slot: int) -> None:
+        self.engine.close_sequence(slot)
+
+    def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> list[int]:
+        eng = self.engine
+        logits = eng.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
+        slots_t = torch.tensor(list(slots), dtype=torch.int32, device=eng.device)
+        toks = eng.sampler.sample(logits, slots_t).cpu().tolist()
+        eng.check_status()
+        return toks
+
+    def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> list[int]:
+        out = self.engine.decode_sampled(slots, tokens)
+        return out[:len(slots)].cpu().tolist()
+
+
+class LLM:
+    def __init__(self, model: str, dtype: str = "bfloat16", max_tokens: int = 65536, max_seqs: Optional[int] = None,
+                 device: str = "cuda:0", use_graphs: bool = True):
+        t0 = time.perf_counter()
+        self.engine = Engine.from_folder(model, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs,
+                                         device=device, use_graphs=use_graphs)
+        torch.cuda.synchronize()
+        self.load_s = time.perf_counter() - t0
+        self.last_timing: Optional[Timing] = None
+
+    @property
+    def eos_token_ids(self) -> tuple[int, ...]:
+        return self.engine.spec.eos_token_ids
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new: int = 128, temp: float = 0.6, top_k: int = 20,
+                 top_p: float = 0.95, min_p: float = 0.0, seed: int = 0, repeat_penalty: float = 1.0,
+                 freq_penalty: float = 0.0, presence_penalty: float = 0.0, penalty_window: int = 64,
+                 stop_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False, max_batch: int = 64,
+                 callback: Optional[Callable[[int, int], int]] = None) -> list[Result]:
+        """Generate for every prompt (a list of token ids each). `stop_ids`
+        defaults to the model's stop set (config.json and generation_config.json);
+        `ignore_eos` empties it. Results are in the order of the prompts."""
+        params = SamplingParams(temp=temp, top_k=top_k, top_p=top_p, min_p=min_p, repeat_penalty=repeat_penalty,
+                                freq_penalty=freq_penalty, presence_penalty=presence_penalty,
+                                penalty_window=penalty_window, seed=seed)
+        stop = () if ignore_eos else (self.eos_token_ids if stop_ids is None else tuple(stop_ids))
+        backend = EngineBackend(self.engine, params)
+        timing = Timing(load_s=self.load_s, device_name=torch.cuda.get_device_name(self.engine.device))
+        reqs = [Request(list(p), max_new) for p in prompts]
+        out = generate(backend, reqs, stop_ids=stop, max_batch=max_batch, callback=callback, timing=timing)
+        self.last_timing = timing
+        return out

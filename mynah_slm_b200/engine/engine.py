@@ -1,0 +1,448 @@
+"""The engine: a model on the device, its cache, and the ONE step function.
+
+`Engine.step` takes a batch of sequences that either all bring the first
+tokens of their prompts (or a further piece of them) or all go on by one
+token. It runs exactly the tokens it is given, as one batch, against what
+earlier steps left in the cache, and returns fp32 logits at the wanted
+places. It replaces the reference's `mynah_slm_forward(state, token, logits)`
+(mynah-slm src/arch_qwen3.c:178-252), which takes one token of one sequence;
+a loop of single-token steps here gives the same logits as one step over the
+whole prompt.
+
+A step that brings one token per sequence is replayed from a CUDA graph
+(captured per batch-size bucket; unused rows of a bucket are padding rows
+that read and write nothing), so a decode step costs one copy of the batch
+description and one graph launch. With `sample=True` the graph also samples
+and feeds each sequence's token back as its next input, so that many steps
+can run without the host in between.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.pages import PAGE_TOKENS, CacheError
+from ..cache.storage import Cache
+from ..config.spec import ModelSpec
+from ..ops import kernels
+from ..ops.lib import KernelError
+from ..parts.base import Residual
+from ..registry import read_config_folder
+from ..sampling.sampler import SamplerState, SamplingParams
+from ..weights.loader import load_into
+from ..weights.safetensors_io import Checkpoint
+from .context import StepContext, StepLayout, device_context
+from .model import Model
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()        # places among `tokens` whose logits are wanted
+
+
+class Runtime:
+    """Device-wide things that parts share: the compute type, lookup tables
+    built once, scratch memory, and the status word kernels report through."""
+
+    def __init__(self, device, act_dtype: torch.dtype, max_positions: int):
+        self.device = device
+        self.act_dtype = act_dtype
+        self.max_positions = max_positions
+        self.tables: dict = {}
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self._scratch: Optional[torch.Tensor] = None
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+
+    def attn_scratch(self, B: int, H: int, HD: int, splits: int) -> torch.Tensor:
+        need = B * H * splits * (HD + 2)
+        if self._scratch is None or self._scratch.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                raise EngineError("attention scratch would have to grow during graph capture")
+            self._scratch = torch.empty((need,), dtype=torch.float32, device=self.device)
+        return self._scratch
+
+
+class _Staging:
+    """A few pinned buffers used in turn for the batch description, so that
+    the host can write the next one while an earlier copy is still in flight."""
+
+    def __init__(self, n: int = 4):
+        self.bufs: list[Optional[torch.Tensor]] = [None] * n
+        self.events = [torch.cuda.Event() for _ in range(n)]
+        self.used = [False] * n
+        self.i = 0
+
+    def get(self, size: int) -> tuple[torch.Tensor, int]:
+        i = self.i
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.used[i]:
+            self.events[i].synchronize()
+        b = self.bufs[i]
+        if b is None or b.numel() < size:
+            b = torch.empty((max(size, 1024),), dtype=torch.int32, pin_memory=True)
+            self.bufs[i] = b
+        return b, i
+
+    def sent(self, i: int) -> None:
+        self.events[i].record()
+        self.used[i] = True
+
+
+@dataclass
+class _DecodeGraph:
+    bucket: int
+    layout: StepLayout
+    meta: torch.Tensor                 # static device copy of the batch description
+    ctx: StepContext
+    splits: int
+    graphs: dict = field(default_factory=dict)     # mode -> (CUDAGraph, output tensor, kernels per replay)
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, checkpoint: Checkpoint, dtype="bfloat16", max_tokens: int = 4096,
+                 max_seqs: Optional[int] = None, device="cuda:0", use_graphs: bool = True,
+                 penalty_window: int = 64):
+        if isinstance(dtype, str):
+            if dtype not in DTYPES:
+                raise EngineError(f"dtype {dtype!r} is not one of {sorted(DTYPES)}")
+            dtype = DTYPES[dtype]
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise EngineError(f"dtype {dtype} is not supported (bfloat16 or float32)")
+        if not torch.cuda.is_available():
+            raise EngineError("mynah_slm_b200 needs a CUDA device (B200, sm_100); there is no CPU fallback")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        from ..ops import lib
+        lib.load()                                 # fails loudly when the kernels are missing
+        self.spec = spec
+        self.dtype = dtype
+        self.model = Model(spec)
+        self.runtime = Runtime(self.device, dtype, spec.max_positions)
+        load_into(self.model.tensor_specs(), checkpoint, self.runtime)
+        self.n_pages = max(1, -(-int(max_tokens) // PAGE_TOKENS))
+        self.max_seqs = int(max_seqs) if max_seqs else min(self.n_pages, 1024)
+        self.cache = Cache(self.model.cache_plan(), self.n_pages, self.max_seqs, dtype, self.device)
+        self.n_groups = len(self.cache.plan.groups)
+        self.sampler = SamplerState(self.max_seqs, self.device, penalty_window)
+        self.sampler.set_params(SamplingParams.greedy())
+        self.use_graphs = use_graphs
+        # a part that plans on the host (reads ctx.host_*) cannot be replayed from a graph
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.model.parts())
+        self._staging = _Staging()
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.launches = 0                          # kernels of this package launched (see count_launches)
+        self.vocab_size = spec.vocab_size
+
+    # ------------------------------------------------------------ creation
+    @classmethod
+    def from_folder(cls, folder: str, **kw) -> "Engine":
+        typed = read_config_folder(folder)
+        ckpt = Checkpoint(folder)
+        try:
+            return cls(typed.model_spec(), ckpt, **kw)
+        finally:
+            ckpt.close()
+
+    # ----------------------------------------------------------- sequences
+    def open_sequence(self) -> int:
+        return self.cache.open()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.pages.length[slot]
+
+    def free_tokens(self) -> int:
+        return min(p.n_free for p in self.cache.pages.pools) * PAGE_TOKENS
+
+    # ------------------------------------------------------------- helpers
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise EngineError("a step needs at least one sequence")
+        seen = set()
+        V = self.spec.vocab_size
+        for e in entries:
+            if e.slot in seen:
+                raise EngineError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if e.slot not in self.cache.pages.length:
+                raise EngineError(f"slot {e.slot} is not open")
+            n = len(e.tokens)
+            if n < 1:
+                raise EngineError(f"slot {e.slot} brings no tokens")
+            toks = np.asarray(e.tokens)
+            if toks.dtype.kind not in "iu":
+                raise EngineError(f"the tokens of slot {e.slot} are not integers")
+            if int(toks.min()) < 0 or int(toks.max()) >= V:
+                bad = int(toks.min()) if int(toks.min()) < 0 else int(toks.max())
+                raise EngineError(f"token id {bad} lies outside the vocabulary of {V}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise EngineError(f"wanted place {w} lies outside the {n} tokens of slot {e.slot}")
+            if self.cache.pages.length[e.slot] + n > self.spec.max_positions:
+                raise EngineError(f"slot {e.slot} would grow to {self.cache.pages.length[e.slot] + n} positions, "
+                                  f"the model allows {self.spec.max_positions}")
+
+    def _choose_splits(self, B: int, max_kv: int) -> int:
+        """Splits of the decode attention: enough CTAs for about two waves,
+        never more than the pages of the longest sequence."""
+        kv_heads = max((g.kv_heads for g in self.cache.plan.groups), default=1) or 1
+        want = -(-2 * self.runtime.sm_count // max(1, B * kv_heads))
+        pages = max(1, -(-max_kv // PAGE_TOKENS))
+        return int(max(1, min(want, pages, 64)))
+
+    def _fill(self, buf_np: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], pad_to: int = 0):
+        """Write the batch description into a host buffer. Returns
+        (max_q_len, want_count)."""
+        pages = self.cache.pages
+        v = lambda name: layout.view(buf_np, name)
+        tokens, tok_seq, tok_pos = v("tokens"), v("tok_seq"), v("tok_pos")
+        cu_q, kv_len, slots, want = v("cu_q"), v("kv_len"), v("slots"), v("want")
+        row = 0
+        wi = 0
+        max_q = 0
+        cu_q[0] = 0
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            past = pages.length[e.slot]
+            tokens[row:row + n] = e.tokens
+            tok_seq[row:row + n] = b
+            tok_pos[row:row + n] = np.arange(past, past + n, dtype=np.int32)
+            for w in e.want:
+                want[wi] = row + int(w)
+                wi += 1
+            row += n
+            cu_q[b + 1] = row
+            kv_len[b] = past + n
+            slots[b] = e.slot
+            max_q = max(max_q, n)
+        B = len(entries)
+        if layout.B > B:                                  # padding sequences and rows
+            cu_q[B + 1:] = row
+            kv_len[B:] = 0
+            slots[B:] = -1
+        if layout.T > row:
+            tokens[row:] = 0
+            tok_seq[row:] = -1
+            tok_pos[row:] = 0
+        for g in range(self.n_groups):
+            indptr, base, ids = v(f"indptr{g}"), v(f"base{g}"), v(f"ids{g}")
+            n_ids = 0
+            indptr[0] = 0
+            for b, e in enumerate(entries):
+                held, first = pages.held(e.slot, g)
+                k = len(held)
+                if n_ids + k > len(ids):
+                    raise EngineError("the page lists of this step outgrow their buffer")
+                ids[n_ids:n_ids + k] = held
+                n_ids += k
+                indptr[b + 1] = n_ids
+                base[b] = first
+            if layout.B > B:
+                indptr[B + 1:] = n_ids
+                base[B:] = 0
+        return max_q, wi
+
+    # ------------------------------------------------------------- forward
+    def _forward(self, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
+        """embedding -> layers in schedule order -> final norm of the wanted
+        rows -> head. Returns fp32 logits [rows, vocab]."""
+        x = self.model.embedding.forward(ctx.tokens)
+        stream = Residual(x)
+        views = self.cache.views
+        for i, e in enumerate(self.model.schedule):
+            self.model.layers[e.layer].forward(stream, ctx, views[i])
+        h = self.model.final_norm.apply(stream, rows=want_rows)
+        return self.model.head.forward(h)
+
+    # ---------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the tokens of `entries` and return fp32 logits [n_want, vocab]
+        (device), in the order of the entries and of their `want`."""
+        self._validate(entries)
+        pages = self.cache.pages
+        for e in entries:
+            pages.reserve(e.slot, len(e.tokens))
+        is_decode = all(len(e.tokens) == 1 for e in entries)
+        if is_decode and self.use_graphs and self.graph_safe:
+            logits = self._decode_graph_step(entries, "plain")
+            rows = [b for b, e in enumerate(entries) for _ in e.want]
+            if rows == list(range(len(entries))):
+                out = logits[:len(entries)].clone()          # the graph's output buffer is reused by the next step
+            else:
+                out = logits[torch.tensor(rows, dtype=torch.int64, device=self.device)]
+        else:
+            out = self._eager_step(entries, is_decode)
+        for e in entries:
+            pages.commit(e.slot, len(e.tokens))
+        return out
+
+    def _eager_step(self, entries: Sequence[StepEntry], is_decode: bool) -> torch.Tensor:
+        B = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        wants = [(b, int(w)) for b, e in enumerate(entries) for w in e.want]
+        ids_cap = [sum(len(self.cache.pages.held(e.slot, g)[0]) for e in entries) for g in range(self.n_groups)]
+        # wanted rows are normalised once each; duplicates are expanded afterwards
+        layout = StepLayout(T=T, B=B, W=max(len(wants), 1), ids_cap=ids_cap)
+        host, hi = self._staging.get(layout.size)
+        max_q, n_want = self._fill(host.numpy(), layout, entries)
+        want_np = layout.view(host.numpy(), "want")[:n_want]
+        uniq, inverse = np.unique(want_np, return_inverse=True)
+        layout.view(host.numpy(), "want")[:len(uniq)] = uniq
+        dev = torch.empty((layout.size,), dtype=torch.int32, device=self.device)
+        dev.copy_(host[:layout.size], non_blocking=True)
+        self._staging.sent(hi)
+        max_kv = max(self.cache.pages.length[e.slot] + len(e.tokens) for e in entries)
+        splits = self._choose_splits(B, max_kv) if is_decode else 1
+        ctx = device_context(layout, dev, [self.n_pages] * self.n_groups, max_q, is_decode, splits,
+                             self.runtime.status, self.dtype)
+        self._host_fields(ctx, entries)
+        if n_want == 0:
+            # nothing wanted: the cache is still filled; skip norm and head
+            self._forward_layers_only(ctx)
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        rows = ctx.want[:len(uniq)]
+        logits = self._forward(ctx, rows)
+        if len(uniq) != n_want or not np.array_equal(inverse, np.arange(n_want)):
+            logits = logits[torch.from_numpy(inverse.astype(np.int64)).to(self.device)]
+        return logits
+
+    def _forward_layers_only(self, ctx: StepContext) -> None:
+        x = self.model.embedding.forward(ctx.tokens)
+        stream = Residual(x)
+        for i, e in enumerate(self.model.schedule):
+            self.model.layers[e.layer].forward(stream, ctx, self.cache.views[i])
+
+    def _host_fields(self, ctx: StepContext, entries: Sequence[StepEntry]) -> None:
+        ctx.host_q_lens = [len(e.tokens) for e in entries]
+        ctx.host_past = [self.cache.pages.length[e.slot] for e in entries]
+        ctx.host_slots = [e.slot for e in entries]
+
+    # --------------------------------------------------------- decode graph
+    @staticmethod
+    def _bucket(B: int) -> int:
+        b = 1
+        while b < B:
+            b *= 2
+        return b
+
+    def _graph_for(self, B: int, max_kv: int) -> _DecodeGraph:
+        bucket = self._bucket(B)
+        g = self._graphs.get(bucket)
+        if g is not None:
+            return g
+        max_pages_seq = -(-self.spec.max_positions // PAGE_TOKENS)
+        cap = min(bucket * max_pages_seq, self.n_pages + bucket)
+        layout = StepLayout(T=bucket, B=bucket, W=1, ids_cap=[cap] * self.n_groups)
+        meta = torch.zeros((layout.size,), dtype=torch.int32, device=self.device)
+        # the split count is part of the captured launch: sized for a context of a few thousand
+        splits = self._choose_splits(bucket, max(max_kv, 4096))
+        ctx = device_context(layout, meta, [self.n_pages] * self.n_groups, 1, True, splits, self.runtime.status, self.dtype)
+        g = _DecodeGraph(bucket, layout, meta, ctx, splits)
+        self._graphs[bucket] = g
+        return g
+
+    def _decode_graph_step(self, entries: Sequence[StepEntry], mode: str, replays: int = 1) -> torch.Tensor:
+        B = len(entries)
+        max_kv = max(self.cache.pages.length[e.slot] + 1 for e in entries)
+        g = self._graph_for(B, max_kv)
+        host, hi = self._staging.get(g.layout.size)
+        self._fill(host.numpy(), g.layout, entries)
+        g.meta.copy_(host[:g.layout.size], non_blocking=True)
+        self._staging.sent(hi)
+        self._host_fields(g.ctx, entries)
+        return self._run_graph(g, mode, replays)
+
+    def _run_graph(self, g: _DecodeGraph, mode: str, replays: int = 1) -> torch.Tensor:
+        """mode: "plain" (logits), "sample" (tokens), "loop" (tokens, and each
+        sequence's token becomes its next input one position on)."""
+        from ..ops import lib
+        if mode not in g.graphs:
+            # first use of this bucket: run once for real (this also sizes scratch
+            # memory and warms the library), then record the same launches
+            n0 = lib.launch_count()
+            out = self._decode_body(g, mode)
+            n_kernels = lib.launch_count() - n0
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                res = self._decode_body(g, mode)
+            lib.add_launches(-n_kernels)              # recorded, not run
+            res.copy_(out)                             # the eager run has produced this step's result
+            g.graphs[mode] = (graph, res, n_kernels)
+            replays -= 1
+        graph, res, n_kernels = g.graphs[mode]
+        for _ in range(replays):
+            graph.replay()
+        lib.add_launches(n_kernels * replays)
+        return res
+
+    def _decode_body(self, g: _DecodeGraph, mode: str) -> torch.Tensor:
+        logits = self._forward(g.ctx, None)
+        if mode == "plain":
+            return logits
+        sampled = self.sampler.sample(logits, g.ctx.slots)
+        if mode == "loop":
+            kernels.decode_advance(g.ctx.tokens, sampled, g.ctx.tok_pos, g.ctx.kv_len, g.ctx.slots)
+        return sampled
+
+    # -------------------------------------------------- sampled decode steps
+    def decode_sampled(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+        """One decode step for `slots` with `tokens` as their next inputs;
+        samples on the device with the sampler's current parameters and returns
+        the int32 tokens [bucket] (device; the first len(slots) rows count)."""
+        entries = [StepEntry(s, (int(t),)) for s, t in zip(slots, tokens)]
+        self._validate(entries)
+        pages = self.cache.pages
+        for e in entries:
+            pages.reserve(e.slot, 1)
+        if self.use_graphs and self.graph_safe:
+            out = self._decode_graph_step(entries, "sample")
+        else:
+            logits = self._eager_step([StepEntry(e.slot, e.tokens, (0,)) for e in entries], True)
+            slots_t = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+            out = self.sampler.sample(logits, slots_t)
+        for e in entries:
+            pages.commit(e.slot, 1)
+        return out
+
+    def decode_loop(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int) -> torch.Tensor:
+        """`n_steps` sampled decode steps without the host in between: each
+        sequence's sampled token is fed back on the device. Returns the tokens
+        of the last step (device). Used where only throughput is wanted."""
+        if not (self.use_graphs and self.graph_safe):
+            raise EngineError("decode_loop needs CUDA graphs")
+        entries = [StepEntry(s, (int(t),)) for s, t in zip(slots, tokens)]
+        self._validate(entries)
+        pages = self.cache.pages
+        for e in entries:
+            if pages.length[e.slot] + n_steps > self.spec.max_positions:
+                raise EngineError(f"slot {e.slot} would outgrow the model's {self.spec.max_positions} positions")
+            pages.reserve(e.slot, n_steps)
+        out = self._decode_graph_step(entries, "loop", replays=n_steps)
+        for e in entries:
+            pages.commit(e.slot, n_steps)
+        return out
+
+    def check_status(self) -> None:
+        """Raise if a kernel met an index it had to refuse. Synchronises."""
+        st = int(self.runtime.status.item())
+        if st:
+            self.runtime.status.zero_()
+            what = [name for bit, name in ((kernels.ST_PAGE_RANGE, "a position without a page"),
+                                           (kernels.ST_POS_RANGE, "a position outside the rotation table"),
+                                           (kernels.ST_TOKEN_RANGE, "a token id outside the vocabulary")) if st & bit]
+            raise EngineError("a kernel refused an index: " + ", ".join(what))

@@ -1,0 +1,24 @@
+"""Chooses the attention kernel of a prompt step.
+
+The tensor-core kernel takes bfloat16 with the head sizes it was built for;
+everything else (the whole 32-bit path, other head sizes) runs the general
+kernel. Both read the same paged cache and give the same result up to
+rounding.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels
+
+# Filled by the tensor-core module when it is present: f(...) -> bool (taken).
+TENSOR_CORE_PREFILL = []
+
+
+def prefill(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
+            k_cache: torch.Tensor, v_cache: torch.Tensor, pages, window: int) -> None:
+    for route in TENSOR_CORE_PREFILL:
+        if route(qkv, out, ctx, H, KV, HD, k_cache, v_cache, pages, window):
+            return
+    kernels.attn_prefill_generic(qkv, out, ctx.B, ctx.max_q_len, H, KV, HD, k_cache, v_cache,
+                                 ctx.cu_q, ctx.kv_len, pages, window, ctx.status)

@@ -1,0 +1,238 @@
+"""Tensor-level wrappers of the kernel entry points.
+
+Each function checks what the kernel cannot (device, dtype, contiguity,
+shapes) and launches on the current CUDA stream. Matrix products of the
+bfloat16 path go to the library (`torch.mm`, i.e. cuBLAS) here unless a
+hand-written kernel takes the shape; everything else is this package's own
+CUDA.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import lib
+from .lib import KernelError, call, code, ptr, stream_ptr
+
+PAGE_TOKENS = 64
+MAX_HEAD_DIM = 256
+
+ST_PAGE_RANGE, ST_POS_RANGE, ST_TOKEN_RANGE = 1, 2, 4
+
+
+def _chk(t: torch.Tensor, name: str, dtype=None, dim=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} has {t.dim()} dimensions, expected {dim}")
+
+
+@dataclass
+class PageTableView:
+    """A cache group's page lists for the sequences of one step (device)."""
+    indptr: torch.Tensor      # int32 [B+1]
+    ids: torch.Tensor         # int32 [>= indptr[B]]
+    base: torch.Tensor        # int32 [B]
+    n_pages: int
+
+
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(table, "embedding table", dim=2)
+    _chk(tokens, "tokens", torch.int32, 1)
+    T, (V, D) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    call("mynah_embed_gather", ptr(table), code(table.dtype), ptr(tokens), ptr(out), T, D, V, stream_ptr())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, act_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h = RMSNorm(x (+ delta)) * gain; x is updated in place when delta is given."""
+    _chk(x, "residual", torch.float32, 2)
+    _chk(gain, "norm gain", dim=1)
+    T, D = x.shape
+    if gain.numel() != D:
+        raise KernelError(f"norm gain has {gain.numel()} elements, the rows have {D}")
+    if delta is not None:
+        _chk(delta, "delta", act_dtype, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match the residual {tuple(x.shape)}")
+    n = T
+    if rows is not None:
+        _chk(rows, "rows", torch.int32, 1)
+        n = rows.numel()
+    if out is None:
+        out = torch.empty((n, D), dtype=act_dtype, device=x.device)
+    call("mynah_rmsnorm", ptr(x), ptr(delta), ptr(gain), code(gain.dtype), ptr(rows), ptr(out), code(act_dtype),
+         n, D, float(eps), stream_ptr())
+    return out
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _chk(x, "residual", torch.float32)
+    _chk(delta, "delta")
+    if delta.shape != x.shape:
+        raise KernelError("residual_add: shapes differ")
+    call("mynah_residual_add", ptr(x), ptr(delta), code(delta.dtype), x.numel(), stream_ptr())
+
+
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(gate_up, "gate_up", dim=2)
+    T, F2 = gate_up.shape
+    if F2 % 2:
+        raise KernelError("swiglu: the input must hold gate and up side by side")
+    if out is None:
+        out = torch.empty((T, F2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    call("mynah_swiglu", ptr(gate_up), ptr(out), code(gate_up.dtype), T, F2 // 2, stream_ptr())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x . w^T with w [out, in] row-major (no bias). float32 runs the
+    package's FFMA kernel (true 32-bit); bfloat16 accumulates in fp32."""
+    _chk(x, "linear input", dim=2)
+    _chk(w, "linear weight", dim=2)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or x.dtype != w.dtype:
+        raise KernelError(f"linear: input [{M},{K}] {x.dtype} does not fit weight [{N},{K2}] {w.dtype}")
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise KernelError("linear: the 32-bit path writes float32")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        call("mynah_gemm_f32", ptr(x), ptr(w), ptr(out), M, N, K, K, K, N, stream_ptr())
+        return out
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: unsupported dtype {x.dtype}")
+    from . import gemm_bf16
+    return gemm_bf16.linear_bf16(x, w, out_dtype, out)
+
+
+def rope_table(n_pos: int, rotary_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    half = rotary_dim // 2
+    cos = torch.empty((n_pos, half), dtype=torch.float32, device=device)
+    sin = torch.empty((n_pos, half), dtype=torch.float32, device=device)
+    # theta is a float in the reference's table builder (mynah-slm src/kernels.c:141)
+    theta32 = float(torch.tensor(theta, dtype=torch.float32))
+    call("mynah_rope_table", ptr(cos), ptr(sin), n_pos, rotary_dim, theta32, stream_ptr())
+    return cos, sin
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, H: int, KV: int, HD: int,
+                       q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                       tok_seq: torch.Tensor, tok_pos: torch.Tensor, pages: PageTableView,
+                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                       status: torch.Tensor) -> None:
+    _chk(qkv, "qkv", dim=2)
+    T, ld = qkv.shape
+    if (q_gain is None) != (k_gain is None):
+        raise KernelError("qk_norm_rope_store: q and k gains go together")
+    gd = 0
+    if q_gain is not None:
+        if q_gain.dtype != k_gain.dtype or q_gain.numel() != HD or k_gain.numel() != HD:
+            raise KernelError("qk_norm_rope_store: the head gains must both have head_dim elements of one dtype")
+        gd = code(q_gain.dtype)
+    n_pos = 0
+    if cos is not None:
+        _chk(cos, "cos table", torch.float32, 2)
+        n_pos = cos.shape[0]
+        if cos.shape[1] * 2 != rotary_dim:
+            raise KernelError("qk_norm_rope_store: the rotation table does not match rotary_dim")
+    if k_cache is not None:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope_store: the cache and the activations differ in dtype")
+        if tuple(k_cache.shape[1:]) != (KV, PAGE_TOKENS, HD):
+            raise KernelError(f"qk_norm_rope_store: cache pages are {tuple(k_cache.shape[1:])}, expected {(KV, PAGE_TOKENS, HD)}")
+    call("mynah_qk_norm_rope_store", ptr(qkv), code(qkv.dtype), T, H, KV, HD, ld,
+         ptr(q_gain), ptr(k_gain), gd, float(eps),
+         ptr(cos), ptr(sin), rotary_dim, n_pos,
+         ptr(tok_seq), ptr(tok_pos),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         ptr(k_cache), ptr(v_cache), ptr(status), stream_ptr())
+
+
+def attn_prefill_generic(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len: int, H: int, KV: int, HD: int,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                         pages: PageTableView, window: int, status: torch.Tensor) -> None:
+    """q is read from the first H*HD columns of `qkv` (row stride qkv.shape[1])."""
+    _chk(qkv, "q", dim=2)
+    _chk(out, "attention output", qkv.dtype, 2)
+    call("mynah_attn_prefill_generic", ptr(qkv), ptr(out), code(qkv.dtype), B, max_q_len, H, KV, HD,
+         qkv.shape[1], out.shape[1], ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
+
+
+def attn_decode_scratch_floats(B: int, H: int, HD: int, n_splits: int) -> int:
+    return int(lib.load().mynah_attn_decode_scratch_floats(B, H, HD, n_splits))
+
+
+def attn_decode(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,
+                k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor, pages: PageTableView,
+                window: int, n_splits: int, scratch: torch.Tensor, status: torch.Tensor) -> None:
+    _chk(qkv, "q", dim=2)
+    _chk(out, "attention output", qkv.dtype, 2)
+    _chk(scratch, "scratch", torch.float32)
+    need = B * H * n_splits * (HD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode: scratch holds {scratch.numel()} floats, {need} are needed")
+    call("mynah_attn_decode", ptr(qkv), ptr(out), code(qkv.dtype), B, H, KV, HD, qkv.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, n_splits, ptr(scratch), ptr(status), stream_ptr())
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(logits, "logits", torch.float32, 2)
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    call("mynah_argmax", ptr(logits), B, V, V, ptr(out), stream_ptr())
+    return out
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, rng: torch.Tensor, slots: Optional[torch.Tensor],
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Overwrites `logits`. params: float32 [7] on the device (temp, top_p,
+    min_p, top_k, repeat, freq, presence); rng: int64 generator state per slot."""
+    _chk(logits, "logits", torch.float32, 2)
+    _chk(rng, "rng states", torch.int64, 1)
+    _chk(params, "sampling parameters", torch.float32, 1)
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    call("mynah_sample", ptr(logits), B, V, V, ptr(params), ptr(rng), ptr(slots), ptr(out), stream_ptr())
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, ring: torch.Tensor, ring_n: torch.Tensor, slots: Optional[torch.Tensor],
+                    params: torch.Tensor) -> None:
+    _chk(logits, "logits", torch.float32, 2)
+    _chk(ring, "ring", torch.int32, 2)
+    B, V = logits.shape
+    call("mynah_apply_penalties", ptr(logits), B, V, V, ptr(ring), ptr(ring_n), ring.shape[1], ptr(slots),
+         ptr(params), stream_ptr())
+
+
+def sampler_accept(tokens: torch.Tensor, ring: torch.Tensor, ring_n: torch.Tensor, ring_head: torch.Tensor,
+                   slots: Optional[torch.Tensor], params: torch.Tensor) -> None:
+    _chk(tokens, "tokens", torch.int32, 1)
+    call("mynah_sampler_accept", ptr(tokens), tokens.numel(), ptr(ring), ptr(ring_n), ptr(ring_head),
+         ring.shape[1], ptr(slots), ptr(params), stream_ptr())
+
+
+def decode_advance(tokens: torch.Tensor, sampled: torch.Tensor, tok_pos: torch.Tensor, kv_len: torch.Tensor,
+                   slots: torch.Tensor) -> None:
+    call("mynah_decode_advance", ptr(tokens), ptr(sampled), ptr(tok_pos), ptr(kv_len), ptr(slots),
+         tokens.numel(), stream_ptr())

@@ -1,0 +1,221 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from a `PartSpec` (its kind and its sizes and constants) and
+knows nothing of the model it sits in. Five families:
+
+  mixer       mixes information along the sequence (attention here); may ask
+              for key/value storage and for fixed-size per-sequence state
+  feed-forward  works on each token alone (dense here; could be routed)
+  norm        normalises the residual stream into a part's input
+  position    position encoding that a mixer applies to its queries and keys
+  block       the arrangement of norms, mixer and feed-forward around the
+              residual stream
+
+Each family has a registry from `kind` to a class; `register_*` adds to it,
+from inside this package or from outside. The engine only ever talks to
+these interfaces.
+
+Interface common to all parts:
+  tensor_specs() -> list[TensorSpec]   the tensors it reads from the checkpoint
+  bind(tensors, runtime)               receives them on the device; may fuse
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping, Optional, Sequence
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+# ----------------------------------------------------------------- tensors
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """A checkpoint tensor a part binds by name.
+
+    role decides the type it is kept in on the device:
+      "matrix"  operand of a matrix product: the run's compute type
+      "gain"    vector applied in fp32 arithmetic: fp32 stays fp32; otherwise
+                bf16 in a bf16 run and fp32 in a 32-bit run
+      "table"   integer table: int32
+    init decides how the random-weights writer fills it: "normal" is
+    N(0, std), "gain" is 1 + N(0, std), "zeros" is all zero.
+    """
+    name: str
+    shape: tuple[int, ...]
+    role: str = "matrix"
+    init: str = "normal"
+    std: float = 0.02
+    ignorable: bool = False      # tolerated in the checkpoint but never read (a stored copy of a tied matrix)
+
+
+# ------------------------------------------------------------ cache requests
+
+@dataclass(frozen=True)
+class KVRequest:
+    """Keys and values per position: kv_heads x head_dim each. window=None
+    keeps every position; window=W keeps the last W."""
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Fixed-size state per sequence, zeroed when a sequence starts."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """What one run of a layer sees of the cache.
+
+    group: id of the storage group whose page lists apply (ctx.pages[group]).
+    k, v: this entry's storage [n_pages, kv_heads, 64, head_dim], or None.
+    writes: False when this run reads the cache another run wrote.
+    state: [max_seqs, *shape] fixed-size state of this entry, or None.
+    """
+    group: Optional[int] = None
+    k: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None
+    writes: bool = True
+    state: Optional[torch.Tensor] = None
+
+
+# ------------------------------------------------------------------- parts
+
+class Part:
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], runtime: "Any") -> None:
+        """`tensors` holds exactly the tensors named by tensor_specs() that the
+        checkpoint has, already on the device in their kept types."""
+
+
+class Norm(Part):
+    def apply(self, stream: "Residual", rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Fold the stream's pending delta in and return the normalised rows
+        (all of them, or those that `rows` selects) in the activation type."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    #: True when the mixer's fused kernel applies it from `fused_tables`
+    fusable = False
+
+    def prepare(self, runtime: "Any") -> None:
+        pass
+
+    def fused_tables(self) -> tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]:
+        """(cos, sin, rotary_dim) for the fused norm+rotation+store kernel."""
+        return None, None, 0
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, ctx: "Any") -> None:
+        """Unfused form: encode positions into q and k in place."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def kv_request(self) -> Optional[KVRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx: "Any", cache: CacheView) -> torch.Tensor:
+        """h: [T, hidden] in the activation type -> [T, hidden] likewise."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx: "Any") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of a layer's parts around the residual stream."""
+
+    def __init__(self, spec: PartSpec, mixer: Mixer, ffn: FeedForward, norms: Mapping[str, Norm]):
+        super().__init__(spec)
+        self.mixer, self.ffn, self.norms = mixer, ffn, dict(norms)
+
+    def parts(self) -> list[Part]:
+        return [self.mixer, self.ffn, *self.norms.values()]
+
+    def forward(self, stream: "Residual", ctx: "Any", cache: CacheView) -> None:
+        raise NotImplementedError
+
+
+class Residual:
+    """The residual stream of a step: fp32 [T, hidden], plus at most one
+    delta that has not been added yet. A norm that follows an add takes both
+    and does the add on its way (one pass over the row instead of two)."""
+
+    def __init__(self, x: torch.Tensor):
+        self.x = x
+        self.pending: Optional[torch.Tensor] = None
+
+    def add(self, delta: torch.Tensor) -> None:
+        if self.pending is not None:
+            self.flush()
+        self.pending = delta
+
+    def flush(self) -> torch.Tensor:
+        if self.pending is not None:
+            from ..ops import kernels
+            kernels.residual_add(self.x, self.pending)
+            self.pending = None
+        return self.x
+
+
+# -------------------------------------------------------------- registries
+
+_REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
+}
+
+
+def _register(family: str, kind: str, cls: Callable[..., Part], replace: bool) -> None:
+    reg = _REGISTRIES[family]
+    if kind in reg and not replace:
+        raise ValueError(f"{family} {kind!r} is already registered")
+    reg[kind] = cls
+
+
+def register_mixer(kind: str, cls, replace: bool = False) -> None:
+    _register("mixer", kind, cls, replace)
+
+
+def register_ffn(kind: str, cls, replace: bool = False) -> None:
+    _register("ffn", kind, cls, replace)
+
+
+def register_norm(kind: str, cls, replace: bool = False) -> None:
+    _register("norm", kind, cls, replace)
+
+
+def register_position(kind: str, cls, replace: bool = False) -> None:
+    _register("position", kind, cls, replace)
+
+
+def register_block(kind: str, cls, replace: bool = False) -> None:
+    _register("block", kind, cls, replace)
+
+
+def build_part(family: str, spec: PartSpec, *args, **kwargs) -> Part:
+    reg = _REGISTRIES[family]
+    if spec.kind not in reg:
+        from ..config.keys import ConfigError
+        raise ConfigError(f"unknown {family} {spec.kind!r}; known: {', '.join(sorted(reg))}")
+    return reg[spec.kind](spec, *args, **kwargs)
+
+
+def known_parts(family: str) -> list[str]:
+    return sorted(_REGISTRIES[family])
