@@ -2,7 +2,12 @@
 // cached keys, split over the key range so that a small batch still fills
 // the GPU, then combined.
 //
-// Split kernel: one CTA per (split, kv head [x head tile], sequence). It reads
+// The unit of splitting is one page (64 positions): split s of a sequence is
+// the s-th page it can see. The partial results of a sequence's pages are
+// combined in page order, so a sequence's output has the same bits whatever
+// else is in the batch and however large the launch was made.
+//
+// Split kernel: one CTA per (page, kv head [x head tile], sequence). It reads
 // each K/V byte of its range once and serves all query heads of the group
 // from it (GQA: query head h reads kv head h / (H/KV), mynah-slm
 // src/kernels.c:256-261). A lane owns 8 consecutive dims of a key; the lanes
@@ -23,7 +28,7 @@ constexpr int WARPS = 4;
 struct DecodeArgs {
     int H, KV, HD, ldq, ldo;
     int window;          // 0: all keys
-    int S;               // splits
+    int S;               // pages a sequence may see at most (grid size and scratch stride)
     int lpk;             // lanes per key: power of two >= HD/8, <= 32
     float scale;
 };
@@ -49,18 +54,20 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     const int HD = a.HD;
     const bool lane_on = u * 8 < HD;
 
-    // key range of this split: whole pages of the visible range
+    // key range of this split: the s-th page of the visible range
     const int hi = kv_len[b];
     int lo = 0;
     if (a.window > 0) lo = max(0, hi - a.window);
     int key_begin = 0, key_end = 0;
     if (hi > 0) {
         const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
-        const int pps = (pg1 - pg0 + a.S - 1) / a.S;
-        const int mp0 = pg0 + s * pps, mp1 = min(pg1, mp0 + pps);
-        if (mp0 < mp1) {
-            key_begin = max(lo, mp0 * PAGE_TOKENS);
-            key_end = min(hi, mp1 * PAGE_TOKENS);
+        if (pg1 - pg0 > a.S) {                         // the launch is too small for this sequence: say so
+            if (threadIdx.x == 0 && s == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
+        }
+        const int mp = pg0 + s;
+        if (mp < pg1) {
+            key_begin = max(lo, mp * PAGE_TOKENS);
+            key_end = min(hi, (mp + 1) * PAGE_TOKENS);
         }
     }
 
@@ -176,9 +183,14 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 
 template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           T* __restrict__ out, int H, int HD, int S, int ldo) {
+                                           T* __restrict__ out, const int* __restrict__ kv_len, int window,
+                                           int H, int HD, int S_max, int ldo) {
     const int h = blockIdx.x, b = blockIdx.y;
-    const size_t row0 = ((size_t)b * H + h) * S;
+    const size_t row0 = ((size_t)b * H + h) * S_max;
+    // only the pages the sequence can see have partial results
+    const int hi = kv_len[b];
+    const int lo = window > 0 ? max(0, hi - window) : 0;
+    const int S = hi > 0 ? min(S_max, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
     float mn = -INFINITY;
     for (int s = 0; s < S; s++) mn = fmaxf(mn, part_ml[(row0 + s) * 2]);
     float ls = 0.f;
@@ -216,7 +228,7 @@ int launch_decode(const void* q, void* out, int B, const DecodeArgs& a, const vo
         attn_decode_split_kernel<T, 4><<<grid, WARPS * 32, 0, stream>>>(qp, kp, vp, kv_len, pt, a, part_o, part_ml, status);
     if (mynah_check_launch("attn_decode_split")) return -1;
     const int threads = a.HD >= 128 ? 128 : (a.HD >= 64 ? 64 : 32);
-    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, a.H, a.HD, a.S, a.ldo);
+    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, kv_len, a.window, a.H, a.HD, a.S, a.ldo);
     return mynah_check_launch("attn_decode_combine");
 }
 

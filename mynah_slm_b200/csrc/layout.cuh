@@ -19,6 +19,7 @@ enum MynahStatus : int {
     MYNAH_ST_PAGE_RANGE = 1,      // a position maps to no page of its sequence
     MYNAH_ST_POS_RANGE = 2,       // a position lies outside the rotation table
     MYNAH_ST_TOKEN_RANGE = 4,     // a token id lies outside the vocabulary
+    MYNAH_ST_SPLIT_RANGE = 8,     // a decode launch has fewer page splits than a sequence has visible pages
 };
 
 struct PageTable {

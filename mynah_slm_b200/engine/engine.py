@@ -141,7 +141,7 @@ class Engine:
         # a part that plans on the host (reads ctx.host_*) cannot be replayed from a graph
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.model.parts())
         self._staging = _Staging()
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self.launches = 0                          # kernels of this package launched (see count_launches)
         self.vocab_size = spec.vocab_size
 
@@ -196,15 +196,12 @@ class Engine:
                 raise EngineError(f"slot {e.slot} would grow to {self.cache.pages.length[e.slot] + n} positions, "
                                   f"the model allows {self.spec.max_positions}")
 
-    def _choose_splits(self, B: int, max_kv: int) -> int:
-        """Splits of the decode attention: enough CTAs for about two waves,
-        never more than the pages of the longest sequence."""
-        kv_heads = max((g.kv_heads for g in self.cache.plan.groups), default=1) or 1
-        want = -(-2 * self.runtime.sm_count // max(1, B * kv_heads))
-        pages = max(1, -(-max_kv // PAGE_TOKENS))
-        return int(max(1, min(want, pages, 64)))
+    @staticmethod
+    def _decode_pages(max_kv: int) -> int:
+        """Page splits of a decode launch: one per page the longest sequence can see."""
+        return max(1, -(-max_kv // PAGE_TOKENS))
 
-    def _fill(self, buf_np: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], pad_to: int = 0):
+    def _fill(self, buf_np: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], with_want: bool = True):
         """Write the batch description into a host buffer. Returns
         (max_q_len, want_count)."""
         pages = self.cache.pages
@@ -221,7 +218,7 @@ class Engine:
             tokens[row:row + n] = e.tokens
             tok_seq[row:row + n] = b
             tok_pos[row:row + n] = np.arange(past, past + n, dtype=np.int32)
-            for w in e.want:
+            for w in (e.want if with_want else ()):
                 want[wi] = row + int(w)
                 wi += 1
             row += n
@@ -306,7 +303,7 @@ class Engine:
         dev.copy_(host[:layout.size], non_blocking=True)
         self._staging.sent(hi)
         max_kv = max(self.cache.pages.length[e.slot] + len(e.tokens) for e in entries)
-        splits = self._choose_splits(B, max_kv) if is_decode else 1
+        splits = self._decode_pages(max_kv) if is_decode else 1
         ctx = device_context(layout, dev, [self.n_pages] * self.n_groups, max_q, is_decode, splits,
                              self.runtime.status, self.dtype)
         self._host_fields(ctx, entries)
@@ -340,27 +337,28 @@ class Engine:
         return b
 
     def _graph_for(self, B: int, max_kv: int) -> _DecodeGraph:
+        """The captured step for this batch size and context: batch sizes and
+        page counts are rounded up to powers of two, so a few graphs serve all."""
         bucket = self._bucket(B)
-        g = self._graphs.get(bucket)
+        max_pages_seq = -(-self.spec.max_positions // PAGE_TOKENS)
+        splits = min(max(4, self._bucket(self._decode_pages(max_kv))), max_pages_seq)
+        g = self._graphs.get((bucket, splits))
         if g is not None:
             return g
-        max_pages_seq = -(-self.spec.max_positions // PAGE_TOKENS)
         cap = min(bucket * max_pages_seq, self.n_pages + bucket)
         layout = StepLayout(T=bucket, B=bucket, W=1, ids_cap=[cap] * self.n_groups)
         meta = torch.zeros((layout.size,), dtype=torch.int32, device=self.device)
-        # the split count is part of the captured launch: sized for a context of a few thousand
-        splits = self._choose_splits(bucket, max(max_kv, 4096))
         ctx = device_context(layout, meta, [self.n_pages] * self.n_groups, 1, True, splits, self.runtime.status, self.dtype)
         g = _DecodeGraph(bucket, layout, meta, ctx, splits)
-        self._graphs[bucket] = g
+        self._graphs[(bucket, splits)] = g
         return g
 
-    def _decode_graph_step(self, entries: Sequence[StepEntry], mode: str, replays: int = 1) -> torch.Tensor:
+    def _decode_graph_step(self, entries: Sequence[StepEntry], mode: str, replays: int = 1, grow: int = 1) -> torch.Tensor:
         B = len(entries)
-        max_kv = max(self.cache.pages.length[e.slot] + 1 for e in entries)
+        max_kv = max(self.cache.pages.length[e.slot] + grow for e in entries)
         g = self._graph_for(B, max_kv)
         host, hi = self._staging.get(g.layout.size)
-        self._fill(host.numpy(), g.layout, entries)
+        self._fill(host.numpy(), g.layout, entries, with_want=False)
         g.meta.copy_(host[:g.layout.size], non_blocking=True)
         self._staging.sent(hi)
         self._host_fields(g.ctx, entries)
@@ -432,7 +430,7 @@ class Engine:
             if pages.length[e.slot] + n_steps > self.spec.max_positions:
                 raise EngineError(f"slot {e.slot} would outgrow the model's {self.spec.max_positions} positions")
             pages.reserve(e.slot, n_steps)
-        out = self._decode_graph_step(entries, "loop", replays=n_steps)
+        out = self._decode_graph_step(entries, "loop", replays=n_steps, grow=n_steps)
         for e in entries:
             pages.commit(e.slot, n_steps)
         return out
@@ -444,5 +442,6 @@ class Engine:
             self.runtime.status.zero_()
             what = [name for bit, name in ((kernels.ST_PAGE_RANGE, "a position without a page"),
                                            (kernels.ST_POS_RANGE, "a position outside the rotation table"),
-                                           (kernels.ST_TOKEN_RANGE, "a token id outside the vocabulary")) if st & bit]
+                                           (kernels.ST_TOKEN_RANGE, "a token id outside the vocabulary"),
+                                           (kernels.ST_SPLIT_RANGE, "a decode launch too small for a sequence")) if st & bit]
             raise EngineError("a kernel refused an index: " + ", ".join(what))

@@ -19,7 +19,7 @@ from .lib import KernelError, call, code, ptr, stream_ptr
 PAGE_TOKENS = 64
 MAX_HEAD_DIM = 256
 
-ST_PAGE_RANGE, ST_POS_RANGE, ST_TOKEN_RANGE = 1, 2, 4
+ST_PAGE_RANGE, ST_POS_RANGE, ST_TOKEN_RANGE, ST_SPLIT_RANGE = 1, 2, 4, 8
 
 
 def _chk(t: torch.Tensor, name: str, dtype=None, dim=None) -> None:

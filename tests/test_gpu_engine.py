@@ -1,0 +1,329 @@
+"""The engine against the plain implementation: whole prompts, the last tokens
+one by one, unequal batches one after another, long decoding, the first
+tokens; in 32-bit and in bfloat16, on three tiny configurations that differ in
+every size and option."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import BF16_REL, FP32_REL, TINY, assert_close, make_folder, prompts_for
+from plain.model import PlainQwen3
+from plain.sampler import PlainSampler, plain_generate
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CASES = [("A", "float32", torch.float32), ("A", "bfloat16", torch.bfloat16),
+         ("B", "float32", torch.bfloat16), ("B", "bfloat16", torch.bfloat16),      # bf16 file widened exactly
+         ("C", "float32", torch.float32), ("C", "bfloat16", torch.bfloat16)]
+IDS = [f"{n}-{d}" for n, d, _ in CASES]
+
+
+def tol(dtype: str) -> float:
+    return FP32_REL if dtype == "float32" else BF16_REL
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, _, wdt in CASES:
+        if (name, wdt) not in out:
+            out[(name, wdt)] = make_folder(root, name, wdt)
+    return out
+
+
+@pytest.fixture(scope="module")
+def plain_models(folders):
+    return {key: PlainQwen3.from_folder(path) for key, path in folders.items()}
+
+
+def _engine(folder, dtype, max_tokens, **kw):
+    from mynah_slm_b200.engine.engine import Engine
+    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, **kw)
+
+
+def _entry(slot, tokens, want):
+    from mynah_slm_b200.engine.engine import StepEntry
+    return StepEntry(slot, tokens, want)
+
+
+@pytest.mark.parametrize("name,dtype,wdt", CASES, ids=IDS)
+def test_whole_prompts_alone(folders, plain_models, name, dtype, wdt):
+    eng = _engine(folders[(name, wdt)], dtype, 256)
+    plain = plain_models[(name, wdt)]
+    for toks in prompts_for(name, [1, 2, 17, 64, 65, 150]):
+        slot = eng.open_sequence()
+        got = eng.step([_entry(slot, toks, range(len(toks)))]).cpu().numpy()
+        eng.check_status()
+        eng.close_sequence(slot)
+        assert_close(plain.forward(toks), got, tol(dtype), f"{name} {dtype} whole prompt of {len(toks)}")
+
+
+@pytest.mark.parametrize("name,dtype,wdt", CASES, ids=IDS)
+def test_last_32_tokens_one_by_one(folders, plain_models, name, dtype, wdt):
+    eng = _engine(folders[(name, wdt)], dtype, 192)
+    plain = plain_models[(name, wdt)]
+    for n in (33, 100, 130):
+        toks = prompts_for(name, [n], seed=n)[0]
+        ref = plain.forward(toks)
+        slot = eng.open_sequence()
+        head = n - 32
+        rows = [eng.step([_entry(slot, toks[:head], range(head))]).cpu().numpy()]
+        for t in range(head, n):
+            rows.append(eng.step([_entry(slot, toks[t:t + 1], (0,))]).cpu().numpy())
+        eng.check_status()
+        eng.close_sequence(slot)
+        assert_close(ref, np.concatenate(rows), tol(dtype), f"{name} {dtype} {n} tokens, last 32 one by one")
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graphs", "eager"])
+@pytest.mark.parametrize("name,dtype,wdt", CASES, ids=IDS)
+def test_unequal_batches_one_after_another(folders, plain_models, name, dtype, wdt, graphs):
+    """Batches of unequal prompts; every request decodes a different number of
+    tokens, so the shorter ones end earlier; the next batch starts in the slots
+    and pages the first gave back. The cache is exactly as large as the
+    largest batch needs."""
+    plain = plain_models[(name, wdt)]
+    rng = np.random.default_rng(5)
+    V = TINY[name]["vocab_size"]
+    batches = [[(7, 8), (1, 3), (12, 20)], [(1, 16), (5, 2), (33, 9), (64, 5)], [(70, 1), (3, 40)]]
+    need = max(sum(-(-(p + d) // 64) * 64 for p, d in b) for b in batches)
+    eng = _engine(folders[(name, wdt)], dtype, need, use_graphs=graphs)
+    seen_slots = []
+    for bi, batch in enumerate(batches):
+        seqs = [rng.integers(0, V, size=p + d).tolist() for p, d in batch]
+        slots = [eng.open_sequence() for _ in batch]
+        seen_slots.append(set(slots))
+        got = [[] for _ in batch]
+        out = eng.step([_entry(s, q[:p], range(p)) for s, q, (p, d) in zip(slots, seqs, batch)]).cpu().numpy()
+        row = 0
+        for i, (p, d) in enumerate(batch):
+            got[i].append(out[row:row + p]); row += p
+        live = list(range(len(batch)))
+        t = 0
+        while live:
+            live = [i for i in live if t < batch[i][1]]
+            if not live:
+                break
+            out = eng.step([_entry(slots[i], [seqs[i][batch[i][0] + t]], (0,)) for i in live]).cpu().numpy()
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1])
+            t += 1
+            for i in list(live):
+                if t >= batch[i][1]:
+                    eng.close_sequence(slots[i])                    # ends earlier than the others
+        eng.check_status()
+        for i, q in enumerate(seqs):
+            assert_close(plain.forward(q), np.concatenate(got[i]), tol(dtype),
+                         f"{name} {dtype} batch {bi} request {i} (prompt {batch[i][0]}, decoded {batch[i][1]})")
+    assert seen_slots[1] & seen_slots[0], "the second batch did not reuse a slot"
+    assert eng.free_tokens() == eng.n_pages * 64, "pages were lost"
+
+
+@pytest.mark.parametrize("name,dtype,wdt", [c for c in CASES if c[0] in ("A", "C")], ids=[i for i in IDS if i[0] in "AC"])
+def test_long_decoding(folders, plain_models, name, dtype, wdt):
+    """A short prompt and then hundreds of single steps: across page ends and,
+    on C, far past the window of 40."""
+    plain = plain_models[(name, wdt)]
+    n = 240 if name == "A" else 330
+    toks = prompts_for(name, [n], seed=77)[0]
+    eng = _engine(folders[(name, wdt)], dtype, -(-n // 64) * 64)
+    slot = eng.open_sequence()
+    rows = [eng.step([_entry(slot, toks[:3], (0, 1, 2))]).cpu().numpy()]
+    for t in range(3, n):
+        rows.append(eng.step([_entry(slot, toks[t:t + 1], (0,))]).cpu().numpy())
+    eng.check_status()
+    assert_close(plain.forward(toks), np.concatenate(rows), tol(dtype), f"{name} {dtype} long decoding")
+    if name == "C":
+        # the windowed group has given back what left the window; the full group has not
+        assert len(eng.cache.pages.held(slot, 0)[0]) == -(-n // 64)
+        assert len(eng.cache.pages.held(slot, 1)[0]) <= 2
+
+
+@pytest.mark.parametrize("name,dtype,wdt", CASES, ids=IDS)
+def test_first_tokens_and_chunked_prompt(folders, plain_models, name, dtype, wdt):
+    plain = plain_models[(name, wdt)]
+    eng = _engine(folders[(name, wdt)], dtype, 256)
+    toks = prompts_for(name, [90], seed=3)[0]
+    ref = plain.forward(toks)
+    # one token at a time from the very first
+    slot = eng.open_sequence()
+    rows = [eng.step([_entry(slot, toks[t:t + 1], (0,))]).cpu().numpy() for t in range(5)]
+    assert_close(ref[:5], np.concatenate(rows), tol(dtype), f"{name} {dtype} first tokens")
+    eng.close_sequence(slot)
+    # a prompt cut into pieces of unequal size, beside a whole one in the same steps
+    a, b = eng.open_sequence(), eng.open_sequence()
+    cuts = [(0, 1), (1, 40), (40, 64), (64, 90)]
+    got_a = []
+    for i, (lo, hi) in enumerate(cuts):
+        entries = [_entry(a, toks[lo:hi], range(hi - lo))]
+        if i == 1:
+            entries.append(_entry(b, toks, (len(toks) - 1,)))
+        out = eng.step(entries).cpu().numpy()
+        got_a.append(out[:hi - lo])
+        if i == 1:
+            assert_close(ref[-1:], out[hi - lo:], tol(dtype), f"{name} {dtype} whole prompt beside a piece")
+    eng.check_status()
+    assert_close(ref, np.concatenate(got_a), tol(dtype), f"{name} {dtype} prompt in pieces")
+    # nothing wanted: the step still fills the cache
+    eng.close_sequence(a)
+    eng.close_sequence(b)
+    c = eng.open_sequence()
+    assert eng.step([_entry(c, toks[:50], ())]).shape == (0, TINY[name]["vocab_size"])
+    out = eng.step([_entry(c, toks[50:51], (0,))]).cpu().numpy()
+    assert_close(ref[50:51], out, tol(dtype), f"{name} {dtype} after a step that wanted nothing")
+
+
+@pytest.mark.parametrize("name,dtype,wdt", [CASES[0], CASES[3], CASES[4]], ids=[IDS[0], IDS[3], IDS[4]])
+def test_trace_run_program(folders, plain_models, tmp_path, name, dtype, wdt):
+    """bin/trace_run as a user runs it: a process, JSON lines in, .f32 files out."""
+    plain = plain_models[(name, wdt)]
+    V = TINY[name]["vocab_size"]
+    a, b = prompts_for(name, [70, 9], seed=21)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [0, 59]}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[60:61], "want": [0]}, {"id": "b", "tokens": b[8:9], "want": []}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[61:62], "want": [0]}], "end": []},
+        {"step": 3, "entries": [{"id": "c", "tokens": b, "want": [8]}], "end": ["a", "c"]},
+    ]
+    out = tmp_path / "out"
+    env = dict(os.environ, HOME=str(tmp_path / "home"))
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[(name, wdt)], "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", "192"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    ra, rb = plain.forward(a), plain.forward(b)
+    load = lambda i: np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, V)
+    assert_close(np.stack([ra[0], ra[59], rb[7]]), load(0), tol(dtype), "trace step 0")
+    assert_close(ra[60:61], load(1), tol(dtype), "trace step 1")
+    assert_close(ra[61:62], load(2), tol(dtype), "trace step 2")
+    assert_close(rb[8:9], load(3), tol(dtype), "trace step 3")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padding_and_company_change_nothing(folders, dtype):
+    """A decode step's logits for one sequence have the same bits whether its
+    rows are padding or other sequences and whichever row it takes. In 32-bit
+    this holds across batch sizes too (every sum has a fixed order); in
+    bfloat16 the library's matrix product may pick another kernel for another
+    batch size, so across sizes the comparison is to rounding."""
+    eng = _engine(folders[("B", torch.bfloat16)], dtype, 1024)
+    p = prompts_for("B", [20, 31, 5, 9, 14], seed=8)
+
+    def run(which):
+        slots = {i: eng.open_sequence() for i in which}
+        eng.step([_entry(slots[i], p[i], ()) for i in which])
+        out = eng.step([_entry(slots[i], [p[i][0]], (0,)) for i in which]).cpu().numpy()
+        for s in slots.values():
+            eng.close_sequence(s)
+        return {i: out[r] for r, i in enumerate(which)}
+    three = run([0, 1, 2])                    # a bucket of 4 with one padding row
+    four = run([3, 2, 1, 0])                  # the same bucket, full, other rows
+    assert np.array_equal(three[1], four[1]) and np.array_equal(three[2], four[2]) and np.array_equal(three[0], four[0])
+    alone, five = run([1]), run([4, 3, 2, 1, 0])
+    if dtype == "float32":
+        assert np.array_equal(alone[1], three[1]) and np.array_equal(alone[1], five[1])
+    else:
+        assert_close(alone[1][None], three[1][None], 1e-2, "alone against a batch of three")
+        assert_close(alone[1][None], five[1][None], 1e-2, "alone against a batch of five")
+
+
+def test_step_refuses_bad_input(folders):
+    from mynah_slm_b200.cache.pages import CacheError
+    from mynah_slm_b200.engine.engine import EngineError
+    eng = _engine(folders[("A", torch.float32)], "float32", 128)
+    s = eng.open_sequence()
+    with pytest.raises(EngineError, match="outside the vocabulary"):
+        eng.step([_entry(s, [512], (0,))])
+    with pytest.raises(EngineError, match="wanted place"):
+        eng.step([_entry(s, [1, 2], (2,))])
+    with pytest.raises(EngineError, match="not open"):
+        eng.step([_entry(99, [1], (0,))])
+    with pytest.raises(EngineError, match="twice"):
+        eng.step([_entry(s, [1], ()), _entry(s, [2], ())])
+    with pytest.raises(EngineError, match="the model allows 256"):
+        eng.step([_entry(s, [1] * 257, ())])
+    with pytest.raises(CacheError, match="full"):
+        eng.step([_entry(s, [1] * 129, ())])
+    assert eng.length(s) == 0                                    # nothing was taken by the refused steps
+    eng.step([_entry(s, [1] * 128, ())])
+
+
+@pytest.mark.parametrize("name,dtype,wdt", [CASES[0], CASES[2], CASES[5]], ids=[IDS[0], IDS[2], IDS[5]])
+def test_greedy_generation_through_the_entry_point(folders, plain_models, name, dtype, wdt):
+    from mynah_slm_b200 import LLM
+    plain = plain_models[(name, wdt)]
+    llm = LLM(folders[(name, wdt)], dtype=dtype, max_tokens=64 * 8)
+    prompts = prompts_for(name, [7, 1, 12, 30, 3], seed=31)
+    n_new = [8, 5, 12, 3, 9]
+    res = []
+    for batch in (2, 8):                                         # two batches after one another, and one
+        # each distinct limit is its own call
+        outs = {}
+        for m in sorted(set(n_new)):
+            idx = [i for i, k in enumerate(n_new) if k == m]
+            r = llm.generate([prompts[i] for i in idx], max_new=m, temp=0.0, ignore_eos=True, max_batch=batch)
+            for i, x in zip(idx, r):
+                outs[i] = x
+        res.append([outs[i].tokens for i in range(len(prompts))])
+    assert res[0] == res[1]
+    if dtype == "float32":
+        for i, p in enumerate(prompts):
+            want, _ = plain_generate(plain, p, n_new[i], PlainSampler(temp=0))
+            assert res[0][i] == want, f"request {i}"
+    # the model's own stop set ends a sequence before the stop token is emitted
+    p0 = prompts[2]
+    free = llm.generate([p0], max_new=12, temp=0.0, ignore_eos=True)[0].tokens
+    stop_at = next((j for j in range(1, len(free)) if free[j] not in free[:j]), 0)
+    r = llm.generate([p0], max_new=12, temp=0.0, stop_ids=[free[stop_at]])[0]
+    assert r.tokens == free[:stop_at] and r.produced == stop_at + 1 and r.finish_reason == "stop"
+    assert llm.last_timing.n_gen == stop_at + 1 and "decode" in llm.last_timing.format()
+
+
+def test_temperature_generation_matches_plain_in_32_bit(folders, plain_models):
+    """Temperature 0.8, seed 1, on B in 32-bit: token for token what the plain
+    sampler draws from the plain model, whatever the batch."""
+    from mynah_slm_b200 import LLM
+    from mynah_slm_b200.sampling.sampler import stream_state
+    key = ("B", torch.bfloat16)
+    llm = LLM(folders[key], dtype="float32", max_tokens=64 * 8)
+    prompts = prompts_for("B", [1, 5, 33, 64], seed=41)
+    kw = dict(max_new=16, temp=0.8, top_k=0, top_p=1.0, seed=1, ignore_eos=True)
+    together = [r.tokens for r in llm.generate(prompts, **kw)]
+    apart = [r.tokens for r in llm.generate(prompts, max_batch=1, **kw)]
+    assert together == apart                                       # a sequence's draws do not depend on its batch
+    for i, p in enumerate(prompts):
+        s = PlainSampler(temp=0.8, top_k=0, top_p=1.0, rng_state=stream_state(1, i))
+        want, _ = plain_generate(plain_models[key], p, 16, s)
+        assert together[i] == want, f"request {i}"
+    # the reference's defaults (top-k 20, top-p 0.95) and the penalties
+    kw = dict(max_new=10, temp=0.6, top_k=20, top_p=0.95, seed=7, repeat_penalty=1.2, ignore_eos=True)
+    got = llm.generate(prompts[:2], **kw)
+    for i, p in enumerate(prompts[:2]):
+        s = PlainSampler(temp=0.6, top_k=20, top_p=0.95, repeat_penalty=1.2, rng_state=stream_state(7, i))
+        want, _ = plain_generate(plain_models[key], p, 10, s)
+        assert got[i].tokens == want, f"request {i} with filters and penalty"
+
+
+def test_command_line(folders, tmp_path):
+    folder = folders[("A", torch.float32)]
+    cli = [sys.executable, os.path.join(ROOT, "bin", "mynah-slm")]
+    p = subprocess.run(cli + ["run", "-m", folder, "--tokens", "5,17,3", "--tokens", "9", "-n", "6", "--temp", "0",
+                              "--dtype", "float32", "--ignore-eos"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l.split() for l in p.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(l) == 6 for l in lines)
+    assert "prefill" in p.stderr and "decode" in p.stderr and "TTFT" in p.stderr
+    q = subprocess.run(cli + ["run", "-m", folder, "--tokens", "5,17,3", "-n", "6", "--temp", "0", "--dtype", "float32",
+                              "--ignore-eos", "--quiet"], capture_output=True, text=True, timeout=600)
+    assert q.returncode == 0 and q.stdout.split() == lines[0] and "prefill" not in q.stderr
+    bad = subprocess.run(cli + ["run", "-m", folder, "--bogus"], capture_output=True, text=True)
+    assert bad.returncode == 2 and "unknown option '--bogus'" in bad.stderr
+    assert subprocess.run(cli + ["--version"], capture_output=True, text=True).stdout.strip()

@@ -1,0 +1,416 @@
+"""Each kernel alone against its plain reference, at sizes other than the
+engine's tiny models (widths and vocabularies that are no power of two, head
+sizes in steps of 16, odd numbers of heads and groups)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_err
+from plain.model import gqa_attention, rms_norm, rope_apply, rope_table, swiglu as plain_swiglu
+from plain.sampler import PlainSampler
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"f32": torch.float32, "bf16": torch.bfloat16}
+
+
+def _k():
+    from mynah_slm_b200.ops import kernels
+    return kernels
+
+
+def _tol(dt):
+    return 2e-6 if dt == "f32" else 8e-3
+
+
+def _round(a: np.ndarray, dt: str) -> np.ndarray:
+    """What the values are after being stored in the run's type."""
+    if dt == "f32":
+        return a.astype(np.float32)
+    return torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def test_library_is_ours_and_loaded():
+    from mynah_slm_b200.ops import lib
+    handle = lib.load()
+    assert handle.mynah_device_arch() == 100
+    maps = open("/proc/self/maps").read()
+    assert "libmynah_slm_b200.so" in maps
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("V,D,T", [(777, 100, 13), (1000, 1024, 3)])
+def test_embed_gather(dt, V, D, T):
+    k = _k()
+    rng = np.random.default_rng(0)
+    table = torch.from_numpy(rng.standard_normal((V, D)).astype(np.float32)).to(DT[dt]).to(DEV)
+    toks = torch.from_numpy(rng.integers(0, V, size=T).astype(np.int32)).to(DEV)
+    x = k.embed_gather(table, toks)
+    assert x.dtype == torch.float32
+    assert torch.equal(x, table.float()[toks.long()])          # a lookup: exact, no scaling
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("T,D,eps", [(7, 100, 1e-5), (3, 1000, 1e-6), (5, 4096, 1e-6), (2, 24, 1e-3)])
+def test_rmsnorm_with_residual_and_rows(dt, T, D, eps):
+    k = _k()
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((T, D)) * 30).astype(np.float32)
+    delta = _round(rng.standard_normal((T, D)), dt)
+    gain = _round(1 + 0.1 * rng.standard_normal(D), dt)
+    xd = torch.from_numpy(x.copy()).to(DEV)
+    out = k.rmsnorm(xd, torch.from_numpy(gain).to(DT[dt]).to(DEV), eps, DT[dt],
+                    delta=torch.from_numpy(delta).to(DT[dt]).to(DEV))
+    assert np.array_equal(xd.cpu().numpy(), (x + delta).astype(np.float32))           # the add is exact fp32
+    ref = rms_norm(x + delta, gain, eps)
+    assert rel_err(ref, out.float().cpu().numpy()) < _tol(dt)
+    # a selection of rows, no add
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = k.rmsnorm(xd, torch.from_numpy(gain).to(DT[dt]).to(DEV), eps, DT[dt], rows=rows)
+    assert torch.equal(out2, out[[T - 1, 0]])
+    # a gain stored in 32-bit stays 32-bit in a bf16 run
+    g32 = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    out3 = k.rmsnorm(xd, torch.from_numpy(g32).to(DEV), eps, DT[dt])
+    assert rel_err(rms_norm(x + delta, g32, eps), out3.float().cpu().numpy()) < _tol(dt)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+def test_swiglu_and_residual_add(dt):
+    k = _k()
+    rng = np.random.default_rng(2)
+    T, F = 5, 333
+    gu = _round(rng.standard_normal((T, 2 * F)) * 4, dt)
+    gu[0, :4] = [-1e4, 1e4, -90.0, 90.0]                                             # the sigmoid must stay finite
+    out = k.swiglu(torch.from_numpy(gu).to(DT[dt]).to(DEV)).float().cpu().numpy()
+    assert np.isfinite(out).all()
+    assert rel_err(plain_swiglu(gu[:, :F], gu[:, F:]), out) < _tol(dt)
+    x = rng.standard_normal((T, F)).astype(np.float32)
+    d = _round(rng.standard_normal((T, F)), dt)
+    xd = torch.from_numpy(x.copy()).to(DEV)
+    k.residual_add(xd, torch.from_numpy(d).to(DT[dt]).to(DEV))
+    assert np.array_equal(xd.cpu().numpy(), x + d)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 100), (65, 64, 17), (130, 777, 96), (2, 1000, 1024)])
+def test_gemm_f32_is_true_fp32_and_cut_invariant(M, N, K):
+    k = _k()
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    ad, wd = torch.from_numpy(a).to(DEV), torch.from_numpy(w).to(DEV)
+    c = k.linear(ad, wd).cpu().numpy()
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    assert rel_err(ref, c) < 1e-6 * max(1.0, np.sqrt(K) / 8)        # fp32 accumulation, not tf32 (which gives ~1e-3)
+    # a row's result does not depend on the rows computed with it
+    one = k.linear(ad[M - 1:M].contiguous(), wd).cpu().numpy()
+    assert np.array_equal(one[0], c[M - 1])
+
+
+def _paged(kv: np.ndarray, page_ids, n_pages, dt, poison=None):
+    """Scatter [T, KV, HD] into pages [n_pages, KV, 64, HD]."""
+    T, KV, HD = kv.shape
+    pages = np.full((n_pages, KV, 64, HD), 0.0 if poison is None else poison, dtype=np.float32)
+    for t in range(T):
+        pages[page_ids[t // 64], :, t % 64, :] = kv[t]
+    return torch.from_numpy(pages).to(DT[dt]).to(DEV)
+
+
+def _page_table(lists, bases=None):
+    from mynah_slm_b200.ops.kernels import PageTableView
+    indptr = np.cumsum([0] + [len(l) for l in lists]).astype(np.int32)
+    ids = np.array([p for l in lists for p in l] or [0], dtype=np.int32)
+    base = np.array(bases if bases is not None else [0] * len(lists), dtype=np.int32)
+    return lambda n_pages: PageTableView(torch.from_numpy(indptr).to(DEV), torch.from_numpy(ids).to(DEV),
+                                         torch.from_numpy(base).to(DEV), n_pages)
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("H,KV,HD,rot", [(4, 2, 16, 16), (6, 3, 48, 48), (5, 5, 128, 128), (8, 2, 64, 32), (3, 1, 256, 256)])
+def test_qk_norm_rope_store(dt, H, KV, HD, rot):
+    k = _k()
+    rng = np.random.default_rng(4)
+    lens, past = [5, 1, 70], [0, 130, 60]                                        # three sequences; positions continue
+    T = sum(lens)
+    W = (H + 2 * KV) * HD
+    qkv = _round(rng.standard_normal((T, W)) * 2, dt)
+    qg, kg = _round(1 + 0.1 * rng.standard_normal(HD), dt), _round(1 + 0.1 * rng.standard_normal(HD), dt)
+    eps, theta = 1e-5, 12345.0
+    tok_seq = np.concatenate([[b] * n for b, n in enumerate(lens)]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(past, lens)]).astype(np.int32)
+    n_pages = 9
+    lists = [[7], [0, 3, 5], [2, 8, 4]]                                          # scattered pages
+    pt = _page_table(lists)(n_pages)
+    kc = torch.full((n_pages, KV, 64, HD), 99.0, dtype=DT[dt], device=DEV)
+    vc = torch.full((n_pages, KV, 64, HD), 99.0, dtype=DT[dt], device=DEV)
+    cos, sin = k.rope_table(256, rot, theta, DEV)
+    cr, sr = rope_table(rot, np.arange(256), theta)
+    assert np.array_equal(cos.cpu().numpy(), cr) and np.array_equal(sin.cpu().numpy(), sr)   # built in double, as the reference
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    qd = torch.from_numpy(qkv).to(DT[dt]).to(DEV)
+    k.qk_norm_rope_store(qd, H, KV, HD, torch.from_numpy(qg).to(DT[dt]).to(DEV), torch.from_numpy(kg).to(DT[dt]).to(DEV),
+                         eps, cos, sin, rot, torch.from_numpy(tok_seq).to(DEV), torch.from_numpy(tok_pos).to(DEV), pt, kc, vc, status)
+    assert status.item() == 0
+    q = qkv[:, :H * HD].reshape(T, H, HD)
+    kk = qkv[:, H * HD:(H + KV) * HD].reshape(T, KV, HD)
+    vv = qkv[:, (H + KV) * HD:].reshape(T, KV, HD)
+
+    def ref(x, g):
+        n = rms_norm(x, g, eps)
+        r = rope_apply(n[..., :rot], cr[tok_pos], sr[tok_pos])
+        return np.concatenate([r, n[..., rot:]], axis=-1)
+    got_q = qd.float().cpu().numpy()[:, :H * HD].reshape(T, H, HD)
+    assert rel_err(ref(q, qg).reshape(T, -1), got_q.reshape(T, -1)) < _tol(dt)
+    kc_np, vc_np = kc.float().cpu().numpy(), vc.float().cpu().numpy()
+    rk = ref(kk, kg)
+    written = np.zeros((n_pages, 64), dtype=bool)
+    for t in range(T):
+        pg, off = lists[tok_seq[t]][tok_pos[t] // 64], tok_pos[t] % 64
+        written[pg, off] = True
+        assert rel_err(rk[t].reshape(1, -1), kc_np[pg, :, off].reshape(1, -1)) < _tol(dt)
+        assert np.array_equal(vc_np[pg, :, off], vv[t])                         # V is neither normed nor rotated
+    untouched = ~written
+    assert np.all(kc_np.transpose(0, 2, 1, 3)[untouched] == 99.0) and np.all(vc_np.transpose(0, 2, 1, 3)[untouched] == 99.0)
+    # a position with no page is refused, not written somewhere
+    bad_pos = torch.from_numpy(tok_pos + 64 * 3).to(DEV)
+    k.qk_norm_rope_store(qd, H, KV, HD, None, None, eps, None, None, 0, torch.from_numpy(tok_seq).to(DEV), bad_pos, pt, kc, vc, status)
+    assert status.item() & 1
+    status.zero_()
+
+
+def _attn_case(rng, lens_q, past, H, KV, HD, dt, scale_key=None):
+    """Random q for the new tokens and K/V for whole sequences; returns the plain outputs."""
+    seqs = []
+    for nq, p in zip(lens_q, past):
+        n = p + nq
+        q = _round(rng.standard_normal((nq, H, HD)), dt)
+        kk = _round(rng.standard_normal((n, KV, HD)), dt)
+        vv = _round(rng.standard_normal((n, KV, HD)), dt)
+        seqs.append((q, kk, vv))
+    return seqs
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("H,KV,HD,window", [(4, 2, 16, 0), (6, 2, 32, 0), (6, 3, 48, 40), (5, 1, 80, 0), (2, 2, 128, 70), (3, 3, 256, 0)])
+def test_attn_prefill_generic(dt, H, KV, HD, window):
+    k = _k()
+    rng = np.random.default_rng(5)
+    lens_q, past = [7, 1, 33, 70], [0, 0, 100, 64]
+    seqs = _attn_case(rng, lens_q, past, H, KV, HD, dt)
+    n_pages, free = 16, list(np.random.default_rng(9).permutation(16))
+    lists, kcs = [], None
+    kc = torch.zeros((n_pages, KV, 64, HD), dtype=DT[dt], device=DEV)
+    vc = torch.zeros_like(kc)
+    for q, kk, vv in seqs:
+        need = -(-kk.shape[0] // 64)
+        pages = [int(free.pop()) for _ in range(need)]
+        lists.append(pages)
+        kc_s, vc_s = _paged(kk, pages, n_pages, dt, poison=1e4), _paged(vv, pages, n_pages, dt, poison=1e4)
+        for pg in pages:
+            kc[pg], vc[pg] = kc_s[pg], vc_s[pg]                                   # the tail of a page holds poison
+    pt = _page_table(lists)(n_pages)
+    T = sum(lens_q)
+    qkv = torch.from_numpy(np.concatenate([s[0].reshape(s[0].shape[0], -1) for s in seqs])).to(DT[dt]).to(DEV)
+    out = torch.zeros((T, H * HD), dtype=DT[dt], device=DEV)
+    cu = torch.tensor(np.cumsum([0] + lens_q), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor([p + n for p, n in zip(past, lens_q)], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.attn_prefill_generic(qkv, out, len(seqs), max(lens_q), H, KV, HD, kc, vc, cu, kvl, pt, window, status)
+    assert status.item() == 0
+    got = out.float().cpu().numpy()
+    row = 0
+    for (q, kk, vv), nq, p in zip(seqs, lens_q, past):
+        ref = gqa_attention(q, kk, vv, window=window or None, q_pos=np.arange(p, p + nq), k_pos=np.arange(p + nq))
+        assert rel_err(ref.reshape(nq, -1), got[row:row + nq]) < (3e-6 if dt == "f32" else 1e-2), (nq, p)
+        row += nq
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("H,KV,HD,window,splits", [(4, 2, 16, 0, 9), (6, 2, 32, 0, 16), (6, 3, 48, 40, 2), (5, 1, 80, 0, 9),
+                                                   (16, 8, 128, 0, 12), (8, 1, 64, 100, 3), (3, 3, 256, 0, 9)])
+def test_attn_decode(dt, H, KV, HD, window, splits):
+    k = _k()
+    rng = np.random.default_rng(6)
+    lens = [1, 64, 65, 300, 0, 517]                                               # a padding sequence among them
+    B = len(lens)
+    n_pages = 24
+    free = list(np.random.default_rng(10).permutation(n_pages))
+    kc = torch.zeros((n_pages, KV, 64, HD), dtype=DT[dt], device=DEV)
+    vc = torch.zeros_like(kc)
+    lists, seqs = [], []
+    for n in lens:
+        kk, vv = _round(rng.standard_normal((n, KV, HD)), dt), _round(rng.standard_normal((n, KV, HD)), dt)
+        pages = [int(free.pop()) for _ in range(-(-n // 64))]
+        lists.append(pages)
+        seqs.append((kk, vv))
+        if n:
+            kc_s, vc_s = _paged(kk, pages, n_pages, dt, poison=1e4), _paged(vv, pages, n_pages, dt, poison=1e4)
+            for pg in pages:
+                kc[pg], vc[pg] = kc_s[pg], vc_s[pg]
+    q = _round(rng.standard_normal((B, H, HD)), dt)
+    qd = torch.from_numpy(q.reshape(B, -1)).to(DT[dt]).to(DEV)
+    out = torch.full((B, H * HD), 7.0, dtype=DT[dt], device=DEV)
+    kvl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(k.attn_decode_scratch_floats(B, H, HD, splits), dtype=torch.float32, device=DEV)
+    k.attn_decode(qd, out, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, splits, scratch, status)
+    assert status.item() == 0
+    got = out.float().cpu().numpy()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert np.all(got[b] == 0)
+            continue
+        kk, vv = seqs[b]
+        ref = gqa_attention(q[b:b + 1], kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
+        assert rel_err(ref.reshape(1, -1), got[b:b + 1]) < (3e-6 if dt == "f32" else 1e-2), (b, n)
+    # a larger launch gives the same bits; one that is too small says so instead of dropping keys
+    out2 = torch.zeros_like(out)
+    scratch2 = torch.empty(k.attn_decode_scratch_floats(B, H, HD, splits + 5), dtype=torch.float32, device=DEV)
+    k.attn_decode(qd, out2, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, splits + 5, scratch2, status)
+    assert torch.equal(out, out2) and status.item() == 0
+    k.attn_decode(qd, out2, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, 1, scratch2, status)
+    assert status.item() == 8
+    status.zero_()
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("kind", ["prefill", "decode"])
+def test_one_far_key_and_the_window_edge(dt, kind):
+    """Random values hide a missed key among hundreds. Here one key's score
+    stands out, so the output is that key's value or is not: at a far
+    position, at the first position of a page, and on both sides of the
+    window's edge. Two sequences with interleaved pages share the launch."""
+    k = _k()
+    H, KV, HD, n = 2, 1, 64, 400
+    rng = np.random.default_rng(7)
+    for window, target, visible in [(0, 3, True), (0, 64, True), (0, 399, True), (120, 280, True), (120, 279, False)]:
+        # query at position n-1 sees keys > n-1-window
+        kk = _round(rng.standard_normal((n, KV, HD)) * 0.1, dt)
+        vv = _round(rng.standard_normal((n, KV, HD)), dt)
+        q = _round(rng.standard_normal((1, H, HD)) * 0.1, dt)
+        kk[target, 0] = q[0, 0] / np.linalg.norm(q[0, 0]) * 60.0            # score far above the others for head 0
+        q[0, 0] *= 20
+        other_k = _round(rng.standard_normal((n, KV, HD)) * 0.1, dt)
+        other_v = _round(rng.standard_normal((n, KV, HD)), dt)
+        lists = [[0, 2, 4, 6, 8, 10, 12], [1, 3, 5, 7, 9, 11, 13]]
+        n_pages = 14
+        kc = _paged(kk, lists[0], n_pages, dt) + _paged(other_k, lists[1], n_pages, dt)
+        vc = _paged(vv, lists[0], n_pages, dt) + _paged(other_v, lists[1], n_pages, dt)
+        pt = _page_table(lists)(n_pages)
+        qd = torch.from_numpy(np.concatenate([q, q]).reshape(2, -1)).to(DT[dt]).to(DEV)
+        out = torch.zeros((2, H * HD), dtype=DT[dt], device=DEV)
+        kvl = torch.tensor([n, n], dtype=torch.int32, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        if kind == "decode":
+            scratch = torch.empty(k.attn_decode_scratch_floats(2, H, HD, 7), dtype=torch.float32, device=DEV)
+            k.attn_decode(qd, out, 2, H, KV, HD, kc, vc, kvl, pt, window, 7, scratch, status)
+        else:
+            cu = torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV)
+            k.attn_prefill_generic(qd, out, 2, 1, H, KV, HD, kc, vc, cu, kvl, pt, window, status)
+        got = out.float().cpu().numpy()[0, :HD]
+        hit = np.abs(got - vv[target, 0]).max() < 0.05
+        assert hit == visible, (window, target, visible)
+        ref = gqa_attention(q, kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
+        assert rel_err(ref.reshape(1, -1), out.float().cpu().numpy()[0:1]) < (1e-5 if dt == "f32" else 2e-2)
+
+
+@pytest.mark.parametrize("V", [777, 151936, 1000])
+def test_argmax_first_maximum(V):
+    k = _k()
+    rng = np.random.default_rng(8)
+    lg = rng.standard_normal((5, V)).astype(np.float32)
+    lg[1, [V - 1, 17, 300]] = 9.0                                                  # ties: the lowest id wins
+    lg[2, :] = 0.0
+    got = k.argmax(torch.from_numpy(lg).to(DEV)).cpu().numpy()
+    assert got.tolist() == [int(np.argmax(r)) for r in lg]
+    assert got[1] == 17 and got[2] == 0
+
+
+def _sampler_state(B, seeds):
+    st = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in seeds], dtype=torch.int64, device=DEV)
+    return st
+
+
+@pytest.mark.parametrize("V", [777, 32000])
+@pytest.mark.parametrize("temp,top_k,top_p,min_p", [(0.8, 0, 1.0, 0.0), (0.6, 20, 0.95, 0.0), (1.0, 5, 1.0, 0.0),
+                                                    (1.3, 0, 0.7, 0.0), (1.0, 0, 1.0, 0.05), (0.7, 50, 0.9, 0.02),
+                                                    (1.0, 1, 1.0, 0.0), (0.0, 20, 0.95, 0.0), (2.0, 0, 0.999, 0.0)])
+def test_sample_matches_plain_sampler(V, temp, top_k, top_p, min_p):
+    """Same logits, same generator state -> same token, draw after draw."""
+    k = _k()
+    rng = np.random.default_rng(11)
+    B, rounds = 6, 12
+    seeds = [int(rng.integers(1, 2 ** 62)) for _ in range(B)]
+    plain = [PlainSampler(temp=temp, top_k=top_k, top_p=top_p, min_p=min_p, rng_state=s) for s in seeds]
+    state = _sampler_state(B, seeds)
+    params = torch.tensor([temp, top_p, min_p, float(top_k), 1.0, 0.0, 0.0, 0.0], dtype=torch.float32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    for r in range(rounds):
+        lg = (rng.standard_normal((B, V)) * (1.0 + r % 3)).astype(np.float32)
+        lg[0, :8] = lg[0, 0]                                                       # equal probabilities: ids break ties
+        want = [p.sample(lg[b].copy()) for b, p in enumerate(plain)]
+        got = k.sample(torch.from_numpy(lg.copy()).to(DEV), params, state, slots).cpu().tolist()
+        assert got == want, (r, got, want)
+    # the states advanced exactly as the plain generators did (greedy draws nothing)
+    want_state = [p.rng.state for p in plain]
+    got_state = [(int(s) + (1 << 64)) % (1 << 64) for s in state.cpu().tolist()]
+    assert got_state == want_state
+
+
+def test_sample_padding_rows_and_slot_mapping():
+    k = _k()
+    rng = np.random.default_rng(12)
+    V = 500
+    lg = rng.standard_normal((3, V)).astype(np.float32)
+    state = _sampler_state(4, [11, 22, 33, 44])
+    params = torch.tensor([1.0, 1.0, 0.0, 0.0, 1.0, 0.0, 0.0, 0.0], dtype=torch.float32, device=DEV)
+    slots = torch.tensor([3, -1, 1], dtype=torch.int32, device=DEV)
+    got = k.sample(torch.from_numpy(lg.copy()).to(DEV), params, state, slots).cpu().tolist()
+    assert got[0] == PlainSampler(temp=1.0, top_k=0, top_p=1.0, rng_state=44).sample(lg[0].copy())
+    assert got[2] == PlainSampler(temp=1.0, top_k=0, top_p=1.0, rng_state=22).sample(lg[2].copy())
+    st = state.cpu().tolist()
+    assert st[0] == 11 and st[2] == 33                                              # untouched slots keep their state
+
+
+def test_penalties_and_ring_match_plain():
+    k = _k()
+    rng = np.random.default_rng(13)
+    V, W, stride, B = 300, 5, 8, 3
+    plain = [PlainSampler(temp=0, repeat_penalty=1.3, freq_penalty=0.2, presence_penalty=0.1, penalty_window=W) for _ in range(B)]
+    ring = torch.zeros((B, stride), dtype=torch.int32, device=DEV)
+    ring_n = torch.zeros(B, dtype=torch.int32, device=DEV)
+    ring_head = torch.zeros(B, dtype=torch.int32, device=DEV)
+    params = torch.tensor([0.0, 1.0, 0.0, 0.0, 1.3, 0.2, 0.1, float(W)], dtype=torch.float32, device=DEV)
+    slots = torch.arange(B, dtype=torch.int32, device=DEV)
+    for step in range(12):
+        toks = rng.integers(0, 6, size=B).astype(np.int32)                           # few ids: repeats inside the window
+        for b in range(B):
+            plain[b].accept(int(toks[b]))
+        k.sampler_accept(torch.from_numpy(toks).to(DEV), ring, ring_n, ring_head, slots, params)
+        lg = rng.standard_normal((B, V)).astype(np.float32)
+        ref = lg.copy()
+        for b in range(B):
+            plain[b].apply_penalties(ref[b])
+        d = torch.from_numpy(lg.copy()).to(DEV)
+        k.apply_penalties(d, ring, ring_n, slots, params)
+        assert np.allclose(d.cpu().numpy(), ref, rtol=1e-6, atol=1e-6), step
+    assert ring_n.cpu().tolist() == [W] * B
+
+
+def test_refusals_are_errors_not_wrong_results():
+    from mynah_slm_b200.ops.lib import KernelError
+    k = _k()
+    q = torch.zeros((1, 4 * 264), dtype=torch.float32, device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pt = _page_table([[0]])(1)
+    kc = torch.zeros((1, 1, 64, 264), dtype=torch.float32, device=DEV)
+    with pytest.raises(KernelError, match="head_dim 264"):
+        k.attn_decode(q, q.clone(), 1, 4, 1, 264, kc, kc, torch.ones(1, dtype=torch.int32, device=DEV), pt, 0, 1,
+                      torch.zeros(10000, device=DEV), st)
+    with pytest.raises(KernelError, match="head_dim 264 exceeds"):
+        k.attn_prefill_generic(q, q.clone(), 1, 1, 4, 1, 264, kc, kc, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                               torch.ones(1, dtype=torch.int32, device=DEV), pt, 0, st)
+    with pytest.raises(KernelError, match="not contiguous"):
+        k.swiglu(torch.zeros((4, 8), device=DEV)[:, ::2])
+    with pytest.raises(KernelError, match="unsupported dtype"):
+        k.swiglu(torch.zeros((4, 8), device=DEV, dtype=torch.float16))
