@@ -1,0 +1,267 @@
+"""Benchmark of mynah_slm_b200 on one B200: decode tokens per second at the
+Qwen3-0.6B shape with random weights (batch 8 by default, 2,048-token prompts,
+4,096-token context), prefill of one 2,048-token prompt, and decode at batch 1
+and 64.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout. A step is one decode step of the batch.
+  value     decoded tokens per second, timed on the device with CUDA events
+            around exactly K steps that run from a captured graph with the
+            sampled token fed back on the device
+  e2e       the same through the Python entry point (LLM.generate): every
+            step copies its inputs from pinned host memory to the device and
+            reads the sampled tokens back to the host
+  prefill   one 2,048-token prompt in one step; frac = flops / time / peak
+  roofline  bytes a decode step has to read (every weight once, the cache of
+            the live requests) / its time, against the HBM peak
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from
+the stated fallback.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen3-0.6B layer sizes (the benchmark configuration; random weights, seed 2)
+QWEN3_0_6B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=28, hidden_size=1024,
+                  num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+                  vocab_size=151936, rope_theta=1000000, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                  max_position_embeddings=40960, hidden_act="silu", attention_bias=False, rope_scaling=None,
+                  use_sliding_window=False, sliding_window=None, eos_token_id=151645)
+PROMPT_LEN, CTX_LEN, PREFILL_TOKENS = 2048, 4096, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.proc = None
+        self.lines: list[str] = []
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_flops_prefill(c: dict, T: int, layers: int) -> float:
+    D, H, KV, HD, F, V = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                          c["intermediate_size"], c["vocab_size"])
+    linear = 2.0 * T * (D * (H + 2 * KV) * HD + H * HD * D + D * 2 * F + F * D)
+    attn = 2.0 * 2.0 * H * HD * (T * (T + 1) / 2.0)          # QK^T and PV, causal
+    return layers * (linear + attn) + 2.0 * D * V            # the head runs on the last row only
+
+
+def decode_bytes(c: dict, layers: int, batch: int, ctx: float) -> float:
+    D, H, KV, HD, F, V = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                          c["intermediate_size"], c["vocab_size"])
+    per_layer = 2 * (D * (H + 2 * KV) * HD + H * HD * D + D * 2 * F + F * D) + 2 * (2 * D + 2 * HD)
+    head = 2 * D * V if c["tie_word_embeddings"] else 2 * D * V      # read once as the head (the gather reads B rows)
+    kv = batch * ctx * layers * 2 * KV * HD * 2
+    return layers * per_layer + head + 2 * D + kv
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "mynah-slm is a C program built by make with no Python package to install "
+                          "(pip install of the checkout fails: no setup.py or pyproject.toml), and it has no GPU path, "
+                          "no batch and no safetensors loader, so it cannot run this metric on a B200"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only (this library does not use several); --gpus {args.gpus} is not run")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from mynah_slm_b200 import LLM, parse_config
+    from mynah_slm_b200.engine.engine import StepEntry
+    from mynah_slm_b200.ops import gemm_bf16, lib
+    from mynah_slm_b200.sampling.sampler import SamplingParams
+    from mynah_slm_b200.weights.random_init import write_random_model
+
+    cfg = dict(QWEN3_0_6B)
+    layers_model = cfg["num_hidden_layers"]
+    layers = args.layers or layers_model
+    cfg["num_hidden_layers"] = layers
+    pk, pk_src = peaks()
+    K, W, B = args.steps, args.warmup, args.batch
+    max_batch = B if args.no_points else max(B, 64)
+    rng = np.random.default_rng(2)
+    V = cfg["vocab_size"]
+
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_random_model(os.path.join(tmp, "qwen3_0_6b_random"), parse_config(cfg), seed=2,
+                                    dtype=torch.bfloat16)
+        llm = LLM(folder, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
+    eng = llm.engine
+    eng.sampler.set_params(SamplingParams.greedy())
+
+    def device_decode(batch: int, steps: int, warmup: int):
+        """Prompts of PROMPT_LEN, then `warmup` untimed and `steps` timed decode steps on the device."""
+        prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(batch)]
+        slots = [eng.open_sequence() for _ in range(batch)]
+        eng.sampler.start_sequences(slots, list(range(1, batch + 1)), prompts)
+        logits = eng.step([StepEntry(s, p, (PROMPT_LEN - 1,)) for s, p in zip(slots, prompts)])
+        first = eng.sampler.sample(logits, torch.tensor(slots, dtype=torch.int32, device=eng.device)).cpu().tolist()
+        last = eng.decode_loop(slots, first, warmup)
+        toks = last[:batch].cpu().tolist()
+        torch.cuda.synchronize()
+        n0 = lib.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.decode_loop(slots, toks, steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        launches = lib.launch_count() - n0
+        eng.check_status()
+        for s in slots:
+            eng.close_sequence(s)
+        mean_ctx = PROMPT_LEN + 1 + warmup + steps / 2.0
+        return ms, launches, mean_ctx
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, mean_ctx = device_decode(B, K, W)
+    clock_info = clocks.stop()
+    value = B * K / (ms / 1e3)
+    bytes_step = decode_bytes(cfg, layers, B, mean_ctx)
+    achieved = bytes_step / (ms / K / 1e3) / 1e9
+
+    # end to end through the public entry point: host token ids in, host token ids out, every step
+    prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(B)]
+    llm.generate(prompts, max_new=W + 1, temp=0.0, ignore_eos=True, max_batch=B)
+    llm.generate(prompts, max_new=K + 1, temp=0.0, ignore_eos=True, max_batch=B)
+    t = llm.last_timing
+    e2e_value = B * K / t.decode_s if t.decode_s > 0 else 0.0
+    bucket = eng._bucket(B)
+    graph = eng._graphs[max(k for k in eng._graphs if k[0] == bucket)]
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": graph.layout.size * 4,
+           "d2h_bytes_per_step": B * 4}
+
+    # prefill of one prompt of 2,048 tokens (logits of the last position)
+    p = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+    times = []
+    for i in range(3 + 5):
+        s = eng.open_sequence()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([StepEntry(s, p, (PREFILL_TOKENS - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.close_sequence(s)
+        if i >= 3:
+            times.append(e0.elapsed_time(e1))
+    pre_ms = statistics.median(times)
+    flops = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
+    prefill = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    points = {}
+    if not args.no_points:
+        for b, steps in ((1, max(64, K)), (64, min(K, 64))):
+            pms, _, _ = device_decode(b, steps, W)
+            points[f"decode_b{b}"] = round(b * steps / (pms / 1e3), 1)
+
+    out = {
+        "metric": "decode tok/s at batch 8, 2,048-token prompts, 4,096 context (Qwen3-0.6B shape)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights (seed 2), uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen3-0.6B shape", "layers": layers, "layers_of_model": layers_model,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "ffn": cfg["intermediate_size"], "vocab": V, "tied_head": True, "global_batch": B,
+                   "prompt_len": PROMPT_LEN, "seq_len": CTX_LEN, "sampling": "greedy", "cache_dtype": "bf16",
+                   "parallelism": "1 GPU", "l2": "inputs larger than L2 (weights 1.2 GB + cache)",
+                   "peaks": f"{pk_src}: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s"},
+        "e2e": e2e, "gpu_launches": int(launches),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clock_info,
+        "matmul_calls": dict(gemm_bf16.counters),
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
