@@ -266,3 +266,60 @@ MYNAH_API int mynah_attn_decode(
         return launch_decode<bf16>(q, out, B, a, k_cache, v_cache, kv_len, pt, part_o, part_ml, status, stream);
     return mynah_fail("attn_decode: unsupported dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate: the partial
+// results go to a fixed array of this library instead of caller-provided
+// scratch. See no_alloc.h for who needs this and for the rules of use.
+#include "no_alloc.h"
+
+#include <mutex>
+
+namespace {
+
+static __device__ __align__(256) float g_no_alloc_scratch[MYNAH_NO_ALLOC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_no_alloc_mutex;
+float* g_no_alloc_ptr[MAX_DEVICES] = {};
+
+// Device address of the array on the current device. In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device.
+int no_alloc_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return mynah_fail("attn_decode_no_alloc: no current device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return mynah_fail("attn_decode_no_alloc: device ordinal %d is out of range", dev);
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return mynah_fail("attn_decode_no_alloc: cannot find the scratch array on device %d: %s", dev,
+                              cudaGetErrorString(e));
+        g_no_alloc_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_no_alloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+MYNAH_API int mynah_attn_decode_no_alloc(
+    const void* q, void* out, int dtype, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int n_splits, int* status, cudaStream_t stream) {
+    if (B == 0) return 0;
+    MYNAH_REQUIRE(B > 0 && H > 0 && HD > 0 && n_splits >= 1, "attn_decode_no_alloc: bad sizes B=%d H=%d HD=%d splits=%d", B, H, HD, n_splits);
+    const long long need = mynah_attn_decode_scratch_floats(B, H, HD, n_splits);
+    MYNAH_REQUIRE(need <= (long long)MYNAH_NO_ALLOC_SCRATCH_FLOATS,
+                  "attn_decode_no_alloc: B=%d H=%d head_dim=%d splits=%d need %lld floats of scratch, the built-in "
+                  "array holds %d; use mynah_attn_decode with scratch of your own",
+                  B, H, HD, n_splits, need, MYNAH_NO_ALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (no_alloc_scratch(&scratch) != 0) return -1;
+    return mynah_attn_decode(q, out, dtype, B, H, KV, HD, ldq, ldo, k_cache, v_cache, kv_len, page_indptr, page_ids,
+                             page_base, n_pages, window, n_splits, scratch, status, stream);
+}
