@@ -1,0 +1,357 @@
+"""Each part of a layer alone against the plain functions, and the library's
+generality: a toy architecture defined HERE (a mixer with fixed-size state of
+its own, a layer that runs twice, a run that reads another run's cache) is
+registered, written as a random folder, built and stepped without a change to
+the library's files."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import FP32_REL, assert_close, rel_err
+from plain.model import gqa_attention, linear, read_folder, rms_norm, rope_apply, rope_table, swiglu
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ctx(lens, past, page_lists, n_pages, dtype, is_decode=False, splits=1):
+    """A step's batch description built by hand (what Engine.step builds)."""
+    from mynah_slm_b200.engine.context import StepLayout, device_context
+    B, T = len(lens), sum(lens)
+    layout = StepLayout(T=T, B=B, W=1, ids_cap=[sum(len(p) for p in page_lists)])
+    buf = np.zeros(layout.size, dtype=np.int32)
+    v = lambda n: layout.view(buf, n)
+    row = 0
+    for b, (n, p) in enumerate(zip(lens, past)):
+        v("tok_seq")[row:row + n] = b
+        v("tok_pos")[row:row + n] = np.arange(p, p + n)
+        row += n
+        v("cu_q")[b + 1] = row
+        v("kv_len")[b] = p + n
+        v("slots")[b] = b
+        v("indptr0")[b + 1] = v("indptr0")[b] + len(page_lists[b])
+    v("ids0")[:] = [pg for l in page_lists for pg in l]
+    dev = torch.from_numpy(buf).to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ctx = device_context(layout, dev, [n_pages], max(lens), is_decode, splits, status, dtype)
+    ctx.host_q_lens, ctx.host_past, ctx.host_slots = list(lens), list(past), list(range(B))
+    return ctx
+
+
+def _runtime(dtype, max_positions=512):
+    from mynah_slm_b200.engine.engine import Runtime
+    return Runtime(torch.device(DEV), dtype, max_positions)
+
+
+def _t(a, dtype=torch.float32):
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(dtype).to(DEV)
+
+
+def test_rmsnorm_part_and_residual_stream():
+    from mynah_slm_b200.config.spec import PartSpec
+    from mynah_slm_b200.parts import Residual, build_part
+    rng = np.random.default_rng(0)
+    D = 72
+    norm = build_part("norm", PartSpec("rmsnorm", {"eps": 1e-5, "dim": D, "name": "n.weight"}))
+    assert [(s.name, s.shape, s.role) for s in norm.tensor_specs()] == [("n.weight", (D,), "gain")]
+    g = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    norm.bind({"n.weight": _t(g)}, _runtime(torch.float32))
+    x = rng.standard_normal((5, D)).astype(np.float32)
+    d1, d2 = rng.standard_normal((5, D)).astype(np.float32), rng.standard_normal((5, D)).astype(np.float32)
+    stream = Residual(_t(x))
+    stream.add(_t(d1))
+    stream.add(_t(d2))                          # a second add flushes the first
+    h = norm.apply(stream).cpu().numpy()
+    assert stream.pending is None
+    assert np.allclose(stream.x.cpu().numpy(), x + d1 + d2, atol=1e-6)
+    assert rel_err(rms_norm(x + d1 + d2, g, 1e-5), h) < 2e-6
+
+
+def test_swiglu_part_alone():
+    from mynah_slm_b200.config.spec import PartSpec
+    from mynah_slm_b200.parts import build_part
+    rng = np.random.default_rng(1)
+    D, F = 40, 104
+    ffn = build_part("ffn", PartSpec("swiglu_dense", {"hidden_size": D, "intermediate_size": F, "activation": "silu",
+                                                      "prefix": "m."}))
+    assert sorted(s.name for s in ffn.tensor_specs()) == ["m.down_proj.weight", "m.gate_proj.weight", "m.up_proj.weight"]
+    w = {n: (rng.standard_normal(s) * 0.2).astype(np.float32) for n, s in
+         (("m.gate_proj.weight", (F, D)), ("m.up_proj.weight", (F, D)), ("m.down_proj.weight", (D, F)))}
+    ffn.bind({k: _t(v) for k, v in w.items()}, _runtime(torch.float32))
+    h = rng.standard_normal((7, D)).astype(np.float32)
+    got = ffn.forward(_t(h), None).cpu().numpy()
+    ref = linear(swiglu(linear(h, w["m.gate_proj.weight"]), linear(h, w["m.up_proj.weight"])), w["m.down_proj.weight"])
+    assert rel_err(ref, got) < 5e-6
+
+
+@pytest.mark.parametrize("position,qk_norm,window", [("rope_neox", True, None), ("none", False, None), ("rope_neox", True, 20),
+                                                     ("rope_half", True, None)])
+def test_attention_part_alone(position, qk_norm, window):
+    """The mixer with its options switched one by one: with and without the
+    per-head norm, with and without rotation, rotation over half the head
+    (another position encoding), with a window; a prompt step, then a decode
+    step on the cache it left."""
+    from mynah_slm_b200.config.spec import PartSpec
+    from mynah_slm_b200.parts import CacheView, build_part
+    rng = np.random.default_rng(2)
+    D, H, KV, HD, eps, theta = 56, 4, 2, 32, 1e-5, 777.0
+    rot = HD if position == "rope_neox" else HD // 2
+    pos_spec = PartSpec("none", {}) if position == "none" else PartSpec("rope_neox", {"theta": theta, "rotary_dim": rot})
+    spec = PartSpec("gqa_attention", {"hidden_size": D, "num_heads": H, "num_kv_heads": KV, "head_dim": HD,
+                                      "qk_norm": PartSpec("rmsnorm", {"eps": eps}) if qk_norm else None,
+                                      "position": pos_spec, "window": window, "prefix": "a."})
+    att = build_part("mixer", spec)
+    names = {s.name: s.shape for s in att.tensor_specs()}
+    assert ("a.q_norm.weight" in names) == qk_norm and names["a.q_proj.weight"] == (H * HD, D)
+    assert att.kv_request().window == window
+    w = {n: ((1 + 0.1 * rng.standard_normal(s)) if "norm" in n else rng.standard_normal(s) * 0.2).astype(np.float32)
+         for n, s in names.items()}
+    rt = _runtime(torch.float32)
+    att.bind({k: _t(v) for k, v in w.items()}, rt)
+    lens, n_pages = [70, 9], 4
+    lists = [[2, 0], [3]]
+    kc = torch.zeros((n_pages, KV, 64, HD), device=DEV)
+    vc = torch.zeros_like(kc)
+    cache = CacheView(group=0, k=kc, v=vc, writes=True)
+    hs = [rng.standard_normal((n + 1, D)).astype(np.float32) for n in lens]       # one more row for the decode step
+
+    def plain(h):
+        n = h.shape[0]
+        q = linear(h, w["a.q_proj.weight"]).reshape(n, H, HD)
+        k = linear(h, w["a.k_proj.weight"]).reshape(n, KV, HD)
+        v = linear(h, w["a.v_proj.weight"]).reshape(n, KV, HD)
+        if qk_norm:
+            q, k = rms_norm(q, w["a.q_norm.weight"], eps), rms_norm(k, w["a.k_norm.weight"], eps)
+        if position != "none":
+            c, s = rope_table(rot, np.arange(n), theta)
+            q = np.concatenate([rope_apply(q[..., :rot], c, s), q[..., rot:]], -1)
+            k = np.concatenate([rope_apply(k[..., :rot], c, s), k[..., rot:]], -1)
+        a = gqa_attention(q, k, v, window=window)
+        return linear(a.reshape(n, H * HD), w["a.o_proj.weight"])
+    refs = [plain(h) for h in hs]
+    ctx = _ctx(lens, [0, 0], lists, n_pages, torch.float32)
+    got = att.forward(_t(np.concatenate([h[:-1] for h in hs])), ctx, cache).cpu().numpy()
+    assert ctx.status.item() == 0
+    assert rel_err(np.concatenate([r[:-1] for r in refs]), got) < 5e-6
+    ctx = _ctx([1, 1], lens, lists, n_pages, torch.float32, is_decode=True, splits=2)
+    got = att.forward(_t(np.stack([h[-1] for h in hs])), ctx, cache).cpu().numpy()
+    assert ctx.status.item() == 0
+    assert rel_err(np.stack([r[-1] for r in refs]), got) < 5e-6
+
+
+def test_block_part_alone():
+    from mynah_slm_b200.config.spec import PartSpec
+    from mynah_slm_b200.parts import CacheView, Residual, build_part
+    rng = np.random.default_rng(3)
+    D, F, H, KV, HD, eps = 48, 80, 3, 1, 16, 1e-6
+    mixer = build_part("mixer", PartSpec("gqa_attention", {
+        "hidden_size": D, "num_heads": H, "num_kv_heads": KV, "head_dim": HD, "qk_norm": None,
+        "position": PartSpec("rope_neox", {"theta": 100.0, "rotary_dim": HD}), "window": None, "prefix": "a."}))
+    ffn = build_part("ffn", PartSpec("swiglu_dense", {"hidden_size": D, "intermediate_size": F, "prefix": "m."}))
+    norms = {k: build_part("norm", PartSpec("rmsnorm", {"eps": eps, "dim": D, "name": f"{k}.weight"})) for k in ("mixer", "ffn")}
+    block = build_part("block", PartSpec("prenorm_residual", {}), mixer, ffn, norms)
+    w = {}
+    rt = _runtime(torch.float32)
+    for part in block.parts():
+        specs = part.tensor_specs()
+        mine = {s.name: ((1 + 0.1 * rng.standard_normal(s.shape)) if s.role == "gain" else rng.standard_normal(s.shape) * 0.2)
+                .astype(np.float32) for s in specs}
+        w.update(mine)
+        part.bind({k: _t(v) for k, v in mine.items()}, rt)
+    n = 11
+    x = rng.standard_normal((n, D)).astype(np.float32)
+    kc = torch.zeros((1, KV, 64, HD), device=DEV)
+    stream = Residual(_t(x))
+    block.forward(stream, _ctx([n], [0], [[0]], 1, torch.float32), CacheView(group=0, k=kc, v=torch.zeros_like(kc)))
+    got = stream.flush().cpu().numpy()
+    h = rms_norm(x, w["mixer.weight"], eps)
+    c, s = rope_table(HD, np.arange(n), 100.0)
+    q = rope_apply(linear(h, w["a.q_proj.weight"]).reshape(n, H, HD), c, s)
+    k = rope_apply(linear(h, w["a.k_proj.weight"]).reshape(n, KV, HD), c, s)
+    v = linear(h, w["a.v_proj.weight"]).reshape(n, KV, HD)
+    x1 = x + linear(gqa_attention(q, k, v).reshape(n, -1), w["a.o_proj.weight"])
+    h = rms_norm(x1, w["ffn.weight"], eps)
+    ref = x1 + linear(swiglu(linear(h, w["m.gate_proj.weight"]), linear(h, w["m.up_proj.weight"])), w["m.down_proj.weight"])
+    assert rel_err(ref, got) < 5e-6
+    with pytest.raises(Exception, match="'ffn' norm"):
+        build_part("block", PartSpec("prenorm_residual", {}), mixer, ffn, {"mixer": norms["mixer"]})
+
+
+# --------------------------------------------------------------- a toy model
+
+TOY_ARCH = "ToyStateForCausalLM"
+
+
+def _register_toy():
+    """A mixer with state of its own and an architecture that uses it: all of
+    it lives in this test file."""
+    from dataclasses import dataclass
+
+    from mynah_slm_b200.config.keys import req_float, req_int
+    from mynah_slm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from mynah_slm_b200.parts import Mixer, StateRequest, TensorSpec, register_mixer
+    from mynah_slm_b200.registry import known_architectures, register_architecture
+
+    class DecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + W_in h_t ;  out_t = W_out s_t. State: s, per sequence."""
+        graph_safe = False                   # plans on the host, token by token
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.D, self.S, self.decay, self.prefix = spec["hidden_size"], spec["state_size"], spec["decay"], spec["prefix"]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "in.weight", (self.S, self.D), std=0.2),
+                    TensorSpec(self.prefix + "out.weight", (self.D, self.S), std=0.2)]
+
+        def bind(self, tensors, runtime):
+            self.w_in, self.w_out = tensors[self.prefix + "in.weight"], tensors[self.prefix + "out.weight"]
+
+        def state_request(self):
+            return StateRequest((self.S,), torch.float32)
+
+        def forward(self, h, ctx, cache):
+            u = h.float() @ self.w_in.float().t()
+            out = torch.empty_like(u)
+            row = 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):
+                s = cache.state[slot]
+                for t in range(row, row + n):
+                    s = self.decay * s + u[t]
+                    out[t] = s
+                cache.state[slot] = s
+                row += n
+            return (out @ self.w_out.float().t()).to(h.dtype)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        raw: tuple
+
+        @classmethod
+        def from_dict(cls, d, generation=None):
+            for k in ("hidden_size", "vocab_size", "state_size", "num_heads", "num_kv_heads", "head_dim", "ffn_size",
+                      "max_positions"):
+                req_int(d, k)
+            req_float(d, "decay"), req_float(d, "eps"), req_float(d, "theta")
+            return cls(tuple(sorted((k, json.dumps(v)) for k, v in d.items())))
+
+        def to_dict(self):
+            return {k: json.loads(v) for k, v in self.raw}
+
+        def model_spec(self):
+            d = self.to_dict()
+            D = d["hidden_size"]
+
+            def norms(p):
+                return {k: PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": f"{p}{k}_norm.weight"}) for k in ("mixer", "ffn")}
+
+            def ffn(p):
+                return PartSpec("swiglu_dense", {"hidden_size": D, "intermediate_size": d["ffn_size"], "prefix": p + "mlp."})
+            layers = []
+            for i, kind in enumerate(d["mixers"]):
+                p = f"layers.{i}."
+                if kind == "decay":
+                    mixer = PartSpec("toy_decay", {"hidden_size": D, "state_size": d["state_size"], "decay": d["decay"],
+                                                   "prefix": p + "mix."})
+                else:
+                    mixer = PartSpec("gqa_attention", {"hidden_size": D, "num_heads": d["num_heads"],
+                                                       "num_kv_heads": d["num_kv_heads"], "head_dim": d["head_dim"],
+                                                       "qk_norm": None, "window": None, "prefix": p + "attn.",
+                                                       "position": PartSpec("rope_neox", {"theta": d["theta"],
+                                                                                          "rotary_dim": d["head_dim"]})})
+                layers.append(LayerSpec(PartSpec("prenorm_residual", {}), mixer, ffn(p), norms(p), p))
+            sched = tuple(ScheduleEntry(l, c) for l, c in d["schedule"])
+            return ModelSpec(TOY_ARCH, d["vocab_size"], D, d["max_positions"], tuple(layers), sched,
+                             PartSpec("token_embedding", {"name": "embed.weight", "vocab_size": d["vocab_size"], "dim": D}),
+                             PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": "final_norm.weight"}),
+                             PartSpec("linear_head", {"tied": True, "name": "head.weight", "vocab_size": d["vocab_size"], "dim": D}))
+
+    register_mixer("toy_decay", DecayMixer, replace=True)
+    if TOY_ARCH not in known_architectures():
+        register_architecture(TOY_ARCH, ToyConfig.from_dict)
+
+
+TOY = dict(architectures=[TOY_ARCH], hidden_size=40, vocab_size=300, state_size=24, num_heads=4, num_kv_heads=2,
+           head_dim=16, ffn_size=72, max_positions=256, decay=0.9, eps=1e-5, theta=500.0,
+           mixers=["decay", "attn", "attn"],
+           # layer 1 runs twice (a cache of its own each time); the last run of layer 2 reads the cache of run 2
+           schedule=[[0, None], [1, None], [2, None], [1, None], [2, 2]])
+
+
+def _toy_plain(cfg, t, tokens):
+    D, H, KV, HD = cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    n = len(tokens)
+    x = t["embed.weight"][np.asarray(tokens)]
+    c, s = rope_table(HD, np.arange(n), cfg["theta"])
+    kept = {}
+    for e, (l, src) in enumerate(cfg["schedule"]):
+        p = f"layers.{l}."
+        h = rms_norm(x, t[p + "mixer_norm.weight"], cfg["eps"])
+        if cfg["mixers"][l] == "decay":
+            u = linear(h, t[p + "mix.in.weight"])
+            st = np.zeros(cfg["state_size"], dtype=np.float32)
+            rows = []
+            for i in range(n):
+                st = np.float32(cfg["decay"]) * st + u[i]
+                rows.append(st.copy())
+            m = linear(np.stack(rows), t[p + "mix.out.weight"])
+        else:
+            q = rope_apply(linear(h, t[p + "attn.q_proj.weight"]).reshape(n, H, HD), c, s)
+            if src is None:
+                k = rope_apply(linear(h, t[p + "attn.k_proj.weight"]).reshape(n, KV, HD), c, s)
+                v = linear(h, t[p + "attn.v_proj.weight"]).reshape(n, KV, HD)
+                kept[e] = (k, v)
+            else:
+                k, v = kept[src]
+            m = linear(gqa_attention(q, k, v).reshape(n, H * HD), t[p + "attn.o_proj.weight"])
+        x = x + m
+        h = rms_norm(x, t[p + "ffn_norm.weight"], cfg["eps"])
+        x = x + linear(swiglu(linear(h, t[p + "mlp.gate_proj.weight"]), linear(h, t[p + "mlp.up_proj.weight"])),
+                       t[p + "mlp.down_proj.weight"])
+    return linear(rms_norm(x, t["final_norm.weight"], cfg["eps"]), t["embed.weight"])
+
+
+def test_toy_architecture_with_state_registers_builds_and_steps(tmp_path):
+    _register_toy()
+    from mynah_slm_b200.engine.engine import Engine, StepEntry
+    from mynah_slm_b200.registry import parse_config
+    from mynah_slm_b200.weights.random_init import write_random_model
+    folder = write_random_model(str(tmp_path / "toy"), parse_config(TOY), seed=3, dtype=torch.float32)
+    cfg, tensors = read_folder(folder)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 6)
+    plan = eng.cache.plan
+    assert [e.group for e in plan.entries] == [None, 0, 0, 0, None] and plan.entries[4].source == 2
+    assert plan.entries[0].state is not None and len(plan.groups[0].entries) == 3
+    assert not eng.graph_safe
+    rng = np.random.default_rng(4)
+    seqs = [rng.integers(0, 300, size=n).tolist() for n in (70, 9, 33)]
+    refs = [_toy_plain(cfg, tensors, s) for s in seqs]
+    # whole, alone
+    for s, r in zip(seqs, refs):
+        slot = eng.open_sequence()
+        assert_close(r, eng.step([StepEntry(slot, s, range(len(s)))]).cpu().numpy(), FP32_REL, "toy whole")
+        eng.close_sequence(slot)
+    # together with unequal lengths, then token by token; the state carries over; slots are reused
+    slots = [eng.open_sequence() for _ in seqs]
+    heads = [len(s) - 5 for s in seqs]
+    out = eng.step([StepEntry(sl, s[:h], range(h)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+    got = [[] for _ in seqs]
+    row = 0
+    for i, h in enumerate(heads):
+        got[i].append(out[row:row + h]); row += h
+    for t in range(5):
+        out = eng.step([StepEntry(sl, [s[h + t]], (0,)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+        for i in range(len(seqs)):
+            got[i].append(out[i:i + 1])
+    eng.check_status()
+    for i, r in enumerate(refs):
+        assert_close(r, np.concatenate(got[i]), FP32_REL, f"toy request {i} in a batch, last 5 one by one")
+    for sl in slots:
+        eng.close_sequence(sl)
+    # a reused slot starts from a zero state
+    slot = eng.open_sequence()
+    assert slot in slots
+    assert_close(refs[1], eng.step([StepEntry(slot, seqs[1], range(len(seqs[1])))]).cpu().numpy(), FP32_REL, "toy reused slot")
