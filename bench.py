@@ -131,6 +131,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run one small phase and print a short line (for profiling a kernel on a small case)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -160,7 +163,8 @@ def main() -> int:
     cfg["num_hidden_layers"] = layers
     pk, pk_src = peaks()
     K, W, B = args.steps, args.warmup, args.batch
-    max_batch = B if args.no_points else max(B, 64)
+    max_batch = B if (args.no_points or args.only) else max(B, 64)
+    prompt_len = args.prompt_len
     rng = np.random.default_rng(2)
     V = cfg["vocab_size"]
 
@@ -173,10 +177,10 @@ def main() -> int:
 
     def device_decode(batch: int, steps: int, warmup: int):
         """Prompts of PROMPT_LEN, then `warmup` untimed and `steps` timed decode steps on the device."""
-        prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(batch)]
+        prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(batch)]
         slots = [eng.open_sequence() for _ in range(batch)]
         eng.sampler.start_sequences(slots, list(range(1, batch + 1)), prompts)
-        logits = eng.step([StepEntry(s, p, (PROMPT_LEN - 1,)) for s, p in zip(slots, prompts)])
+        logits = eng.step([StepEntry(s, p, (prompt_len - 1,)) for s, p in zip(slots, prompts)])
         first = eng.sampler.sample(logits, torch.tensor(slots, dtype=torch.int32, device=eng.device)).cpu().tolist()
         last = eng.decode_loop(slots, first, warmup)
         toks = last[:batch].cpu().tolist()
@@ -192,8 +196,39 @@ def main() -> int:
         eng.check_status()
         for s in slots:
             eng.close_sequence(s)
-        mean_ctx = PROMPT_LEN + 1 + warmup + steps / 2.0
+        mean_ctx = prompt_len + 1 + warmup + steps / 2.0
         return ms, launches, mean_ctx
+
+    def time_prefill(n_timed: int = 5):
+        p = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+        times = []
+        for i in range(3 + n_timed):
+            s = eng.open_sequence()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([StepEntry(s, p, (PREFILL_TOKENS - 1,))])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.close_sequence(s)
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        return statistics.median(times)
+
+    if args.only == "decode":
+        ms, launches, mean_ctx = device_decode(B, K, W)
+        gbs = decode_bytes(cfg, layers, B, mean_ctx) / (ms / K / 1e3) / 1e9
+        print(json.dumps({"only": "decode", "batch": B, "layers": layers, "prompt_len": prompt_len, "steps": K,
+                          "ms_per_step": round(ms / K, 4), "tokens_per_s": round(B * K / (ms / 1e3), 1),
+                          "GBps": round(gbs, 1), "launches": launches}))
+        return 0
+    if args.only == "prefill":
+        pre_ms = time_prefill(max(1, K))
+        fl = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                          "tokens_per_s": round(PREFILL_TOKENS / (pre_ms / 1e3), 1),
+                          "TFLOPs": round(fl / (pre_ms / 1e3) / 1e12, 1)}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()
@@ -204,7 +239,7 @@ def main() -> int:
     achieved = bytes_step / (ms / K / 1e3) / 1e9
 
     # end to end through the public entry point: host token ids in, host token ids out, every step
-    prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(B)]
+    prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(B)]
     llm.generate(prompts, max_new=W + 1, temp=0.0, ignore_eos=True, max_batch=B)
     llm.generate(prompts, max_new=K + 1, temp=0.0, ignore_eos=True, max_batch=B)
     t = llm.last_timing
@@ -215,20 +250,7 @@ def main() -> int:
            "d2h_bytes_per_step": B * 4}
 
     # prefill of one prompt of 2,048 tokens (logits of the last position)
-    p = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
-    times = []
-    for i in range(3 + 5):
-        s = eng.open_sequence()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        eng.step([StepEntry(s, p, (PREFILL_TOKENS - 1,))])
-        e1.record()
-        torch.cuda.synchronize()
-        eng.close_sequence(s)
-        if i >= 3:
-            times.append(e0.elapsed_time(e1))
-    pre_ms = statistics.median(times)
+    pre_ms = time_prefill()
     flops = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
     prefill = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
@@ -249,7 +271,7 @@ def main() -> int:
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "ffn": cfg["intermediate_size"], "vocab": V, "tied_head": True, "global_batch": B,
-                   "prompt_len": PROMPT_LEN, "seq_len": CTX_LEN, "sampling": "greedy", "cache_dtype": "bf16",
+                   "prompt_len": prompt_len, "seq_len": CTX_LEN, "sampling": "greedy", "cache_dtype": "bf16",
                    "parallelism": "1 GPU", "l2": "inputs larger than L2 (weights 1.2 GB + cache)",
                    "peaks": f"{pk_src}: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s"},
         "e2e": e2e, "gpu_launches": int(launches),

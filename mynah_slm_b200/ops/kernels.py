@@ -193,6 +193,26 @@ def attn_decode(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, H
          window or 0, n_splits, ptr(scratch), ptr(status), stream_ptr())
 
 
+def attn_decode_tc_supported(dtype: torch.dtype, H: int, KV: int, HD: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib.load().mynah_attn_decode_tc_supported(H, KV, HD))
+
+
+def attn_decode_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor, pages: PageTableView,
+                   window: int, n_splits: int, scratch: torch.Tensor, status: torch.Tensor) -> None:
+    """The tensor-core decode attention (bfloat16, head_dim 64 or 128); same contract as attn_decode."""
+    _chk(qkv, "q", torch.bfloat16, 2)
+    _chk(out, "attention output", torch.bfloat16, 2)
+    _chk(scratch, "scratch", torch.float32)
+    need = B * H * n_splits * (HD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode_tc: scratch holds {scratch.numel()} floats, {need} are needed")
+    call("mynah_attn_decode_tc", ptr(qkv), ptr(out), B, H, KV, HD, qkv.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, n_splits, ptr(scratch), ptr(status), stream_ptr())
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _chk(logits, "logits", torch.float32, 2)
     B, V = logits.shape

@@ -46,6 +46,10 @@ _SIGNATURES: dict[str, list] = {
                           P, P, P,
                           P, P, P, c_int,
                           c_int, c_int, P, P, P],
+    "mynah_attn_decode_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                             P, P, P,
+                             P, P, P, c_int,
+                             c_int, c_int, P, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
@@ -72,6 +76,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_device_arch.argtypes = []
     lib.mynah_attn_decode_scratch_floats.restype = c_longlong
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mynah_attn_decode_tc_supported.restype = c_int
+    lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)

@@ -102,12 +102,11 @@ class GQAttention(Mixer):
             ctx.tok_seq, ctx.tok_pos, pages,
             cache.k if writes else None, cache.v if writes else None, ctx.status)
         out = torch.empty((T, H * HD), dtype=qkv.dtype, device=qkv.device)
+        from ..ops import attention_dispatch
         if ctx.is_decode:
-            kernels.attn_decode(qkv, out, ctx.B, H, KV, HD, cache.k, cache.v, ctx.kv_len, pages,
-                                self.window or 0, ctx.decode_splits, self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits),
-                                ctx.status)
+            attention_dispatch.decode(qkv, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0,
+                                      self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits))
         else:
-            from ..ops import attention_dispatch
             attention_dispatch.prefill(qkv, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0)
         return kernels.linear(out, self.w_o)
 

@@ -414,3 +414,81 @@ def test_refusals_are_errors_not_wrong_results():
         k.swiglu(torch.zeros((4, 8), device=DEV)[:, ::2])
     with pytest.raises(KernelError, match="unsupported dtype"):
         k.swiglu(torch.zeros((4, 8), device=DEV, dtype=torch.float16))
+
+
+@pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (8, 1, 64, 100), (32, 8, 128, 0), (16, 1, 128, 0), (6, 2, 64, 70)])
+def test_attn_decode_tensor_cores(H, KV, HD, window):
+    """The tensor-core decode kernel against the plain attention, with stale
+    values (NaN bit patterns) in the unused tail of every page."""
+    k = _k()
+    assert k.attn_decode_tc_supported(torch.bfloat16, H, KV, HD)
+    assert not k.attn_decode_tc_supported(torch.bfloat16, 6, 2, 48) and not k.attn_decode_tc_supported(torch.float32, H, KV, HD)
+    rng = np.random.default_rng(14)
+    lens = [1, 64, 65, 300, 0, 517, 128]
+    B, n_pages = len(lens), 26
+    free = list(np.random.default_rng(15).permutation(n_pages))
+    kc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lists, seqs = [], []
+    for n in lens:
+        kk, vv = _round(rng.standard_normal((n, KV, HD)), "bf16"), _round(rng.standard_normal((n, KV, HD)), "bf16")
+        pages = [int(free.pop()) for _ in range(-(-n // 64))]
+        lists.append(pages)
+        seqs.append((kk, vv))
+        for t in range(n):
+            kc[pages[t // 64], :, t % 64] = torch.from_numpy(kk[t]).to(torch.bfloat16).to(DEV)
+            vc[pages[t // 64], :, t % 64] = torch.from_numpy(vv[t]).to(torch.bfloat16).to(DEV)
+    q = _round(rng.standard_normal((B, H, HD)), "bf16")
+    qd = torch.from_numpy(q.reshape(B, -1)).to(torch.bfloat16).to(DEV)
+    kvl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = []
+    for splits in (9, 16):
+        out = torch.full((B, H * HD), 7.0, dtype=torch.bfloat16, device=DEV)
+        scratch = torch.full((k.attn_decode_scratch_floats(B, H, HD, splits),), float("nan"), dtype=torch.float32, device=DEV)
+        k.attn_decode_tc(qd, out, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, splits, scratch, status)
+        assert status.item() == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])                       # the size of the launch does not change a bit
+    got = outs[0].float().cpu().numpy()
+    assert np.isfinite(got).all()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert np.all(got[b] == 0)
+            continue
+        kk, vv = seqs[b]
+        ref = gqa_attention(q[b:b + 1], kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
+        assert rel_err(ref.reshape(1, -1), got[b:b + 1]) < 1e-2, (b, n)
+    # each sequence alone gives the same bits as in the batch
+    b = 5
+    out1 = torch.zeros((1, H * HD), dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty(k.attn_decode_scratch_floats(1, H, HD, 9), dtype=torch.float32, device=DEV)
+    k.attn_decode_tc(qd[b:b + 1].contiguous(), out1, 1, H, KV, HD, kc, vc, kvl[b:b + 1].contiguous(),
+                     _page_table([lists[b]])(n_pages), window, 9, scratch, status)
+    assert torch.equal(out1[0], outs[0][b])
+    k.attn_decode_tc(qd, out, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, 2, scratch.new_empty(B * H * 2 * (HD + 2)), status)
+    assert status.item() == 8
+    status.zero_()
+
+
+def test_attn_decode_tensor_cores_one_far_key():
+    k = _k()
+    H, KV, HD, n = 4, 2, 128, 400
+    rng = np.random.default_rng(16)
+    for window, target, visible in [(0, 3, True), (0, 64, True), (0, 399, True), (120, 280, True), (120, 279, False)]:
+        kk = _round(rng.standard_normal((n, KV, HD)) * 0.1, "bf16")
+        vv = _round(rng.standard_normal((n, KV, HD)), "bf16")
+        q = _round(rng.standard_normal((1, H, HD)) * 0.1, "bf16")
+        kk[target, 1] = _round(q[0, 3] / np.linalg.norm(q[0, 3]) * 60.0, "bf16")      # head 3 reads kv head 1
+        q[0, 3] = _round(q[0, 3] * 16, "bf16")
+        lists = [[5, 1, 6, 2, 0, 3, 4]]
+        kc, vc = _paged(kk, lists[0], 7, "bf16"), _paged(vv, lists[0], 7, "bf16")
+        out = torch.zeros((1, H * HD), dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(k.attn_decode_scratch_floats(1, H, HD, 7), dtype=torch.float32, device=DEV)
+        k.attn_decode_tc(torch.from_numpy(q.reshape(1, -1)).to(torch.bfloat16).to(DEV), out, 1, H, KV, HD, kc, vc,
+                         torch.tensor([n], dtype=torch.int32, device=DEV), _page_table(lists)(7), window, 7, scratch, status)
+        got = out.float().cpu().numpy()[0, 3 * HD:4 * HD]
+        assert (np.abs(got - vv[target, 1]).max() < 0.05) == visible, (window, target)
+        ref = gqa_attention(q, kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
+        assert rel_err(ref.reshape(1, -1), out.float().cpu().numpy()) < 2e-2
