@@ -1,0 +1,240 @@
+// Matrix products of a decode step: y[M, N] = x[M, K] . W[N, K]^T for a
+// handful of rows M (at most 16: one row per sequence of the batch), bf16
+// operands, fp32 accumulation. The weights are read once, straight from global
+// memory, 16 bytes per lane; the kernel is bound by that stream, so what is
+// fused around it costs no extra pass over memory:
+//
+//   prologue  RMSNorm of the residual stream (with the pending residual add)
+//             computed by every CTA into shared memory, so the normalised rows
+//             are never written out; CTA 0 also writes the updated residual.
+//   epilogue  plain bf16 rows | SwiGLU of a gate row and its up row | fp32 rows
+//             (the output head's logits).
+//
+// Tensor-core mapping (mma.sync m16n8k16): the batch rows are the 16 rows of
+// the A operand, eight weight rows are the 8 columns of the B operand, so one
+// warp instruction covers 8 weight rows x 16 k. Each lane loads 16 contiguous
+// bytes of a weight row; the k indices inside a block of 32 are permuted
+// consistently for both operands (a dot product does not care about the order
+// of its terms), which is what lets a lane use its 16 bytes as two B fragments
+// without any shuffle. The 8 warps of a CTA split K and add their partial sums
+// in warp order, so the result does not depend on timing.
+//
+// y = W.x with W [out, in] row-major, as in the reference
+// (mynah-slm src/arch_qwen3.c:51-52); norm as src/kernels.c:118-128; SwiGLU as
+// src/kernels.c:193-205.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int MAX_M = 16;
+constexpr int XPAD = 32;              // elements of padding per row of x in shared memory (bank spread)
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+
+struct GemvArgs {
+    const bf16* W;
+    int N, K, M;                      // N: rows of W that produce outputs (for SwiGLU: gate rows; up rows follow at +N)
+    const bf16* x_bf16;               // [M, K] when there is no norm prologue
+    const float* x_res;               // [M, K] residual (norm prologue)
+    const bf16* delta;                // [M, K] pending add, or null
+    float* x_res_out;                 // [M, K] updated residual, written by CTA 0 when delta is given
+    VecRef gain;
+    float eps;
+    void* out;
+    int ldo;
+    int groups_per_cta;               // groups of 8 weight rows each CTA works through
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float stable_sigmoid_f(float v) {
+    if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
+    const float e = expf(v);
+    return e / (1.0f + e);
+}
+
+template <int EPI, bool NORM>
+__global__ void __launch_bounds__(THREADS)
+gemv_decode_kernel(GemvArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                    // [MAX_M or 8][K + XPAD]
+    __shared__ float red[WARPS][32][EPI == EPI_SWIGLU ? 8 : 4];
+    const int K = a.K, M = a.M, ldx = K + XPAD;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rows_x = M > 8 ? 16 : 8;
+
+    // ---- the input rows, in bf16, into shared memory
+    if (NORM) {
+        for (int m = warp; m < M; m += WARPS) {                      // one warp per row, rows in parallel
+            const float* xr = a.x_res + (size_t)m * K;
+            const bf16* dr = a.delta ? a.delta + (size_t)m * K : nullptr;
+            float ss = 0.f;
+            for (int i = lane; i < K; i += 32) {
+                float v = xr[i];
+                if (dr) v += to_f32(dr[i]);
+                ss += v * v;
+            }
+            ss = warp_sum(ss);
+            const float s = 1.0f / sqrtf(ss / (float)K + a.eps);
+            for (int i = lane; i < K; i += 32) {
+                float v = xr[i];
+                if (dr) {
+                    v += to_f32(dr[i]);
+                    if (blockIdx.x == 0) a.x_res_out[(size_t)m * K + i] = v;
+                }
+                xs[m * ldx + i] = __float2bfloat16_rn((v * s) * a.gain.at(i));
+            }
+        }
+    } else {
+        for (int i = tid; i < M * (K / 8); i += THREADS) {
+            const int m = i / (K / 8), c = i % (K / 8);
+            *reinterpret_cast<uint4*>(xs + m * ldx + c * 8) = *reinterpret_cast<const uint4*>(a.x_bf16 + (size_t)m * K + c * 8);
+        }
+    }
+    for (int i = tid; i < (rows_x - M) * (K / 8); i += THREADS) {   // rows beyond the batch are zero
+        const int m = M + i / (K / 8), c = i % (K / 8);
+        *reinterpret_cast<uint4*>(xs + m * ldx + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+
+    const int nkb = K / 32;                                          // blocks of 32 k
+    for (int gi = 0; gi < a.groups_per_cta; gi++) {
+        const int n0 = (blockIdx.x * a.groups_per_cta + gi) * 8;
+        if (n0 >= a.N) break;                                        // uniform over the CTA
+        const int row = n0 + g;                                      // this lane's weight row (as B column g)
+        const bool row_ok = row < a.N;
+        const bf16* w_gate = a.W + (size_t)(row_ok ? row : 0) * K;
+        const bf16* w_up = EPI == EPI_SWIGLU ? a.W + (size_t)((row_ok ? row : 0) + a.N) * K : nullptr;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int kb0 = warp; kb0 < nkb; kb0 += WARPS * 4) {
+            uint4 wv[4], uv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {                            // loads first: up to 8 x 16 bytes in flight per lane
+                const int kb = kb0 + u * WARPS;
+                const bool ok = kb < nkb && row_ok;
+                wv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_gate + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+                if (EPI == EPI_SWIGLU)
+                    uv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_up + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int kb = kb0 + u * WARPS;
+                if (kb < nkb) {                                      // uniform over the warp
+                    const uint4 xa = *reinterpret_cast<const uint4*>(xs + g * ldx + kb * 32 + t * 8);
+                    uint4 xb = make_uint4(0, 0, 0, 0);
+                    if (rows_x == 16) xb = *reinterpret_cast<const uint4*>(xs + (g + 8) * ldx + kb * 32 + t * 8);
+                    const uint32_t a1[4] = {xa.x, xb.x, xa.y, xb.y};   // k-permuted: both operands use the same order
+                    const uint32_t a2[4] = {xa.z, xb.z, xa.w, xb.w};
+                    mma_bf16(c0, a1, wv[u].x, wv[u].y);
+                    mma_bf16(c0, a2, wv[u].z, wv[u].w);
+                    if (EPI == EPI_SWIGLU) {
+                        mma_bf16(c1, a1, uv[u].x, uv[u].y);
+                        mma_bf16(c1, a2, uv[u].z, uv[u].w);
+                    }
+                }
+            }
+        }
+        // ---- add the warps' partial sums in warp order
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            red[warp][lane][e] = c0[e];
+            if (EPI == EPI_SWIGLU) red[warp][lane][4 + e] = c1[e];
+        }
+        __syncthreads();
+        if (warp == 0) {
+            float s0[4], s1[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                s0[e] = red[0][lane][e];
+                if (EPI == EPI_SWIGLU) s1[e] = red[0][lane][4 + e];
+            }
+            for (int w = 1; w < WARPS; w++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    s0[e] += red[w][lane][e];
+                    if (EPI == EPI_SWIGLU) s1[e] += red[w][lane][4 + e];
+                }
+            }
+            // C layout: s[0..1] -> batch row g, weight rows n0 + 2t + {0,1}; s[2..3] -> batch row g + 8
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int m = g + 8 * half;
+                if (m >= M) continue;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int n = n0 + 2 * t + j;
+                    if (n >= a.N) continue;
+                    float v = s0[2 * half + j];
+                    if (EPI == EPI_SWIGLU) {
+                        // both rounded to the activation type first, as when gate and up are stored before the activation
+                        const float gt = round_to<bf16>(v), up = round_to<bf16>(s1[2 * half + j]);
+                        v = (gt * stable_sigmoid_f(gt)) * up;
+                    }
+                    if (EPI == EPI_F32) static_cast<float*>(a.out)[(size_t)m * a.ldo + n] = v;
+                    else static_cast<bf16*>(a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int EPI, bool NORM>
+int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
+    auto kern = gemv_decode_kernel<EPI, NORM>;
+    static int allowed = 0;                           // per instantiation: the largest size opted in to so far
+    if (smem > 48 * 1024 && (int)smem > allowed) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return mynah_fail("gemv_decode: %s", cudaGetErrorString(e));
+        allowed = (int)smem;
+    }
+    kern<<<n_ctas, THREADS, smem, stream>>>(a);
+    return mynah_check_launch("gemv_decode");
+}
+
+}  // namespace
+
+// Whether the kernel takes these sizes.
+MYNAH_API int mynah_gemv_decode_supported(int M, int N, int K) {
+    if (M < 1 || M > MAX_M || N < 1 || K < 32 || K % 32 != 0) return 0;
+    const size_t smem = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
+    return smem <= 200 * 1024;
+}
+
+// epilogue: 0 bf16 rows [M, N]; 1 SwiGLU: W holds N gate rows then N up rows, out is [M, N] bf16; 2 fp32 rows.
+// With x_res given the norm prologue runs (delta, x_res_out optional together); otherwise x_bf16 is the input.
+MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* x_bf16,
+                                const float* x_res, const void* delta, float* x_res_out,
+                                const void* gain, int gain_dtype, float eps,
+                                void* out, int ldo, int epilogue, int sm_count, cudaStream_t stream) {
+    MYNAH_REQUIRE(mynah_gemv_decode_supported(M, N, K), "gemv_decode: M=%d N=%d K=%d is not taken by this kernel", M, N, K);
+    MYNAH_REQUIRE((x_res != nullptr) != (x_bf16 != nullptr), "gemv_decode: give either the residual or bf16 input rows");
+    MYNAH_REQUIRE(x_res == nullptr || gain != nullptr, "gemv_decode: the norm prologue needs a gain");
+    MYNAH_REQUIRE((delta == nullptr) == (x_res_out == nullptr), "gemv_decode: delta and the updated residual go together");
+    MYNAH_REQUIRE(epilogue >= 0 && epilogue <= 2 && ldo >= N, "gemv_decode: bad epilogue or output stride");
+    GemvArgs a;
+    a.W = (const bf16*)W; a.N = N; a.K = K; a.M = M;
+    a.x_bf16 = (const bf16*)x_bf16; a.x_res = x_res; a.delta = (const bf16*)delta; a.x_res_out = x_res_out;
+    a.gain = VecRef{gain, gain_dtype}; a.eps = eps; a.out = out; a.ldo = ldo;
+    const int groups = ceil_div(N, 8);
+    const int target = (sm_count > 0 ? sm_count : 148) * 2;          // about two CTAs per SM
+    a.groups_per_cta = groups <= target ? 1 : ceil_div(groups, target);
+    const int n_ctas = ceil_div(groups, a.groups_per_cta);
+    const size_t smem = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
+    const bool norm = x_res != nullptr;
+    switch (epilogue * 2 + (norm ? 1 : 0)) {
+        case 0: return launch<EPI_BF16, false>(a, n_ctas, smem, stream);
+        case 1: return launch<EPI_BF16, true>(a, n_ctas, smem, stream);
+        case 2: return launch<EPI_SWIGLU, false>(a, n_ctas, smem, stream);
+        case 3: return launch<EPI_SWIGLU, true>(a, n_ctas, smem, stream);
+        case 4: return launch<EPI_F32, false>(a, n_ctas, smem, stream);
+        default: return launch<EPI_F32, true>(a, n_ctas, smem, stream);
+    }
+}

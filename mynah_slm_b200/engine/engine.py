@@ -262,7 +262,7 @@ class Engine:
         views = self.cache.views
         for i, e in enumerate(self.model.schedule):
             self.model.layers[e.layer].forward(stream, ctx, views[i])
-        h = self.model.final_norm.apply(stream, rows=want_rows)
+        h = self.model.final_norm.apply(stream, rows=want_rows, lazy=want_rows is None)
         return self.model.head.forward(h)
 
     # ---------------------------------------------------------------- step

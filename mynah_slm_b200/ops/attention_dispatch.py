@@ -11,15 +11,13 @@ import torch
 
 from . import kernels
 
-# Filled by the tensor-core module when it is present: f(...) -> bool (taken).
-TENSOR_CORE_PREFILL = []
-
 
 def prefill(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
             k_cache: torch.Tensor, v_cache: torch.Tensor, pages, window: int) -> None:
-    for route in TENSOR_CORE_PREFILL:
-        if route(qkv, out, ctx, H, KV, HD, k_cache, v_cache, pages, window):
-            return
+    if kernels.attn_prefill_tc_supported(qkv.dtype, H, KV, HD):
+        kernels.attn_prefill_tc(qkv, out, ctx.B, ctx.max_q_len, H, KV, HD, k_cache, v_cache,
+                                ctx.cu_q, ctx.kv_len, pages, window, ctx.status)
+        return
     kernels.attn_prefill_generic(qkv, out, ctx.B, ctx.max_q_len, H, KV, HD, k_cache, v_cache,
                                  ctx.cu_q, ctx.kv_len, pages, window, ctx.status)
 

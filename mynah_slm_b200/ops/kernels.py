@@ -95,17 +95,94 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.T
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+class NormedInput:
+    """A norm that has not been run yet: the residual rows, the pending add and
+    the gain. A matrix product that can compute the norm on its way takes it as
+    it is (`linear`, `linear_swiglu`); anything else calls `materialize`."""
+
+    def __init__(self, stream, delta, gain: torch.Tensor, eps: float, act_dtype: torch.dtype):
+        self.stream, self.delta, self.gain, self.eps, self.act_dtype = stream, delta, gain, float(eps), act_dtype
+        self.shape = stream.x.shape
+        self.dtype = act_dtype
+        self._h: Optional[torch.Tensor] = None
+
+    def materialize(self) -> torch.Tensor:
+        if self._h is None:
+            self._h = rmsnorm(self.stream.x, self.gain, self.eps, self.act_dtype, delta=self.delta)
+            self.delta = None
+        return self._h
+
+
+_SM_COUNT: dict = {}
+
+
+def _sm_count(device) -> int:
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[device]
+
+
+def gemv_decode_supported(M: int, N: int, K: int) -> bool:
+    return bool(lib.load().mynah_gemv_decode_supported(M, N, K))
+
+
+def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
+    """x: bf16 rows [M, K] or a NormedInput. epilogue 0: bf16, 1: SwiGLU (w holds N gate rows then N up rows), 2: fp32."""
+    K = w.shape[1]
+    if isinstance(x, NormedInput) and x._h is None:
+        st = x.stream
+        M = st.x.shape[0]
+        new_x = torch.empty_like(st.x) if x.delta is not None else None
+        call("mynah_gemv_decode", ptr(w), N, K, M, None, ptr(st.x), ptr(x.delta), ptr(new_x),
+             ptr(x.gain), code(x.gain.dtype), x.eps, ptr(out), out.shape[1], epilogue, _sm_count(w.device), stream_ptr())
+        if new_x is not None:
+            st.x = new_x                       # the residual with the add done, written by the kernel
+            x.delta = None
+        return out
+    if isinstance(x, NormedInput):
+        x = x._h
+    call("mynah_gemv_decode", ptr(w), N, K, x.shape[0], ptr(x), None, None, None, None, 0, 0.0,
+         ptr(out), out.shape[1], epilogue, _sm_count(w.device), stream_ptr())
+    return out
+
+
+def _fusable(x, w: torch.Tensor, N: int) -> bool:
+    if w.dtype != torch.bfloat16 or not w.is_contiguous():
+        return False
+    if isinstance(x, NormedInput):
+        if x.act_dtype != torch.bfloat16:
+            return False
+        M, K = x.shape
+        if x._h is None and (x.gain.numel() != K or not x.stream.x.is_contiguous()):
+            return False
+    else:
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            return False
+        M, K = x.shape
+    return K == w.shape[1] and gemv_decode_supported(M, N, K)
+
+
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x . w^T with w [out, in] row-major (no bias). float32 runs the
-    package's FFMA kernel (true 32-bit); bfloat16 accumulates in fp32."""
-    _chk(x, "linear input", dim=2)
+    package's FFMA kernel (true 32-bit); bfloat16 accumulates in fp32. `x` may
+    be a NormedInput: a few bf16 rows then take the fused norm+product kernel."""
     _chk(w, "linear weight", dim=2)
+    out_dtype = out_dtype or (x.dtype if not isinstance(x, NormedInput) else x.act_dtype)
+    N = w.shape[0]
+    if out_dtype in (torch.bfloat16, torch.float32) and _fusable(x, w, N):
+        if out is None:
+            out = torch.empty((x.shape[0], N), dtype=out_dtype, device=w.device)
+        from . import gemm_bf16
+        gemm_bf16.counters["own"] += 1
+        return _gemv_decode(x, w, N, 0 if out_dtype == torch.bfloat16 else 2, out)
+    if isinstance(x, NormedInput):
+        x = x.materialize()
+    _chk(x, "linear input", dim=2)
     M, K = x.shape
     N, K2 = w.shape
     if K != K2 or x.dtype != w.dtype:
         raise KernelError(f"linear: input [{M},{K}] {x.dtype} does not fit weight [{N},{K2}] {w.dtype}")
-    out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32:
         if out_dtype != torch.float32:
             raise KernelError("linear: the 32-bit path writes float32")
@@ -117,6 +194,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
     from . import gemm_bf16
     return gemm_bf16.linear_bf16(x, w, out_dtype, out)
+
+
+def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) with w_gate_up = [Wg; Wu] ([2F, K]); one kernel for a few bf16 rows."""
+    F = w_gate_up.shape[0] // 2
+    if _fusable(x, w_gate_up, F):
+        out = torch.empty((x.shape[0], F), dtype=torch.bfloat16, device=w_gate_up.device)
+        from . import gemm_bf16
+        gemm_bf16.counters["own"] += 1
+        return _gemv_decode(x, w_gate_up, F, 1, out)
+    return swiglu(linear(x, w_gate_up))
 
 
 def rope_table(n_pos: int, rotary_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
@@ -171,6 +259,21 @@ def attn_prefill_generic(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len
     _chk(out, "attention output", qkv.dtype, 2)
     call("mynah_attn_prefill_generic", ptr(qkv), ptr(out), code(qkv.dtype), B, max_q_len, H, KV, HD,
          qkv.shape[1], out.shape[1], ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
+
+
+def attn_prefill_tc_supported(dtype: torch.dtype, H: int, KV: int, HD: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib.load().mynah_attn_prefill_tc_supported(H, KV, HD))
+
+
+def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len: int, H: int, KV: int, HD: int,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                    pages: PageTableView, window: int, status: torch.Tensor) -> None:
+    """The tensor-core prompt attention (bfloat16, head_dim 64 or 128); same contract as attn_prefill_generic."""
+    _chk(qkv, "q", torch.bfloat16, 2)
+    _chk(out, "attention output", torch.bfloat16, 2)
+    call("mynah_attn_prefill_tc", ptr(qkv), ptr(out), B, max_q_len, H, KV, HD, qkv.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
 
 

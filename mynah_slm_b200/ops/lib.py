@@ -46,10 +46,15 @@ _SIGNATURES: dict[str, list] = {
                           P, P, P,
                           P, P, P, c_int,
                           c_int, c_int, P, P, P],
+    "mynah_attn_prefill_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              P, P, P, P,
+                              P, P, P, c_int,
+                              c_int, P, P],
     "mynah_attn_decode_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                              P, P, P,
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
+    "mynah_gemv_decode": [P, c_int, c_int, c_int, P, P, P, P, P, c_int, c_float, P, c_int, c_int, c_int, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
@@ -78,6 +83,10 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_attn_decode_tc_supported.restype = c_int
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_attn_prefill_tc_supported.restype = c_int
+    lib.mynah_attn_prefill_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_gemv_decode_supported.restype = c_int
+    lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)

@@ -29,6 +29,8 @@ from .base import (CacheView, KVRequest, Mixer, TensorSpec, build_part, register
 
 
 class GQAttention(Mixer):
+    accepts_normed = True        # its first product can compute the norm on its way
+
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.D = int(spec["hidden_size"])

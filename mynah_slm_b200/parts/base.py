@@ -100,9 +100,13 @@ class Part:
 
 
 class Norm(Part):
-    def apply(self, stream: "Residual", rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def apply(self, stream: "Residual", rows: Optional[torch.Tensor] = None, lazy: bool = False):
         """Fold the stream's pending delta in and return the normalised rows
-        (all of them, or those that `rows` selects) in the activation type."""
+        (all of them, or those that `rows` selects) in the activation type.
+        With `lazy` a norm may return an object that stands for its result
+        (with `.shape` and `.materialize()`), for a consumer that can compute
+        the norm on its way; a part says that it can take one with
+        `accepts_normed = True`."""
         raise NotImplementedError
 
 

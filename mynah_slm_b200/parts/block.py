@@ -20,9 +20,9 @@ class PreNormResidual(Block):
                 raise ConfigError(f"prenorm_residual: the layer gives no {need!r} norm")
 
     def forward(self, stream: Residual, ctx, cache: CacheView) -> None:
-        h = self.norms["mixer"].apply(stream)
+        h = self.norms["mixer"].apply(stream, lazy=getattr(self.mixer, "accepts_normed", False))
         stream.add(self.mixer.forward(h, ctx, cache))
-        h = self.norms["ffn"].apply(stream)
+        h = self.norms["ffn"].apply(stream, lazy=getattr(self.ffn, "accepts_normed", False))
         stream.add(self.ffn.forward(h, ctx))
 
 

@@ -18,6 +18,8 @@ from .base import FeedForward, TensorSpec, register_ffn
 
 
 class SwiGLUDense(FeedForward):
+    accepts_normed = True        # its first product can compute the norm on its way
+
     def __init__(self, spec):
         super().__init__(spec)
         self.D = int(spec["hidden_size"])
@@ -40,8 +42,7 @@ class SwiGLUDense(FeedForward):
         self.w_down = tensors[p + "down_proj.weight"]
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        gate_up = kernels.linear(h, self.w_gate_up)
-        return kernels.linear(kernels.swiglu(gate_up), self.w_down)
+        return kernels.linear(kernels.linear_swiglu(h, self.w_gate_up), self.w_down)
 
 
 register_ffn("swiglu_dense", SwiGLUDense)

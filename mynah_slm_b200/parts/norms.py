@@ -31,8 +31,10 @@ class RMSNorm(Norm):
         self.gain = tensors[self.name]
         self.act_dtype = runtime.act_dtype
 
-    def apply(self, stream: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def apply(self, stream: Residual, rows: Optional[torch.Tensor] = None, lazy: bool = False):
         delta, stream.pending = stream.pending, None
+        if lazy and rows is None:
+            return kernels.NormedInput(stream, delta, self.gain, self.eps, self.act_dtype)
         return kernels.rmsnorm(stream.x, self.gain, self.eps, self.act_dtype, delta=delta, rows=rows)
 
 

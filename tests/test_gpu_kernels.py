@@ -492,3 +492,133 @@ def test_attn_decode_tensor_cores_one_far_key():
         assert (np.abs(got - vv[target, 1]).max() < 0.05) == visible, (window, target)
         ref = gqa_attention(q, kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
         assert rel_err(ref.reshape(1, -1), out.float().cpu().numpy()) < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 151936, 1024), (2, 20, 64)])
+def test_gemv_decode_fused_kernels(M, N, K):
+    """The decode products with their fusions: plain rows, fp32 rows, the norm
+    prologue with the residual add, and the SwiGLU epilogue."""
+    from mynah_slm_b200.parts.base import Residual
+    k = _k()
+    assert k.gemv_decode_supported(M, N, K) and not k.gemv_decode_supported(17, N, K) and not k.gemv_decode_supported(M, N, 80)
+    rng = np.random.default_rng(17)
+    w = _round(rng.standard_normal((N, K)) * 0.05, "bf16")
+    x = _round(rng.standard_normal((M, K)), "bf16")
+    wd = torch.from_numpy(w).to(torch.bfloat16).to(DEV)
+    xd = torch.from_numpy(x).to(torch.bfloat16).to(DEV)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    got = k.linear(xd, wd)
+    assert got.dtype == torch.bfloat16 and rel_err(ref, got.float().cpu().numpy()) < 6e-3
+    got32 = k.linear(xd, wd, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32 and rel_err(ref, got32.cpu().numpy()) < 2e-5      # fp32 accumulation of bf16 products
+    # a row's result does not depend on the other rows of the batch
+    one = k.linear(xd[M - 1:M].contiguous(), wd, out_dtype=torch.float32)
+    assert torch.equal(one[0], got32[M - 1])
+    # norm prologue: residual + pending add -> norm -> product; the residual comes back updated
+    res = (rng.standard_normal((M, K)) * 3).astype(np.float32)
+    delta = _round(rng.standard_normal((M, K)), "bf16")
+    gain = _round(1 + 0.1 * rng.standard_normal(K), "bf16")
+    eps = 1e-5
+    h_ref = _round(rms_norm(res + delta, gain, eps), "bf16")
+    stream = Residual(torch.from_numpy(res.copy()).to(DEV))
+    normed = k.NormedInput(stream, torch.from_numpy(delta).to(torch.bfloat16).to(DEV),
+                           torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps, torch.bfloat16)
+    old_x = stream.x
+    got = k.linear(normed, wd, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(h_ref.astype(np.float64) @ w.astype(np.float64).T, got) < 5e-3      # h may round the other way here and there
+    assert stream.x is not old_x and np.array_equal(stream.x.cpu().numpy(), res + delta)
+    assert np.array_equal(old_x.cpu().numpy(), res)                                     # the input rows are left alone
+    # the same through the separate norm kernel gives the same rounding points
+    h_dev = k.rmsnorm(torch.from_numpy(res.copy()).to(DEV), torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps,
+                      torch.bfloat16, delta=torch.from_numpy(delta).to(torch.bfloat16).to(DEV))
+    sep = k.linear(h_dev, wd, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(sep, got) < 5e-3
+    # SwiGLU epilogue: N gate rows then N up rows
+    if N % 2 == 0 and N <= 4096:
+        F = N // 2
+        act = k.linear_swiglu(xd, wd).float().cpu().numpy()
+        gu = _round(ref, "bf16")
+        assert act.shape == (M, F) and rel_err(plain_swiglu(gu[:, :F], gu[:, F:]), act) < 1.5e-2
+
+
+def test_fused_decode_path_equals_the_unfused_one(tmp_path):
+    """A decode step through the fused kernels (a few rows) against the same
+    step through the library product and the separate norm and activation
+    kernels (forced by a batch of more than 16 rows is not needed: the fused
+    path is switched off instead)."""
+    from helpers import make_folder, prompts_for
+    from mynah_slm_b200.engine.engine import Engine, StepEntry
+    from mynah_slm_b200.ops import kernels
+    folder = make_folder(tmp_path, "B", torch.bfloat16)
+    p = prompts_for("B", [40, 7, 70], seed=19)
+    outs = []
+    for fused in (True, False):
+        saved = kernels.gemv_decode_supported
+        if not fused:
+            kernels.gemv_decode_supported = lambda M, N, K: False
+        try:
+            eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=512, use_graphs=False)
+            slots = [eng.open_sequence() for _ in p]
+            eng.step([StepEntry(s, q, ()) for s, q in zip(slots, p)])
+            rows = [eng.step([StepEntry(s, [q[t]], (0,)) for s, q in zip(slots, p)]).cpu().numpy() for t in range(3)]
+            eng.check_status()
+            outs.append(np.concatenate(rows))
+        finally:
+            kernels.gemv_decode_supported = saved
+    assert rel_err(outs[1], outs[0]) < 1e-2
+
+
+@pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (4, 1, 64, 0), (6, 2, 128, 100), (8, 8, 64, 33)])
+def test_attn_prefill_tensor_cores(H, KV, HD, window):
+    """The tensor-core prompt kernel against the plain attention: a ragged
+    batch, prompts that continue earlier ones, a window, NaN in unused page tails."""
+    k = _k()
+    assert k.attn_prefill_tc_supported(torch.bfloat16, H, KV, HD) and not k.attn_prefill_tc_supported(torch.bfloat16, 4, 2, 48)
+    rng = np.random.default_rng(18)
+    lens_q, past = [7, 1, 130, 70, 64, 200], [0, 0, 100, 64, 0, 313]
+    seqs = _attn_case(rng, lens_q, past, H, KV, HD, "bf16")
+    n_pages = sum(-(-(p + n) // 64) for p, n in zip(past, lens_q)) + 3
+    free = list(np.random.default_rng(20).permutation(n_pages))
+    kc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lists = []
+    for q, kk, vv in seqs:
+        pages = [int(free.pop()) for _ in range(-(-kk.shape[0] // 64))]
+        lists.append(pages)
+        kt, vt = torch.from_numpy(kk).to(torch.bfloat16).to(DEV), torch.from_numpy(vv).to(torch.bfloat16).to(DEV)
+        for i, pg in enumerate(pages):
+            n = min(64, kk.shape[0] - 64 * i)
+            kc[pg, :, :n] = kt[64 * i:64 * i + n].transpose(0, 1)
+            vc[pg, :, :n] = vt[64 * i:64 * i + n].transpose(0, 1)
+    pt = _page_table(lists)(n_pages)
+    T = sum(lens_q)
+    qkv = torch.from_numpy(np.concatenate([s[0].reshape(s[0].shape[0], -1) for s in seqs])).to(torch.bfloat16).to(DEV)
+    out = torch.zeros((T, H * HD), dtype=torch.bfloat16, device=DEV)
+    cu = torch.tensor(np.cumsum([0] + lens_q), dtype=torch.int32, device=DEV)
+    kvl = torch.tensor([p + n for p, n in zip(past, lens_q)], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.attn_prefill_tc(qkv, out, len(seqs), max(lens_q), H, KV, HD, kc, vc, cu, kvl, pt, window, status)
+    assert status.item() == 0
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    row = 0
+    for (q, kk, vv), nq, p in zip(seqs, lens_q, past):
+        ref = gqa_attention(q, kk, vv, window=window or None, q_pos=np.arange(p, p + nq), k_pos=np.arange(p + nq))
+        assert rel_err(ref.reshape(nq, -1), got[row:row + nq]) < 1e-2, (nq, p)
+        row += nq
+    # one far key, at a page's first position and on both sides of the window's edge
+    n, HDk = 400, HD
+    for win, target, visible in [(0, 3, True), (0, 64, True), (120, 280, True), (120, 279, False)]:
+        kk = _round(rng.standard_normal((n, KV, HDk)) * 0.1, "bf16")
+        vv = _round(rng.standard_normal((n, KV, HDk)), "bf16")
+        q = _round(rng.standard_normal((2, H, HDk)) * 0.1, "bf16")       # queries at positions n-2 and n-1
+        kk[target, 0] = _round(q[1, 0] / np.linalg.norm(q[1, 0]) * 60.0, "bf16")
+        q[1, 0] = _round(q[1, 0] * 16, "bf16")
+        lst = [[6, 0, 5, 1, 4, 2, 3]]
+        kc2, vc2 = _paged(kk, lst[0], 7, "bf16"), _paged(vv, lst[0], 7, "bf16")
+        o2 = torch.zeros((2, H * HDk), dtype=torch.bfloat16, device=DEV)
+        k.attn_prefill_tc(torch.from_numpy(q.reshape(2, -1)).to(torch.bfloat16).to(DEV), o2, 1, 2, H, KV, HDk, kc2, vc2,
+                          torch.tensor([0, 2], dtype=torch.int32, device=DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
+                          _page_table(lst)(7), win, status)
+        hit = np.abs(o2.float().cpu().numpy()[1, :HDk] - vv[target, 0]).max() < 0.05
+        assert hit == visible, (win, target)
