@@ -73,6 +73,8 @@ attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
     const int G = a.H / a.KV;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    griddep_launch();
+    griddep_wait();
     const int hi = kv_len[b];
     const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
     int key_begin = 0, key_end = 0, page = -1;
@@ -256,6 +258,8 @@ __global__ void attn_decode_combine_fast_kernel(const float* __restrict__ part_o
     __shared__ float inv_s;
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t row0 = ((size_t)b * H + h) * S_max;
+    griddep_wait();
+    griddep_launch();
     const int hi = kv_len[b];
     const int lo = window > 0 ? max(0, hi - window) : 0;
     const int S = hi > 0 ? min(S_max, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
@@ -313,14 +317,14 @@ MYNAH_API int mynah_attn_decode_tc(
     float* part_ml = scratch + (size_t)B * H * n_splits * HD;
     const dim3 grid(n_splits, KV, B);
     if (HD == 128)
-        attn_decode_tc_kernel<128><<<grid, WARPS * 32, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+        mynah_launch(attn_decode_tc_kernel<128>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                                     kv_len, pt, a, part_o, part_ml, status);
     else
-        attn_decode_tc_kernel<64><<<grid, WARPS * 32, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+        mynah_launch(attn_decode_tc_kernel<64>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                                    kv_len, pt, a, part_o, part_ml, status);
     if (mynah_check_launch("attn_decode_tc")) return -1;
     const int threads = HD >= 128 ? 128 : 64;
-    attn_decode_combine_fast_kernel<bf16><<<dim3(H, B), threads, n_splits * sizeof(float), stream>>>(
+    mynah_launch(attn_decode_combine_fast_kernel<bf16>, dim3(H, B), dim3(threads), n_splits * sizeof(float), stream,
         part_o, part_ml, (bf16*)out, kv_len, window, H, HD, n_splits, ldo);
     return mynah_check_launch("attn_decode_combine");
 }

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <utility>
 
 #define MYNAH_API extern "C" __attribute__((visibility("default")))
 
@@ -98,6 +99,34 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
         w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Programmatic dependent launch: a kernel launched with the attribute may
+// start while the kernel before it on the stream is still running. Until its
+// griddep_wait() returns it may touch only memory no kernel writes (weights,
+// lookup tables); after it, everything the earlier kernels wrote is visible.
+// griddep_launch() lets the next kernel begin its own preamble. Both are
+// no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1: launch the decode-path kernels with the programmatic-serialization attribute.
+int mynah_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mynah_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = mynah_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

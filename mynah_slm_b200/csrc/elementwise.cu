@@ -11,6 +11,8 @@
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ x, int D, int V) {
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* out = x + (size_t)t * D;
@@ -28,9 +30,9 @@ MYNAH_API int mynah_embed_gather(const void* table, int table_dtype, const int* 
     MYNAH_REQUIRE(T > 0 && D > 0 && V > 0, "embed_gather: bad sizes T=%d D=%d V=%d", T, D, V);
     const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
     if (table_dtype == MYNAH_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, x, D, V);
+        mynah_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, x, D, V);
     else if (table_dtype == MYNAH_BF16)
-        embed_gather_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)table, tokens, x, D, V);
+        mynah_launch(embed_gather_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, tokens, x, D, V);
     else
         return mynah_fail("embed_gather: unsupported table dtype %d", table_dtype);
     return mynah_check_launch("embed_gather");
@@ -46,6 +48,8 @@ template <typename TA>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
                                const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
     __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + (size_t)r * D;
     const TA* dr = delta ? delta + (size_t)r * D : nullptr;
@@ -72,9 +76,9 @@ MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dt
     const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 32));
     const VecRef wr{w, w_dtype};
     if (act_dtype == MYNAH_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, (const float*)delta, wr, rows, (float*)out, D, eps);
+        mynah_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
     else if (act_dtype == MYNAH_BF16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+        mynah_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
     else
         return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("rmsnorm");
@@ -83,6 +87,8 @@ MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dt
 // ----------------------------------------------------------- residual add
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+    griddep_launch();
+    griddep_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) x[i] += to_f32(delta[i]);          // mynah-slm src/kernels.c:222-224
 }
@@ -91,9 +97,9 @@ MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, lon
     if (n == 0) return 0;
     const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
     if (act_dtype == MYNAH_F32)
-        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+        mynah_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n);
     else if (act_dtype == MYNAH_BF16)
-        residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n);
+        mynah_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n);
     else
         return mynah_fail("residual_add: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("residual_add");
@@ -111,6 +117,8 @@ __device__ __forceinline__ float stable_sigmoid(float v) {
 
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, int F) {
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x;
     const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= F) return;
@@ -125,9 +133,9 @@ MYNAH_API int mynah_swiglu(const void* gate_up, void* out, int act_dtype, int T,
     MYNAH_REQUIRE(ceil_div(F, 256) <= 65535, "swiglu: width %d exceeds one launch", F);
     const dim3 grid(T, ceil_div(F, 256));
     if (act_dtype == MYNAH_F32)
-        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, (float*)out, F);
+        mynah_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gate_up, (float*)out, F);
     else if (act_dtype == MYNAH_BF16)
-        swiglu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, F);
+        mynah_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, F);
     else
         return mynah_fail("swiglu: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("swiglu");

@@ -33,3 +33,12 @@ MYNAH_API int mynah_device_arch(void) {
     cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
     return major * 10 + minor;
 }
+
+// Programmatic dependent launch of the decode-path kernels. Off by default: on this part the decode step
+// measured slower with it (dependents that become resident early take slots from the running kernel).
+static int g_pdl = 0;
+int mynah_pdl_enabled() { return g_pdl; }
+MYNAH_API int mynah_set_pdl(int on) {
+    g_pdl = on ? 1 : 0;
+    return 0;
+}

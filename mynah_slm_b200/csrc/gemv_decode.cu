@@ -69,28 +69,66 @@ gemv_decode_kernel(GemvArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int rows_x = M > 8 ? 16 : 8;
+    const int nkb = K / 32;                                          // blocks of 32 k
+
+    // ---- the first weights of this CTA, before anything an earlier kernel wrote is touched: the
+    // weights are never written, so their loads may run while the kernel before this one finishes
+    uint4 wv[4], uv[4];
+    auto load_weights = [&](int n0, int kb0) {
+        const int row = n0 + g;
+        const bool row_ok = row < a.N;
+        const bf16* w_gate = a.W + (size_t)(row_ok ? row : 0) * K;
+        const bf16* w_up = EPI == EPI_SWIGLU ? a.W + (size_t)((row_ok ? row : 0) + a.N) * K : nullptr;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {                                // up to 8 x 16 bytes in flight per lane
+            const int kb = kb0 + u * WARPS;
+            const bool ok = kb < nkb && row_ok;
+            wv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_gate + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+            if (EPI == EPI_SWIGLU)
+                uv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_up + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    const int n_first = blockIdx.x * a.groups_per_cta * 8;
+    griddep_launch();
+    load_weights(n_first, warp);
+    griddep_wait();
 
     // ---- the input rows, in bf16, into shared memory
     if (NORM) {
-        for (int m = warp; m < M; m += WARPS) {                      // one warp per row, rows in parallel
-            const float* xr = a.x_res + (size_t)m * K;
-            const bf16* dr = a.delta ? a.delta + (size_t)m * K : nullptr;
+        // teams of warps share a row: all 8 warps on one row when M = 1, one warp per row from M = 8 on
+        __shared__ float part[WARPS];
+        int mp = 1;
+        while (mp < M && mp < WARPS) mp <<= 1;
+        const int wpr = WARPS / mp;                                  // warps per row
+        const int sub = warp % wpr;                                  // this warp's place in its team
+        for (int m0 = 0; m0 < M; m0 += mp) {
+            const int m = m0 + warp / wpr;
+            const bool on = m < M;
+            const float* xr = a.x_res + (size_t)(on ? m : 0) * K;
+            const bf16* dr = a.delta ? a.delta + (size_t)(on ? m : 0) * K : nullptr;
             float ss = 0.f;
-            for (int i = lane; i < K; i += 32) {
-                float v = xr[i];
-                if (dr) v += to_f32(dr[i]);
-                ss += v * v;
-            }
-            ss = warp_sum(ss);
-            const float s = 1.0f / sqrtf(ss / (float)K + a.eps);
-            for (int i = lane; i < K; i += 32) {
-                float v = xr[i];
-                if (dr) {
-                    v += to_f32(dr[i]);
-                    if (blockIdx.x == 0) a.x_res_out[(size_t)m * K + i] = v;
+            if (on)
+                for (int i = sub * 32 + lane; i < K; i += wpr * 32) {
+                    float v = xr[i];
+                    if (dr) v += to_f32(dr[i]);
+                    ss += v * v;
                 }
-                xs[m * ldx + i] = __float2bfloat16_rn((v * s) * a.gain.at(i));
-            }
+            ss = warp_sum(ss);
+            __syncthreads();
+            if (lane == 0) part[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (int w = 0; w < wpr; w++) tot += part[(warp / wpr) * wpr + w];   // fixed order
+            const float s = 1.0f / sqrtf(tot / (float)K + a.eps);
+            if (on)
+                for (int i = sub * 32 + lane; i < K; i += wpr * 32) {
+                    float v = xr[i];
+                    if (dr) {
+                        v += to_f32(dr[i]);
+                        if (blockIdx.x == 0) a.x_res_out[(size_t)m * K + i] = v;
+                    }
+                    xs[m * ldx + i] = __float2bfloat16_rn((v * s) * a.gain.at(i));
+                }
         }
     } else {
         for (int i = tid; i < M * (K / 8); i += THREADS) {
@@ -104,25 +142,12 @@ gemv_decode_kernel(GemvArgs a) {
     }
     __syncthreads();
 
-    const int nkb = K / 32;                                          // blocks of 32 k
     for (int gi = 0; gi < a.groups_per_cta; gi++) {
         const int n0 = (blockIdx.x * a.groups_per_cta + gi) * 8;
         if (n0 >= a.N) break;                                        // uniform over the CTA
-        const int row = n0 + g;                                      // this lane's weight row (as B column g)
-        const bool row_ok = row < a.N;
-        const bf16* w_gate = a.W + (size_t)(row_ok ? row : 0) * K;
-        const bf16* w_up = EPI == EPI_SWIGLU ? a.W + (size_t)((row_ok ? row : 0) + a.N) * K : nullptr;
         float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
         for (int kb0 = warp; kb0 < nkb; kb0 += WARPS * 4) {
-            uint4 wv[4], uv[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {                            // loads first: up to 8 x 16 bytes in flight per lane
-                const int kb = kb0 + u * WARPS;
-                const bool ok = kb < nkb && row_ok;
-                wv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_gate + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
-                if (EPI == EPI_SWIGLU)
-                    uv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_up + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
-            }
+            if (gi != 0 || kb0 != warp) load_weights(n0, kb0);       // the first batch is already here
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const int kb = kb0 + u * WARPS;
@@ -195,7 +220,7 @@ int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
         if (e != cudaSuccess) return mynah_fail("gemv_decode: %s", cudaGetErrorString(e));
         allowed = (int)smem;
     }
-    kern<<<n_ctas, THREADS, smem, stream>>>(a);
+    mynah_launch(kern, dim3(n_ctas), dim3(THREADS), smem, stream, a);
     return mynah_check_launch("gemv_decode");
 }
 

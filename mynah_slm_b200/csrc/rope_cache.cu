@@ -45,6 +45,8 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                           PageTable pt, TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                           QkvArgs a, int* __restrict__ status) {
     __shared__ float stage[WARPS][MAX_HEAD_DIM];
+    griddep_wait();
+    griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = k_cache != nullptr ? a.H + 2 * a.KV : a.H;   // without storage only q is touched
     const long long unit = (long long)blockIdx.x * WARPS + warp;
@@ -149,10 +151,10 @@ MYNAH_API int mynah_qk_norm_rope_store(
     const long long units = (long long)T * heads;
     const unsigned blocks = (unsigned)ceil_div_ll(units, WARPS);
     if (dtype == MYNAH_F32)
-        qk_norm_rope_store_kernel<float, float><<<blocks, WARPS * 32, 0, stream>>>(
+        mynah_launch(qk_norm_rope_store_kernel<float, float>, dim3(blocks), dim3(WARPS * 32), 0, stream,
             (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status);
     else if (dtype == MYNAH_BF16)
-        qk_norm_rope_store_kernel<bf16, bf16><<<blocks, WARPS * 32, 0, stream>>>(
+        mynah_launch(qk_norm_rope_store_kernel<bf16, bf16>, dim3(blocks), dim3(WARPS * 32), 0, stream,
             (bf16*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status);
     else
         return mynah_fail("qk_norm_rope_store: unsupported dtype %d", dtype);

@@ -268,6 +268,8 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict__ params,
               unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out) {
     __shared__ Shared sh;
+    griddep_launch();
+    griddep_wait();
     const SampleParams sp{params[0], params[1], params[2], (int)params[3]};
     const int b = blockIdx.x;
     float* row = logits + (size_t)b * ld;
@@ -353,6 +355,8 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
 __global__ void penalties_kernel(float* __restrict__ logits, int B, int V, int ld, const int* __restrict__ ring,
                                  const int* __restrict__ ring_n, int stride, const int* __restrict__ slots,
                                  const float* __restrict__ params) {
+    griddep_launch();
+    griddep_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const float repeat = params[4], freq = params[5], presence = params[6];
@@ -380,6 +384,8 @@ __global__ void penalties_kernel(float* __restrict__ logits, int B, int V, int l
 __global__ void accept_kernel(const int* __restrict__ tokens, int B, int* __restrict__ ring, int* __restrict__ ring_n,
                               int* __restrict__ ring_head, int stride, const int* __restrict__ slots,
                               const float* __restrict__ params) {
+    griddep_launch();
+    griddep_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     const int window = min((int)params[7], stride);
     if (b >= B || window <= 0) return;
@@ -394,6 +400,8 @@ __global__ void accept_kernel(const int* __restrict__ tokens, int B, int* __rest
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out) {
     __shared__ Shared sh;
+    griddep_launch();
+    griddep_wait();
     float mx;
     const int best = block_argmax(logits + (size_t)blockIdx.x * ld, V, sh, &mx);
     if (threadIdx.x == 0) out[blockIdx.x] = best;
@@ -404,7 +412,7 @@ argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__
 MYNAH_API int mynah_argmax(const float* logits, int B, int V, int ld, int* out, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && V > 0 && ld >= V, "argmax: bad sizes B=%d V=%d ld=%d", B, V, ld);
-    argmax_kernel<<<B, THREADS, 0, stream>>>(logits, V, ld, out);
+    mynah_launch(argmax_kernel, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, out);
     return mynah_check_launch("argmax");
 }
 
@@ -418,14 +426,14 @@ MYNAH_API int mynah_sample(float* logits, int B, int V, int ld, const float* par
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && V > 0 && ld >= V, "sample: bad sizes B=%d V=%d ld=%d", B, V, ld);
     MYNAH_REQUIRE(params != nullptr && rng != nullptr, "sample: parameters and generator states are required");
-    sample_kernel<<<B, THREADS, 0, stream>>>(logits, V, ld, params, rng, slots, out);
+    mynah_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out);
     return mynah_check_launch("sample");
 }
 
 MYNAH_API int mynah_apply_penalties(float* logits, int B, int V, int ld, const int* ring, const int* ring_n,
                                     int window, const int* slots, const float* params, cudaStream_t stream) {
     if (B == 0 || window == 0) return 0;
-    penalties_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(logits, B, V, ld, ring, ring_n, window, slots, params);
+    mynah_launch(penalties_kernel, dim3(ceil_div(B, 64)), dim3(64), 0, stream, logits, B, V, ld, ring, ring_n, window, slots, params);
     return mynah_check_launch("apply_penalties");
 }
 
@@ -435,6 +443,8 @@ namespace {
 __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __restrict__ sampled,
                                       int* __restrict__ tok_pos, int* __restrict__ kv_len,
                                       const int* __restrict__ slots, int B) {
+    griddep_launch();
+    griddep_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B || slots[b] < 0) return;
     tokens[b] = sampled[b];
@@ -446,13 +456,13 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, const int* __res
 MYNAH_API int mynah_decode_advance(int* tokens, const int* sampled, int* tok_pos, int* kv_len, const int* slots,
                                    int B, cudaStream_t stream) {
     if (B == 0) return 0;
-    decode_advance_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(tokens, sampled, tok_pos, kv_len, slots, B);
+    mynah_launch(decode_advance_kernel, dim3(ceil_div(B, 64)), dim3(64), 0, stream, tokens, sampled, tok_pos, kv_len, slots, B);
     return mynah_check_launch("decode_advance");
 }
 
 MYNAH_API int mynah_sampler_accept(const int* tokens, int B, int* ring, int* ring_n, int* ring_head, int window,
                                    const int* slots, const float* params, cudaStream_t stream) {
     if (B == 0 || window == 0) return 0;
-    accept_kernel<<<ceil_div(B, 64), 64, 0, stream>>>(tokens, B, ring, ring_n, ring_head, window, slots, params);
+    mynah_launch(accept_kernel, dim3(ceil_div(B, 64)), dim3(64), 0, stream, tokens, B, ring, ring_n, ring_head, window, slots, params);
     return mynah_check_launch("sampler_accept");
 }

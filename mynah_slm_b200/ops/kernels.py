@@ -129,6 +129,8 @@ def gemv_decode_supported(M: int, N: int, K: int) -> bool:
 def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """x: bf16 rows [M, K] or a NormedInput. epilogue 0: bf16, 1: SwiGLU (w holds N gate rows then N up rows), 2: fp32."""
     K = w.shape[1]
+    if isinstance(x, NormedInput) and x._h is None and x.shape[0] > FUSED_NORM_MAX_ROWS:
+        x.materialize()
     if isinstance(x, NormedInput) and x._h is None:
         st = x.stream
         M = st.x.shape[0]
@@ -159,7 +161,11 @@ def _fusable(x, w: torch.Tensor, N: int) -> bool:
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             return False
         M, K = x.shape
-    return K == w.shape[1] and gemv_decode_supported(M, N, K)
+    return K == w.shape[1] and N <= GEMV_MAX_OUT_ROWS and gemv_decode_supported(M, N, K)
+
+
+FUSED_NORM_MAX_ROWS = 2     # beyond this every CTA recomputing the norm costs more than a separate kernel
+GEMV_MAX_OUT_ROWS = 32768   # wider products (the output head) stream better through the library for now
 
 
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

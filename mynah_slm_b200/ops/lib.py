@@ -56,6 +56,7 @@ _SIGNATURES: dict[str, list] = {
                              c_int, c_int, P, P, P],
     "mynah_gemv_decode": [P, c_int, c_int, c_int, P, P, P, P, P, c_int, c_float, P, c_int, c_int, c_int, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
+    "mynah_set_pdl": [c_int],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
     "mynah_decode_advance": [P, P, P, P, P, c_int, P],
@@ -97,6 +98,9 @@ def load() -> ctypes.CDLL:
     arch = lib.mynah_device_arch()
     if arch != 100:
         raise KernelLibraryError(f"the kernels are built for sm_100a only; the current device reports sm_{arch}")
+    import os
+    if os.environ.get("MYNAH_PDL", "0") == "1":        # programmatic dependent launch of the decode kernels
+        lib.mynah_set_pdl(1)
     _lib = lib
     return lib
 

@@ -494,7 +494,7 @@ def test_attn_decode_tensor_cores_one_far_key():
         assert rel_err(ref.reshape(1, -1), out.float().cpu().numpy()) < 2e-2
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 151936, 1024), (2, 20, 64)])
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 30000, 1024), (2, 20, 64)])
 def test_gemv_decode_fused_kernels(M, N, K):
     """The decode products with their fusions: plain rows, fp32 rows, the norm
     prologue with the residual add, and the SwiGLU epilogue."""
@@ -526,8 +526,9 @@ def test_gemv_decode_fused_kernels(M, N, K):
     old_x = stream.x
     got = k.linear(normed, wd, out_dtype=torch.float32).cpu().numpy()
     assert rel_err(h_ref.astype(np.float64) @ w.astype(np.float64).T, got) < 5e-3      # h may round the other way here and there
-    assert stream.x is not old_x and np.array_equal(stream.x.cpu().numpy(), res + delta)
-    assert np.array_equal(old_x.cpu().numpy(), res)                                     # the input rows are left alone
+    assert np.array_equal(stream.x.cpu().numpy(), res + delta)
+    if M <= k.FUSED_NORM_MAX_ROWS:                 # fused: the updated residual is a new buffer, the input rows are left alone
+        assert stream.x is not old_x and np.array_equal(old_x.cpu().numpy(), res)
     # the same through the separate norm kernel gives the same rounding points
     h_dev = k.rmsnorm(torch.from_numpy(res.copy()).to(DEV), torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps,
                       torch.bfloat16, delta=torch.from_numpy(delta).to(torch.bfloat16).to(DEV))
