@@ -68,13 +68,56 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ del
     for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TA>((xr[i] * s) * w.at(i));
 }
 
+// The same norm with the row kept in registers: four consecutive elements per thread, one pass over
+// memory. Taken when D is a multiple of 4 and fits (D <= 4 * 1024).
+template <typename TA>
+__global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
+                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+    __shared__ float red[32];
+    griddep_launch();
+    griddep_wait();
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = x + (size_t)r * D;
+    const int i = threadIdx.x * 4;
+    const bool on = i < D;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) {
+        v = *reinterpret_cast<const float4*>(xr + i);
+        if (delta) {
+            const TA* dr = delta + (size_t)r * D + i;
+            v.x += to_f32(dr[0]); v.y += to_f32(dr[1]); v.z += to_f32(dr[2]); v.w += to_f32(dr[3]);
+            *reinterpret_cast<float4*>(xr + i) = v;
+        }
+    }
+    float ss = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)D + eps);
+    if (on) {
+        TA* o = out + (size_t)blockIdx.x * D + i;
+        o[0] = from_f32<TA>((v.x * s) * w.at(i));
+        o[1] = from_f32<TA>((v.y * s) * w.at(i + 1));
+        o[2] = from_f32<TA>((v.z * s) * w.at(i + 2));
+        o[3] = from_f32<TA>((v.w * s) * w.at(i + 3));
+    }
+}
+
 MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, const int* rows,
                             void* out, int act_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     MYNAH_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: bad sizes rows=%d D=%d", n_rows, D);
     MYNAH_REQUIRE(w_dtype == MYNAH_F32 || w_dtype == MYNAH_BF16, "rmsnorm: unsupported gain dtype %d", w_dtype);
-    const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 32));
     const VecRef wr{w, w_dtype};
+    if (D % 4 == 0 && D <= 4096 && D >= 128) {
+        const int threads = ((D / 4 + 31) / 32) * 32;
+        if (act_dtype == MYNAH_F32)
+            mynah_launch(rmsnorm_vec4_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
+        else if (act_dtype == MYNAH_BF16)
+            mynah_launch(rmsnorm_vec4_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+        else
+            return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
+        return mynah_check_launch("rmsnorm");
+    }
+    const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 32));
     if (act_dtype == MYNAH_F32)
         mynah_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
     else if (act_dtype == MYNAH_BF16)
@@ -127,10 +170,37 @@ __global__ void swiglu_kernel(const TA* __restrict__ gate_up, TA* __restrict__ o
     out[(size_t)t * F + i] = from_f32<TA>((g * stable_sigmoid(g)) * u);
 }
 
+// Eight elements per thread (16-byte loads and stores) when F is a multiple of 8.
+template <typename TA>
+__global__ void swiglu_vec8_kernel(const TA* __restrict__ gate_up, TA* __restrict__ out, int F) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (i >= F) return;
+    const TA* row = gate_up + (size_t)t * 2 * F;
+    float g[8], u[8], o[8];
+    load8(row + i, g);
+    load8(row + F + i, u);
+#pragma unroll
+    for (int j = 0; j < 8; j++) o[j] = (g[j] * stable_sigmoid(g[j])) * u[j];
+    store8(out + (size_t)t * F + i, o);
+}
+
 MYNAH_API int mynah_swiglu(const void* gate_up, void* out, int act_dtype, int T, int F, cudaStream_t stream) {
     if (T == 0) return 0;
     MYNAH_REQUIRE(T > 0 && F > 0, "swiglu: bad sizes T=%d F=%d", T, F);
     MYNAH_REQUIRE(ceil_div(F, 256) <= 65535, "swiglu: width %d exceeds one launch", F);
+    if (F % 8 == 0) {
+        const dim3 vgrid(T, ceil_div(F / 8, 128));
+        if (act_dtype == MYNAH_F32)
+            mynah_launch(swiglu_vec8_kernel<float>, vgrid, dim3(128), 0, stream, (const float*)gate_up, (float*)out, F);
+        else if (act_dtype == MYNAH_BF16)
+            mynah_launch(swiglu_vec8_kernel<bf16>, vgrid, dim3(128), 0, stream, (const bf16*)gate_up, (bf16*)out, F);
+        else
+            return mynah_fail("swiglu: unsupported activation dtype %d", act_dtype);
+        return mynah_check_launch("swiglu");
+    }
     const dim3 grid(T, ceil_div(F, 256));
     if (act_dtype == MYNAH_F32)
         mynah_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gate_up, (float*)out, F);

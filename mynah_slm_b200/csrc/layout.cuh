@@ -20,6 +20,7 @@ enum MynahStatus : int {
     MYNAH_ST_POS_RANGE = 2,       // a position lies outside the rotation table
     MYNAH_ST_TOKEN_RANGE = 4,     // a token id lies outside the vocabulary
     MYNAH_ST_SPLIT_RANGE = 8,     // a decode launch has fewer page splits than a sequence has visible pages
+    MYNAH_ST_TIMEOUT = 16,        // a bounded wait inside a kernel ran out
 };
 
 struct PageTable {

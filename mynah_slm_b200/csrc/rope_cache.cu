@@ -118,6 +118,110 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
     }
 }
 
+// The same pass for head sizes that are a multiple of 32 with the whole head rotated: a lane keeps
+// head_dim/32 consecutive elements in registers, its rotation partner is the lane 16 further on, so
+// nothing goes through shared memory and every access is a vector.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
+                               const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                               const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                               PageTable pt, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                               QkvArgs a, int* __restrict__ status) {
+    griddep_launch();
+    griddep_wait();
+    constexpr int HD = EPL * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = k_cache != nullptr ? a.H + 2 * a.KV : a.H;
+    const long long unit = (long long)blockIdx.x * WARPS + warp;
+    if (unit >= (long long)a.T * heads) return;
+    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    const int seq = tok_seq[t];
+    if (seq < 0) return;
+    const int pos = tok_pos[t];
+    const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
+    const int kvh = is_q ? 0 : (is_k ? h - a.H : h - a.H - a.KV);
+    T* src = qkv + (size_t)t * a.ld + (size_t)h * HD + lane * EPL;
+    T* dst = src;
+    if (!is_q) {
+        const int page = page_of(pt, seq, pos);
+        if (page < 0) {
+            if (lane == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+            return;
+        }
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * a.KV + kvh) * PAGE_TOKENS + pos % PAGE_TOKENS) * HD + lane * EPL;
+    }
+    T raw[EPL];
+    if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
+    else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
+    else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
+    else {
+#pragma unroll
+        for (int j = 0; j < EPL; j++) raw[j] = src[j];
+    }
+    if (!is_q && !is_k) {                                  // V: copy
+        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(raw);
+        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(raw);
+        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(raw);
+        else {
+#pragma unroll
+            for (int j = 0; j < EPL; j++) dst[j] = raw[j];
+        }
+        return;
+    }
+    float v[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPL; j++) {
+        v[j] = to_f32(raw[j]);
+        ss += v[j] * v[j];
+    }
+    const VecRef gain = is_q ? q_gain : k_gain;
+    if (gain.p != nullptr) {
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+        for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * gain.at(lane * EPL + j));
+    }
+    if (cos_t != nullptr) {
+        if (pos < 0 || pos >= a.n_pos) {
+            if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+            return;
+        }
+        // lanes 0-15 hold the first half of the head, lanes 16-31 the second
+        const int i0 = (lane & 15) * EPL;
+        const float* c = cos_t + (size_t)pos * (HD / 2) + i0;
+        const float* sn = sin_t + (size_t)pos * (HD / 2) + i0;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
+        }
+    }
+    T o[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; j++) o[j] = from_f32<T>(v[j]);
+    if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+    else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
+    else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(o);
+    else {
+#pragma unroll
+        for (int j = 0; j < EPL; j++) dst[j] = o[j];
+    }
+}
+
+template <typename T>
+bool launch_fast(int HD, unsigned blocks, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, const float* cos_t,
+                 const float* sin_t, const int* tok_seq, const int* tok_pos, PageTable pt, T* kc, T* vc, QkvArgs a, int* status) {
+    switch (HD) {
+        case 32: mynah_launch(qk_norm_rope_store_fast_kernel<T, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
+        case 64: mynah_launch(qk_norm_rope_store_fast_kernel<T, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
+        case 128: mynah_launch(qk_norm_rope_store_fast_kernel<T, 4>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
+        case 256: mynah_launch(qk_norm_rope_store_fast_kernel<T, 8>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
+        default: return false;
+    }
+}
+
 }  // namespace
 
 MYNAH_API int mynah_rope_table(float* cos_t, float* sin_t, int n_pos, int rotary_dim, double theta,
@@ -150,6 +254,14 @@ MYNAH_API int mynah_qk_norm_rope_store(
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const long long units = (long long)T * heads;
     const unsigned blocks = (unsigned)ceil_div_ll(units, WARPS);
+    // the register-only kernel: the whole head rotated (or none of it), rows 16-byte aligned
+    const bool fast_ok = (cos_t == nullptr || rotary_dim == HD) && ld % 8 == 0;
+    if (fast_ok && dtype == MYNAH_F32 &&
+        launch_fast<float>(HD, blocks, stream, (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status))
+        return mynah_check_launch("qk_norm_rope_store");
+    if (fast_ok && dtype == MYNAH_BF16 &&
+        launch_fast<bf16>(HD, blocks, stream, (bf16*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status))
+        return mynah_check_launch("qk_norm_rope_store");
     if (dtype == MYNAH_F32)
         mynah_launch(qk_norm_rope_store_kernel<float, float>, dim3(blocks), dim3(WARPS * 32), 0, stream,
             (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status);

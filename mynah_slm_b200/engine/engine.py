@@ -437,11 +437,15 @@ class Engine:
 
     def check_status(self) -> None:
         """Raise if a kernel met an index it had to refuse. Synchronises."""
-        st = int(self.runtime.status.item())
+        from ..ops import gemm_bf16
+        word = gemm_bf16.status_word(self.device)
+        st = int((self.runtime.status | word).item())
         if st:
             self.runtime.status.zero_()
+            word.zero_()
             what = [name for bit, name in ((kernels.ST_PAGE_RANGE, "a position without a page"),
                                            (kernels.ST_POS_RANGE, "a position outside the rotation table"),
                                            (kernels.ST_TOKEN_RANGE, "a token id outside the vocabulary"),
-                                           (kernels.ST_SPLIT_RANGE, "a decode launch too small for a sequence")) if st & bit]
+                                           (kernels.ST_SPLIT_RANGE, "a decode launch too small for a sequence"),
+                                           (16, "a bounded wait inside a kernel ran out")) if st & bit]
             raise EngineError("a kernel refused an index: " + ", ".join(what))

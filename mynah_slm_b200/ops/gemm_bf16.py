@@ -13,8 +13,55 @@ from typing import Callable, Optional
 
 import torch
 
+from . import lib
+from .lib import call, ptr, stream_ptr
+
 # Each route: f(x, w, out_dtype, out) -> Tensor or None (declined).
 ROUTES: list[Callable[..., Optional[torch.Tensor]]] = []
+
+# Switch for the hand-written tcgen05 product (tests compare it with the library's).
+USE_TCGEN05 = True
+# The SwiGLU epilogue of the tcgen05 product (off while its epilogue does not overlap the next tile's main loop).
+USE_TCGEN05_SWIGLU = False
+# Rows from which the tcgen05 tiles (128 rows each) are worth their launch.
+TCGEN05_MIN_ROWS = 17
+
+_STATUS: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Status word that the tcgen05 kernel reports a timed-out wait through."""
+    key = str(device)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def tcgen05_supported(M: int, N: int, K: int) -> bool:
+    return bool(lib.load().mynah_gemm_tcgen05_supported(M, N, K))
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
+    """epilogue 0: bf16 rows, 1: fp32 rows, 2: SwiGLU (w = N gate rows then N up rows)."""
+    M, K = x.shape
+    call("mynah_gemm_tcgen05", ptr(x), ptr(w), ptr(out), M, N, K, out.shape[1], epilogue, ptr(status_word(x.device)),
+         stream_ptr())
+    return out
+
+
+def _tcgen05_route(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor]):
+    M, K = x.shape
+    N = w.shape[0]
+    if not USE_TCGEN05 or M < TCGEN05_MIN_ROWS or N % 8 or not tcgen05_supported(M, N, K):
+        return None
+    if not (x.is_contiguous() and w.is_contiguous()) or (out is not None and not out.is_contiguous()):
+        return None
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    return gemm_tcgen05(x, w, N, 0 if out_dtype == torch.bfloat16 else 1, out)
+
+
+ROUTES.append(_tcgen05_route)
 
 # Launch count of hand-written matrix-product kernels (read by the benchmark).
 counters = {"own": 0, "library": 0}

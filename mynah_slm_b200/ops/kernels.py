@@ -210,6 +210,15 @@ def linear_swiglu(x, w_gate_up: torch.Tensor) -> torch.Tensor:
         from . import gemm_bf16
         gemm_bf16.counters["own"] += 1
         return _gemv_decode(x, w_gate_up, F, 1, out)
+    from . import gemm_bf16
+    if isinstance(x, NormedInput):
+        x = x.materialize()
+    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and gemm_bf16.USE_TCGEN05 and gemm_bf16.USE_TCGEN05_SWIGLU
+            and x.shape[0] >= gemm_bf16.TCGEN05_MIN_ROWS and F % 8 == 0 and x.is_contiguous()
+            and w_gate_up.is_contiguous() and gemm_bf16.tcgen05_supported(x.shape[0], F, x.shape[1])):
+        out = torch.empty((x.shape[0], F), dtype=torch.bfloat16, device=x.device)
+        gemm_bf16.counters["own"] += 1
+        return gemm_bf16.gemm_tcgen05(x, w_gate_up, F, 2, out)      # the activation runs on the accumulator
     return swiglu(linear(x, w_gate_up))
 
 

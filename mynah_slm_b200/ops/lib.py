@@ -55,6 +55,7 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
     "mynah_gemv_decode": [P, c_int, c_int, c_int, P, P, P, P, P, c_int, c_float, P, c_int, c_int, c_int, P],
+    "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_set_pdl": [c_int],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
@@ -86,6 +87,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_attn_prefill_tc_supported.restype = c_int
     lib.mynah_attn_prefill_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_gemm_tcgen05_supported.restype = c_int
+    lib.mynah_gemm_tcgen05_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int
     lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():

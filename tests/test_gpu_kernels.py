@@ -623,3 +623,50 @@ def test_attn_prefill_tensor_cores(H, KV, HD, window):
                           _page_table(lst)(7), win, status)
         hit = np.abs(o2.float().cpu().numpy()[1, :HDk] - vv[target, 0]).max() < 0.05
         assert hit == visible, (win, target)
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 1024), (2048, 1024, 2048), (130, 1000, 96), (17, 264, 64), (128, 128, 8),
+                                   (300, 6144, 1024), (1000, 1024, 3072)])
+def test_gemm_tcgen05(M, N, K):
+    """The tensor-memory product against float64, and against the library's product of the same operands."""
+    from mynah_slm_b200.ops import gemm_bf16
+    rng = np.random.default_rng(21)
+    a = _round(rng.standard_normal((M, K)), "bf16")
+    w = _round(rng.standard_normal((N, K)) * 0.05, "bf16")
+    ad, wd = torch.from_numpy(a).to(torch.bfloat16).to(DEV), torch.from_numpy(w).to(torch.bfloat16).to(DEV)
+    assert gemm_bf16.tcgen05_supported(M, N, K) and not gemm_bf16.tcgen05_supported(M, N, 100)
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    c32 = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    gemm_bf16.gemm_tcgen05(ad, wd, N, 1, c32)
+    assert gemm_bf16.status_word(torch.device(DEV)).item() == 0
+    assert rel_err(ref, c32.cpu().numpy()) < 2e-5                         # bf16 products, fp32 sums
+    c16 = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.gemm_tcgen05(ad, wd, N, 0, c16)
+    assert torch.equal(c16, c32.to(torch.bfloat16))                       # the same accumulator, rounded once
+    lib32 = torch.mm(ad, wd.t(), out_dtype=torch.float32)
+    assert rel_err(lib32.cpu().numpy(), c32.cpu().numpy()) < 2e-5
+    # through the dispatcher: rows >= 17 take this kernel
+    before = dict(gemm_bf16.counters)
+    got = _k().linear(ad, wd)
+    assert gemm_bf16.counters["own"] == before["own"] + 1 and torch.equal(got, c16)
+
+
+@pytest.mark.parametrize("M,F,K", [(2048, 3072, 1024), (300, 200, 64), (129, 128, 96)])
+def test_gemm_tcgen05_swiglu_epilogue(M, F, K):
+    from mynah_slm_b200.ops import gemm_bf16
+    rng = np.random.default_rng(22)
+    a = _round(rng.standard_normal((M, K)), "bf16")
+    w = _round(rng.standard_normal((2 * F, K)) * 0.1, "bf16")
+    ad, wd = torch.from_numpy(a).to(torch.bfloat16).to(DEV), torch.from_numpy(w).to(torch.bfloat16).to(DEV)
+    act = torch.empty((M, F), dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.gemm_tcgen05(ad, wd, F, 2, act)
+    assert act.shape == (M, F) and gemm_bf16.status_word(torch.device(DEV)).item() == 0
+    gu = _round(a.astype(np.float64) @ w.astype(np.float64).T, "bf16")
+    assert rel_err(plain_swiglu(gu[:, :F], gu[:, F:]), act.float().cpu().numpy()) < 1.5e-2
+    # against the unfused path of the library product and the separate activation kernel
+    gemm_bf16.USE_TCGEN05 = False
+    try:
+        unfused = _k().linear_swiglu(ad, wd)
+    finally:
+        gemm_bf16.USE_TCGEN05 = True
+    assert rel_err(unfused.float().cpu().numpy(), act.float().cpu().numpy()) < 1e-2
