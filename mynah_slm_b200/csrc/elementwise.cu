@@ -153,9 +153,9 @@ MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, lon
 // positive argument (mynah-slm src/kernels.c:193-205). gate_up is [T, 2F]:
 // gate in columns [0, F), up in [F, 2F).
 __device__ __forceinline__ float stable_sigmoid(float v) {
-    if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
-    const float e = expf(v);
-    return e / (1.0f + e);
+    // e^-|v| never overflows; the select keeps both branches of the reference's stable form exact
+    const float e = expf(-fabsf(v));
+    return (v >= 0.f ? 1.0f : e) / (1.0f + e);
 }
 
 template <typename TA>

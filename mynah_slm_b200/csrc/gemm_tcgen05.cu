@@ -1,18 +1,23 @@
 // bf16 matrix product on the fifth-generation tensor cores:
 //   C[M, N] = A[M, K] . W[N, K]^T,  fp32 accumulation in tensor memory.
 //
-// One CTA computes a 128 x BN tile of C (BN = 128 or 256). Operand tiles of
-// 64 k (128 bytes per row) are brought into shared memory by TMA
-// (cp.async.bulk.tensor, 128-byte swizzle) through a ring of stages; one
-// elected thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
-// K = 16 per instruction) with shared-memory descriptors for both operands
-// (both are K-major: activations [M, K] and weights [N, K] as stored); the
-// accumulator lives in tensor memory (BN columns of 128 lanes) and is read
-// back with tcgen05.ld by four epilogue warps, one per 32-lane quadrant.
+// A persistent kernel: one CTA per SM walks over 128 x BN tiles of C (BN = 128
+// or 256). Operand tiles of 64 k (128 bytes per row) are brought into shared
+// memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of
+// stages that runs on across tiles; one elected thread issues tcgen05.mma
+// (cta_group::1, kind::f16, M = 128, N = BN, K = 16 per instruction) with
+// shared-memory descriptors for both operands (both are K-major: activations
+// [M, K] and weights [N, K] as stored). The accumulator lives in tensor
+// memory, in two buffers of BN columns, so that the epilogue of one tile
+// (tcgen05.ld, conversion, the activation if any, a swizzled staging tile in
+// shared memory, a TMA store) runs while the tensor cores work on the next.
+//
 // Warp roles: 0 TMA producer, 1 MMA issuer and tensor-memory owner, 2..5
-// epilogue. Stage hand-over is by mbarriers: TMA completes transactions on
-// `full`, tcgen05.commit arrives on `empty` when the instructions that read a
-// stage have finished, and on `acc_full` when the whole tile is accumulated.
+// epilogue (one per 32-lane quadrant of tensor memory). Hand-over is by
+// mbarriers: TMA completes transactions on `full`; tcgen05.commit arrives on
+// `empty` when the instructions that read a stage have finished and on
+// `acc_full` when a tile is accumulated; the epilogue warps arrive on
+// `acc_empty` when they have read a buffer out.
 //
 // Epilogues: bf16 rows; fp32 rows (logits); SwiGLU, where the B tile is 128
 // gate rows followed by the matching 128 up rows of the fused gate/up matrix,
@@ -20,9 +25,9 @@
 // accumulator and only [M, F] is ever written.
 //
 // Every wait on an mbarrier is bounded by a wall-clock limit; a wait that runs
-// out sets a status bit, and the CTA still drains what it started, frees its
-// tensor memory and returns. Rows of A or W beyond the matrix are zero-filled
-// by TMA, and the epilogue stores only what lies inside C.
+// out sets a status bit and an abort flag, and the CTA still drains the copies
+// it started, frees its tensor memory and returns. Rows of A or W beyond the
+// matrix are zero-filled by TMA; TMA stores clip what lies outside C.
 #include "layout.cuh"
 
 #include <cuda.h>
@@ -32,6 +37,7 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int THREADS = 192;
+constexpr int STAGING_BYTES = 32 * 128;              // 32 rows x 128 bytes per epilogue warp and buffer
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 
 enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
@@ -42,12 +48,14 @@ __device__ __forceinline__ unsigned long long now_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for the phase with the given parity. False when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -67,6 +75,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -101,41 +117,58 @@ __host__ __device__ constexpr uint32_t umma_idesc(int n) {
 }
 
 __device__ __forceinline__ float sigmoid_stable(float v) {
-    if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
-    const float e = expf(v);
-    return e / (1.0f + e);
+    // e^-|v| never overflows; the select keeps both branches of the reference's stable form exact
+    const float e = expf(-fabsf(v));
+    return (v >= 0.f ? 1.0f : e) / (1.0f + e);
 }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+struct GemmShape {
+    int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
+    int up_offset;
+    int m_tiles, n_tiles;
+};
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ C, int M, int N, int K, int ldc, int up_offset, int* __restrict__ status) {
+                    const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE = A_BYTES + B_BYTES;
     constexpr int STAGES = BN == 256 ? 4 : 6;
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : BN;           // output columns of a tile
+    constexpr int CHUNK = EPI == EPI_F32 ? 32 : 64;                  // output columns per staged store (128 bytes per row)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), acc_full = smem_u32(bars + 2 * STAGES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    unsigned char* staging = smem + STAGES * STAGE;                  // 4 warps x 2 buffers x 4 KB, 1024-aligned
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 4 * 2 * STAGING_BYTES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tile = blockIdx.x, m_tile = blockIdx.y;
-    const int nk = (K + BK - 1) / BK;
+    const int nk = (g.K + BK - 1) / BK;
+    const int total_tiles = g.m_tiles * g.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);                        // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_async_smem();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -144,125 +177,157 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {                                           // ---- TMA producer
-            int issued = 0;
-            for (int kb = 0; kb < nk; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1) || *abort_flag) {
-                    *abort_flag = 1;
-                    atomicOr(status, MYNAH_ST_TIMEOUT);
-                    break;
-                }
-                const uint32_t a_dst = smem_u32(smem + s * STAGE), b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(full0 + 8 * s, STAGE);
-                tma_load_2d(a_dst, &map_a, kb * BK, m_tile * BM, full0 + 8 * s);
-                if (EPI == EPI_SWIGLU) {                           // 128 gate rows, then their 128 up rows
-                    tma_load_2d(b_dst, &map_b, kb * BK, n_tile * 128, full0 + 8 * s);
-                    tma_load_2d(b_dst + 128 * BK * 2, &map_b, kb * BK, up_offset + n_tile * 128, full0 + 8 * s);
-                } else {
+        if (lane == 0) {                                             // ---- TMA producer
+            int it = 0;                                              // k-blocks issued, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
+                for (int kb = 0; kb < nk; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1) || *abort_flag) {
+                        *abort_flag = 1;
+                        atomicOr(status, MYNAH_ST_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_u32(smem + s * STAGE), b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, STAGE);
+                    tma_load_2d(a_dst, &map_a, kb * BK, m_tile * BM, full0 + 8 * s);
+                    if (EPI == EPI_SWIGLU) {                         // 128 gate rows, then their 128 up rows
+                        tma_load_2d(b_dst, &map_b, kb * BK, n_tile * 128, full0 + 8 * s);
+                        tma_load_2d(b_dst + 128 * BK * 2, &map_b, kb * BK, g.up_offset + n_tile * 128, full0 + 8 * s);
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < BN / 128; j++)
-                        tma_load_2d(b_dst + j * 128 * BK * 2, &map_b, kb * BK, n_tile * BN + j * 128, full0 + 8 * s);
+                        for (int j = 0; j < BN / 128; j++)
+                            tma_load_2d(b_dst + j * 128 * BK * 2, &map_b, kb * BK, n_tile * BN + j * 128, full0 + 8 * s);
+                    }
                 }
-                issued = kb + 1;
             }
-            if (*abort_flag) {
+            if (!ok) {
                 // copies that were started still land in this CTA's shared memory: wait for them (bounded)
-                for (int kb = max(0, issued - STAGES); kb < issued; kb++) mbar_wait(full0 + 8 * (kb % STAGES), (kb / STAGES) & 1);
+                for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {                                           // ---- MMA issuer
+        if (lane == 0) {                                             // ---- MMA issuer
             constexpr uint32_t idesc = umma_idesc(BN);
+            int it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < nk && ok; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait(full0 + 8 * s, ph) || *abort_flag) {
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+                const int buf = local & 1;
+                const uint32_t use = (local >> 1) & 1;
+                if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1) || *abort_flag) {   // the epilogue has read this buffer out
                     *abort_flag = 1;
                     atomicOr(status, MYNAH_ST_TIMEOUT);
-                    ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE), b_addr = a_addr + A_BYTES;
-#pragma unroll
-                for (int k = 0; k < BK / 16; k++)
-                    tc_mma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
-                tc_commit(empty0 + 8 * s);                         // the stage is free once these have read it
-            }
-            tc_commit(acc_full);                                   // arrives when everything issued above is done
-        }
-    } else {                                                       // ---- epilogue: warps 2..5 -> lane quadrants 2,3,0,1
-        const int quad = warp & 3;
-        const bool ok = mbar_wait(acc_full, 0) && !*abort_flag;
-        if (!ok && lane == 0) atomicOr(status, MYNAH_ST_TIMEOUT);
-        tc_fence_after();
-        const int row = m_tile * BM + quad * 32 + lane;
-        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
-        if (ok) {
-            if (EPI == EPI_SWIGLU) {
-                bf16* out = static_cast<bf16*>(C);
-#pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
-                    uint32_t g[32], u[32];
-                    tc_ld32(t_row + c0, g);
-                    tc_ld32(t_row + 128 + c0, u);
-                    if (row < M) {
-                        const int col0 = n_tile * 128 + c0;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float o[8];
-#pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                // gate and up rounded to bf16 first, as when they are stored before the activation
-                                const float gv = round_to<bf16>(__uint_as_float(g[j + e])), uv = round_to<bf16>(__uint_as_float(u[j + e]));
-                                o[e] = (gv * sigmoid_stable(gv)) * uv;
-                            }
-                            if (col0 + j + 8 <= N) store8(out + (size_t)row * ldc + col0 + j, o);
-                            else
-                                for (int e = 0; e < 8; e++)
-                                    if (col0 + j + e < N) out[(size_t)row * ldc + col0 + j + e] = __float2bfloat16_rn(o[e]);
-                        }
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < nk; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph) || *abort_flag) {
+                        *abort_flag = 1;
+                        atomicOr(status, MYNAH_ST_TIMEOUT);
+                        ok = false;
+                        break;
                     }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)
+                        tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+                    tc_commit(empty0 + 8 * s);                       // the stage is free once these have read it
                 }
-            } else {
+                tc_commit(acc_full0 + 8 * buf);                      // arrives when the tile is accumulated
+            }
+        }
+    } else {                                                         // ---- epilogue: warps 2..5 -> lane quadrants 2,3,0,1
+        const int quad = warp & 3;
+        unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
+        int local = 0, n_store = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
+            const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
+            const int buf = local & 1;
+            const uint32_t use = (local >> 1) & 1;
+            if (!mbar_wait(acc_full0 + 8 * buf, use) || *abort_flag) {
+                if (lane == 0) {
+                    *abort_flag = 1;
+                    atomicOr(status, MYNAH_ST_TIMEOUT);
+                }
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
+            const int row0 = m_tile * BM + quad * 32;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < OUT_COLS; c0 += CHUNK, n_store++) {
+                unsigned char* st = my_stage + (n_store & 1) * STAGING_BYTES;
+                // the store that last read this staging buffer must have finished reading it
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                unsigned char* my_row = st + lane * 128;
+                if (EPI == EPI_F32) {
                     uint32_t r[32];
                     tc_ld32(t_row + c0, r);
-                    if (row < M) {
-                        const int col0 = n_tile * BN + c0;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float o[8];
+                    for (int j = 0; j < 8; j++)
+                        *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) * 16)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                } else if (EPI == EPI_BF16) {
 #pragma unroll
-                            for (int e = 0; e < 8; e++) o[e] = __uint_as_float(r[j + e]);
-                            if (EPI == EPI_F32) {
-                                float* out = static_cast<float*>(C) + (size_t)row * ldc + col0 + j;
-                                if (col0 + j + 8 <= N) store8(out, o);
-                                else
-                                    for (int e = 0; e < 8; e++)
-                                        if (col0 + j + e < N) out[e] = o[e];
-                            } else {
-                                bf16* out = static_cast<bf16*>(C) + (size_t)row * ldc + col0 + j;
-                                if (col0 + j + 8 <= N) store8(out, o);
-                                else
-                                    for (int e = 0; e < 8; e++)
-                                        if (col0 + j + e < N) out[e] = __float2bfloat16_rn(o[e]);
-                            }
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t r[32];
+                        tc_ld32(t_row + c0 + half * 32, r);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint4 v = make_uint4(pack2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                                       pack2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                                       pack2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                                       pack2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                            *reinterpret_cast<uint4*>(my_row + (((half * 4 + j) ^ (lane & 7)) * 16)) = v;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t gt[32], up[32];
+                        tc_ld32(t_row + c0 + half * 32, gt);
+                        tc_ld32(t_row + 128 + c0 + half * 32, up);
+                        float o[32];
+#pragma unroll
+                        for (int e = 0; e < 32; e++) {
+                            // gate and up rounded to bf16 first, as when they are stored before the activation
+                            const float gv = round_to<bf16>(__uint_as_float(gt[e])), uv = round_to<bf16>(__uint_as_float(up[e]));
+                            o[e] = (gv * sigmoid_stable(gv)) * uv;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint4 v = make_uint4(pack2(o[8 * j], o[8 * j + 1]), pack2(o[8 * j + 2], o[8 * j + 3]),
+                                                       pack2(o[8 * j + 4], o[8 * j + 5]), pack2(o[8 * j + 6], o[8 * j + 7]));
+                            *reinterpret_cast<uint4*>(my_row + (((half * 4 + j) ^ (lane & 7)) * 16)) = v;
                         }
                     }
                 }
+                fence_async_smem();                                  // the staged rows become visible to the TMA engine
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_c, smem_u32(st), n_tile * OUT_COLS + c0, row0);
+                    tma_store_commit();
+                }
             }
+            // this warp has read its quadrant of the buffer out
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
         }
+        if (lane == 0) tma_store_wait_all();
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
@@ -283,26 +348,27 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [rows, cols] bf16 row-major, boxes of 128 rows x 64 columns, 128-byte swizzle; out-of-range reads give zero.
-int make_map(CUtensorMap* map, const void* base, long long rows, long long cols) {
+// [rows, cols] row-major with a row pitch of `ld` elements; boxes of box_rows x box_cols (box_cols * element size = 128
+// bytes), 128-byte swizzle. Loads outside the tensor give zero; stores outside are dropped.
+int make_map(CUtensorMap* map, const void* base, CUtensorMapDataType dt, int esize, long long rows, long long cols, long long ld,
+             int box_rows, int box_cols) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return mynah_fail("gemm_tcgen05: the driver does not provide cuTensorMapEncodeTiled");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {BK, 128};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return mynah_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return 0;
 }
 
 template <int BN, int EPI>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, int N, int K, int ldc, int up_offset,
-                int* status, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
+                int sm_count, int* status, cudaStream_t stream) {
     constexpr int STAGES = BN == 256 ? 4 : 6;
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 4 * 2 * STAGING_BYTES + 256 + 1024;
     auto kern = gemm_tcgen05_kernel<BN, EPI>;
     static bool opted = false;
     if (!opted) {
@@ -310,38 +376,50 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, void* C, int M, in
         if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
         opted = true;
     }
-    const int n_tiles = EPI == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, BN);
-    const dim3 grid(n_tiles, ceil_div(M, BM));
-    kern<<<grid, THREADS, smem, stream>>>(ma, mb, C, M, N, K, ldc, up_offset, status);
+    GemmShape g;
+    g.M = M; g.N = N; g.K = K; g.up_offset = up_offset;
+    g.m_tiles = ceil_div(M, BM);
+    g.n_tiles = EPI == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, BN);
+    const long long tiles = (long long)g.m_tiles * g.n_tiles;
+    MYNAH_REQUIRE(tiles < (1ll << 30), "gemm_tcgen05: too many tiles");
+    const int ctas = (int)(tiles < sm_count ? tiles : sm_count);
+    kern<<<ctas, THREADS, smem, stream>>>(ma, mb, mc, g, status);
     return mynah_check_launch("gemm_tcgen05");
 }
 
 }  // namespace
 
 MYNAH_API int mynah_gemm_tcgen05_supported(int M, int N, int K) {
-    return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0;      // rows of 16-byte multiples for TMA
+    return M >= 1 && N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0;      // rows of 16-byte multiples for TMA
 }
 
 // epilogue 0: C bf16 [M, N]; 1: C fp32 [M, N]; 2: SwiGLU, W holds N gate rows then N up rows, C bf16 [M, N].
-// A [M, K] and W [rows, K] are bf16, row-major, 16-byte aligned. `status` receives MYNAH_ST_TIMEOUT if a wait ran out.
+// A [M, K] and W [rows, K] are bf16, row-major, 16-byte aligned; ldc is C's row pitch in elements. `status`
+// receives MYNAH_ST_TIMEOUT if a wait inside the kernel ran out.
 MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int epilogue,
-                                 int* status, cudaStream_t stream) {
+                                 int sm_count, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
-    MYNAH_REQUIRE(mynah_gemm_tcgen05_supported(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
+    MYNAH_REQUIRE(mynah_gemm_tcgen05_supported(M, N, K), "gemm_tcgen05: M=%d N=%d K=%d is not taken (N and K must be multiples of 8)", M, N, K);
     MYNAH_REQUIRE(epilogue >= 0 && epilogue <= 2 && ldc >= N, "gemm_tcgen05: bad epilogue or output stride");
-    MYNAH_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0 && ldc % 8 == 0,
-                  "gemm_tcgen05: operands must be 16-byte aligned and the output stride a multiple of 8");
+    const int csize = epilogue == EPI_F32 ? 4 : 2;
+    MYNAH_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0 && (ldc * csize) % 16 == 0,
+                  "gemm_tcgen05: operands must be 16-byte aligned and the output pitch a multiple of 16 bytes");
     MYNAH_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
-    MYNAH_REQUIRE(ceil_div(M, BM) <= 65535, "gemm_tcgen05: %d rows exceed one launch", M);
-    CUtensorMap ma, mb;
-    if (make_map(&ma, A, M, K)) return -1;
-    if (make_map(&mb, W, epilogue == EPI_SWIGLU ? 2LL * N : N, K)) return -1;
-    if (epilogue == EPI_SWIGLU) return launch_gemm<256, EPI_SWIGLU>(ma, mb, C, M, N, K, ldc, N, status, stream);
+    if (sm_count <= 0) sm_count = 148;
+    CUtensorMap ma, mb, mc;
+    if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
+    if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, epilogue == EPI_SWIGLU ? 2LL * N : N, K, K, 128, BK)) return -1;
+    if (epilogue == EPI_F32) {
+        if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32)) return -1;
+    } else {
+        if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
+    }
+    if (epilogue == EPI_SWIGLU) return launch_gemm<256, EPI_SWIGLU>(ma, mb, mc, M, N, K, N, sm_count, status, stream);
     // narrow tiles when wide ones would leave most SMs idle
     const bool wide = (long long)ceil_div(N, 256) * ceil_div(M, BM) >= 120 || N > 4096;
     if (epilogue == EPI_F32)
-        return wide ? launch_gemm<256, EPI_F32>(ma, mb, C, M, N, K, ldc, 0, status, stream)
-                    : launch_gemm<128, EPI_F32>(ma, mb, C, M, N, K, ldc, 0, status, stream);
-    return wide ? launch_gemm<256, EPI_BF16>(ma, mb, C, M, N, K, ldc, 0, status, stream)
-                : launch_gemm<128, EPI_BF16>(ma, mb, C, M, N, K, ldc, 0, status, stream);
+        return wide ? launch_gemm<256, EPI_F32>(ma, mb, mc, M, N, K, 0, sm_count, status, stream)
+                    : launch_gemm<128, EPI_F32>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
+    return wide ? launch_gemm<256, EPI_BF16>(ma, mb, mc, M, N, K, 0, sm_count, status, stream)
+                : launch_gemm<128, EPI_BF16>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
 }

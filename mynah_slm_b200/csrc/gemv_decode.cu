@@ -54,9 +54,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 }
 
 __device__ __forceinline__ float stable_sigmoid_f(float v) {
-    if (v >= 0.f) return 1.0f / (1.0f + expf(-v));
-    const float e = expf(v);
-    return e / (1.0f + e);
+    // e^-|v| never overflows; the select keeps both branches of the reference's stable form exact
+    const float e = expf(-fabsf(v));
+    return (v >= 0.f ? 1.0f : e) / (1.0f + e);
 }
 
 template <int EPI, bool NORM>

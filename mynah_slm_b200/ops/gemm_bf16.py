@@ -21,8 +21,8 @@ ROUTES: list[Callable[..., Optional[torch.Tensor]]] = []
 
 # Switch for the hand-written tcgen05 product (tests compare it with the library's).
 USE_TCGEN05 = True
-# The SwiGLU epilogue of the tcgen05 product (off while its epilogue does not overlap the next tile's main loop).
-USE_TCGEN05_SWIGLU = False
+# The SwiGLU epilogue of the tcgen05 product.
+USE_TCGEN05_SWIGLU = True
 # Rows from which the tcgen05 tiles (128 rows each) are worth their launch.
 TCGEN05_MIN_ROWS = 17
 
@@ -37,6 +37,16 @@ def status_word(device) -> torch.Tensor:
     return _STATUS[key]
 
 
+_SMS: dict = {}
+
+
+def _sm_count(device) -> int:
+    key = str(device)
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SMS[key]
+
+
 def tcgen05_supported(M: int, N: int, K: int) -> bool:
     return bool(lib.load().mynah_gemm_tcgen05_supported(M, N, K))
 
@@ -44,8 +54,8 @@ def tcgen05_supported(M: int, N: int, K: int) -> bool:
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """epilogue 0: bf16 rows, 1: fp32 rows, 2: SwiGLU (w = N gate rows then N up rows)."""
     M, K = x.shape
-    call("mynah_gemm_tcgen05", ptr(x), ptr(w), ptr(out), M, N, K, out.shape[1], epilogue, ptr(status_word(x.device)),
-         stream_ptr())
+    call("mynah_gemm_tcgen05", ptr(x), ptr(w), ptr(out), M, N, K, out.shape[1], epilogue, _sm_count(x.device),
+         ptr(status_word(x.device)), stream_ptr())
     return out
 
 

@@ -55,7 +55,7 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
     "mynah_gemv_decode": [P, c_int, c_int, c_int, P, P, P, P, P, c_int, c_float, P, c_int, c_int, c_int, P],
-    "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
+    "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_set_pdl": [c_int],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
