@@ -32,8 +32,20 @@ TINY_C = dict(  # a window on the upper layers, sizes that are no power of two, 
     rope_theta=50000.0, rms_norm_eps=1e-4, tie_word_embeddings=False, max_position_embeddings=1024,
     hidden_act="silu", attention_bias=False, rope_scaling=None, use_sliding_window=True, sliding_window=40,
     max_window_layers=2, eos_token_id=5)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
+TINY_D = dict(  # head_dim 64, group 2: the sizes the tensor-core and fused decode kernels take
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=128,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=192, vocab_size=640,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=512,
+    hidden_act="silu", attention_bias=False, rope_scaling=None, use_sliding_window=False, sliding_window=None,
+    eos_token_id=3)
+TINY_E = dict(  # head_dim 128, one kv head for four query heads, a window from layer 1 on, untied head
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=96,
+    num_attention_heads=4, num_key_value_heads=1, head_dim=128, intermediate_size=160, vocab_size=500,
+    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512,
+    hidden_act="silu", attention_bias=False, rope_scaling=None, use_sliding_window=True, sliding_window=40,
+    max_window_layers=1, eos_token_id=9)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
 def make_folder(tmp_path, name: str, dtype=torch.float32, seed=None, config=None) -> str:

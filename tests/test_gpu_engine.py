@@ -327,3 +327,32 @@ def test_command_line(folders, tmp_path):
     bad = subprocess.run(cli + ["run", "-m", folder, "--bogus"], capture_output=True, text=True)
     assert bad.returncode == 2 and "unknown option '--bogus'" in bad.stderr
     assert subprocess.run(cli + ["--version"], capture_output=True, text=True).stdout.strip()
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_fused_decode_step_equals_the_step_part_by_part(tmp_path, name):
+    """The persistent decode kernel against the same steps run part by part
+    (and both against the plain implementation): unequal lengths, a padding
+    row in the bucket, the window of E, steps that cross a page end."""
+    key = (name, torch.bfloat16)
+    folders = {key: make_folder(tmp_path, name, torch.bfloat16)}
+    plain = PlainQwen3.from_folder(folders[key])
+    lens = [70, 9, 33, 62, 5]                          # 62 -> crosses the page end at 64 while decoding
+    n_dec = 6
+    seqs = prompts_for(name, [n + n_dec for n in lens], seed=55)
+    outs = {}
+    for fused in (True, False):
+        eng = _engine(folders[key], "bfloat16", 64 * 12, fused_decode=fused)
+        assert (eng.fused is not None) == fused
+        slots = [eng.open_sequence() for _ in seqs]
+        eng.step([_entry(s, q[:n], ()) for s, q, n in zip(slots, seqs, lens)])
+        rows = []
+        for t in range(n_dec):
+            rows.append(eng.step([_entry(s, [q[n + t]], (0,)) for s, q, n in zip(slots, seqs, lens)]).cpu().numpy())
+        eng.check_status()
+        outs[fused] = np.stack(rows, axis=1)             # [seq, step, vocab]
+    for i, (q, n) in enumerate(zip(seqs, lens)):
+        ref = plain.forward(q)[n:n + n_dec]
+        assert_close(ref, outs[True][i], BF16_REL, f"{name} fused decode, request {i}")
+        assert_close(ref, outs[False][i], BF16_REL, f"{name} decode part by part, request {i}")
+        assert_close(outs[False][i], outs[True][i], 1e-2, f"{name} fused against part by part, request {i}")
