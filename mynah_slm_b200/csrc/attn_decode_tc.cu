@@ -22,6 +22,7 @@ namespace {
 constexpr int KEYS = PAGE_TOKENS;     // 64 keys per CTA
 constexpr int WARPS = 4;
 constexpr int MAX_G = 16;             // query heads per kv head that one MMA tile holds
+constexpr int MERGE_MAX_BYTES = KEYS * 64 * 2;   // the merge's weights: (heads per group) * (pages) floats; the smaller K tile holds them
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -248,49 +249,367 @@ attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
     }
 }
 
-// Merge of a sequence's pages, in page order: one CTA per (head, sequence).
-template <typename T>
-__global__ void attn_decode_combine_fast_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                                T* __restrict__ out, const int* __restrict__ kv_len, int window,
-                                                int H, int HD, int S_max, int ldo) {
-    extern __shared__ float w_s[];                    // weights exp(m_s - M) of the pages
-    __shared__ float red[32];
-    __shared__ float inv_s;
+// Merge of the pages of one (sequence, kv head) by a CTA of WARPS warps: the G heads of the group, n_vis pages.
+// A warp computes a head's weights exp(m_s - max) and the sum of the weighted sums; the output rows are added
+// up in NS interleaved series (series k takes pages k, k + NS, ...) that are then added in order. The order
+// depends on the number of pages alone, so a sequence gets the same bits in every batch and from either
+// kernel that calls this. `w_s`: G * S floats, `acc_s`: NS * HD floats, `inv_s`: MAX_G floats, all shared.
+template <int HD>
+__device__ __forceinline__ void merge_pages(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                            bf16* __restrict__ out_row, size_t r0g, int G, int S, int n_vis,
+                                            float* w_s, float* acc_s, float* inv_s) {
+    // (G may also be 1 with r0g and out_row pointing at one head: a head's arithmetic does not involve the others.)
+    constexpr int LPR = HD / 4, NS = WARPS * 32 / LPR;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = warp; i < G; i += WARPS) {
+        const size_t r0h = r0g + (size_t)i * S;
+        float mmax = -INFINITY;
+        for (int s2 = lane; s2 < n_vis; s2 += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (r0h + s2) * 2));
+        mmax = warp_max(mmax);
+        float ls = 0.f;
+        for (int s2 = lane; s2 < n_vis; s2 += 32) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (r0h + s2) * 2));
+            const float w = ml.x == -INFINITY ? 0.f : expf(ml.x - mmax);
+            w_s[i * S + s2] = w;
+            ls = fmaf(ml.y, w, ls);
+        }
+        ls = warp_sum(ls);
+        if (lane == 0) inv_s[i] = ls > 0.f ? 1.0f / ls : 0.f;
+    }
+    __syncthreads();
+    const int ld4 = tid % LPR, slot = tid / LPR;
+    for (int i = 0; i < G; i++) {
+        const size_t r0h = r0g + (size_t)i * S;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int s2 = slot; s2 < n_vis; s2 += NS) {
+            const float w = w_s[i * S + s2];
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(part_o + (r0h + s2) * HD) + ld4);
+            if (w != 0.f) {                           // a page without visible keys wrote no output row
+                acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
+                acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
+            }
+        }
+        reinterpret_cast<float4*>(acc_s + slot * HD)[ld4] = acc;
+        __syncthreads();
+        for (int d = tid; d < HD; d += WARPS * 32) {
+            float os = 0.f;
+#pragma unroll
+            for (int k = 0; k < NS; k++) os += acc_s[k * HD + d];
+            out_row[(size_t)i * HD + d] = __float2bfloat16_rn(os * inv_s[i]);
+        }
+        __syncthreads();
+    }
+}
+
+// The merge as a launch of its own: one CTA per (head, sequence).
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                         const int* __restrict__ kv_len, int window, int H, int S, int ldo) {
+    constexpr int NS = WARPS * 32 / (HD / 4);
+    extern __shared__ float w_s[];
+    __shared__ __align__(16) float acc_s[NS * HD];
+    __shared__ float inv_s[MAX_G];
     const int h = blockIdx.x, b = blockIdx.y;
-    const size_t row0 = ((size_t)b * H + h) * S_max;
     griddep_wait();
     griddep_launch();
     const int hi = kv_len[b];
     const int lo = window > 0 ? max(0, hi - window) : 0;
-    const int S = hi > 0 ? min(S_max, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
-    float mx = -INFINITY;
-    for (int s = threadIdx.x; s < S; s += blockDim.x) mx = fmaxf(mx, part_ml[(row0 + s) * 2]);
-    mx = warp_max(mx);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) red[warp] = mx;
-    __syncthreads();
-    mx = -INFINITY;
-    for (int w = 0; w < (int)((blockDim.x + 31) >> 5); w++) mx = fmaxf(mx, red[w]);
-    for (int s = threadIdx.x; s < S; s += blockDim.x) {
-        const float m = part_ml[(row0 + s) * 2];
-        w_s[s] = m == -INFINITY ? 0.f : expf(m - mx);
+    const int n_vis = hi > 0 ? min(S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
+    merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)h * HD, ((size_t)b * H + h) * S, 1, S, n_vis, w_s, acc_s, inv_s);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The whole attention of a decode step in one launch: what qk_norm_rope_store, the page kernel above and the
+// combine kernel do one after the other. A CTA takes one visible page of one (sequence, kv head):
+//   - it norms and rotates the group's query heads itself (fp32, rounded to bf16 as the separate pass stores them);
+//   - the CTA whose page holds the new position norms and rotates the new k, copies the new v, writes both to
+//     the cache and puts them into its tiles directly (the row is left out of the asynchronous copy, so the
+//     cache is never read where this launch writes it);
+//   - it writes its partial result, and the CTA that finishes a (sequence, kv head) last merges the pages in
+//     page order. The order of the merge does not depend on which CTA does it.
+// The counters are zero before the first launch and are left zero by every launch.
+struct FusedArgs {
+    int H, KV, ldq, ldo;
+    int window, S;
+    int n_pos, write_kv;
+    float scale, qk_eps;
+};
+
+template <int HD>
+__device__ __forceinline__ void head_norm_rope(float (&v)[HD / 32], VecRef gain, float eps, const float* __restrict__ cos_t,
+                                               const float* __restrict__ sin_t, int pos, int lane) {
+    constexpr int EPL = HD / 32;
+    if (gain.p != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) ss += v[j] * v[j];
+        ss = warp_sum(ss);
+        const float sc = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * gain.at(lane * EPL + j));
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float ls = 0.f;
-        for (int s = 0; s < S; s++) ls += part_ml[(row0 + s) * 2 + 1] * w_s[s];     // page order
-        inv_s = ls > 0.f ? 1.0f / ls : 0.f;
-    }
-    __syncthreads();
-    const float inv = inv_s;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float os = 0.f;
-        for (int s = 0; s < S; s++) {
-            const float w = w_s[s];
-            if (w != 0.f) os += part_o[(row0 + s) * HD + d] * w;
+    if (cos_t != nullptr) {
+        const int i0 = (lane & 15) * EPL;           // lanes 0-15 hold the first half of the head, 16-31 the second
+        const float* c = cos_t + (size_t)pos * (HD / 2) + i0;
+        const float* sn = sin_t + (size_t)pos * (HD / 2) + i0;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+            v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
         }
-        out[(size_t)b * ldo + (size_t)h * HD + d] = from_f32<T>(os * inv);
     }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
+                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         const int* __restrict__ tok_pos, const int* __restrict__ kv_len, PageTable pt,
+                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, FusedArgs a,
+                         float* __restrict__ part_o, float* __restrict__ part_ml, unsigned* __restrict__ counters,
+                         bf16* __restrict__ out, int* __restrict__ status) {
+    constexpr int CH = HD / 8, KSTEPS = HD / 16, EPL = HD / 32, NT = HD / 32;
+    constexpr int QLD = HD + 8;                       // padded row of the query tile: no bank conflicts on its loads
+    __shared__ __align__(128) unsigned char k_s[KEYS * HD * 2];     // reused by the merge for the pages' weights
+    __shared__ __align__(128) unsigned char v_s[KEYS * HD * 2];     // reused by the merge for its series
+    __shared__ __align__(16) bf16 q_s[MAX_G * QLD];   // the queries; once they are in registers, the probabilities
+    __shared__ float red_m[WARPS][MAX_G], red_l[WARPS][MAX_G];
+    __shared__ int last_flag;
+    bf16* p_s = q_s;
+    static_assert(MAX_G * QLD >= MAX_G * KEYS, "the probabilities must fit where the queries were");
+
+    const int s = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int G = a.H / a.KV;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    griddep_launch();
+    griddep_wait();
+    const int hi = kv_len[b];
+    const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+    const int pos = hi > 0 ? tok_pos[b] : 0;
+    int key_begin = 0, key_end = 0, page = -1, n_vis = 0, mp = 0;
+    if (hi > 0) {
+        const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
+        n_vis = min(pg1 - pg0, a.S);
+        if (pg1 - pg0 > a.S && tid == 0 && s == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
+        mp = pg0 + s;
+        if (mp < pg1) {
+            key_begin = max(lo, mp * PAGE_TOKENS);
+            key_end = min(hi, (mp + 1) * PAGE_TOKENS);
+            page = page_of(pt, b, mp * PAGE_TOKENS);
+            if (page < 0) {
+                if (tid == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+                key_end = key_begin;
+            }
+            if (cos_t != nullptr && (pos < 0 || pos >= a.n_pos)) {
+                if (tid == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+                key_end = key_begin;
+            }
+        }
+    }
+    const size_t row0 = ((size_t)b * a.H + (size_t)g * G) * a.S + s;
+    if (key_begin >= key_end) {
+        for (int i = tid; i < G; i += blockDim.x) {
+            part_ml[(row0 + (size_t)i * a.S) * 2] = -INFINITY;
+            part_ml[(row0 + (size_t)i * a.S) * 2 + 1] = 0.f;
+        }
+    } else {
+        const int k_first = key_begin % PAGE_TOKENS, k_last = (key_end - 1) % PAGE_TOKENS;
+        const int r_new = (a.write_kv && pos >= mp * PAGE_TOKENS && pos < (mp + 1) * PAGE_TOKENS) ? pos % PAGE_TOKENS : -1;
+        const size_t tile = ((size_t)page * a.KV + g) * PAGE_TOKENS * HD;
+        const uint32_t k_base = smem_u32(k_s), v_base = smem_u32(v_s);
+        for (int i = tid; i < KEYS * CH; i += blockDim.x) {
+            const int r = i / CH, c = i % CH;
+            if (r != r_new) cp_async_16(k_base + swz<CH>(r, c), k_cache + tile + (size_t)r * HD + c * 8, r >= k_first && r <= k_last);
+        }
+        cp_async_commit();
+        for (int i = tid; i < KEYS * CH; i += blockDim.x) {
+            const int r = i / CH, c = i % CH;
+            if (r != r_new) cp_async_16(v_base + swz<CH>(r, c), v_cache + tile + (size_t)r * HD + c * 8, r >= k_first && r <= k_last);
+        }
+        cp_async_commit();
+
+        // ---- the group's queries: norm, rotation, to shared memory as bf16; rows beyond G are zero
+        const bf16* qrow = qkv + (size_t)b * a.ldq;
+        for (int h = warp; h < MAX_G; h += WARPS) {
+            bf16 o[EPL];
+            if (h < G) {
+                float v[EPL];
+                bf16 raw[EPL];
+                const bf16* src = qrow + (size_t)(g * G + h) * HD + lane * EPL;
+                if (EPL == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
+                else *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
+#pragma unroll
+                for (int j = 0; j < EPL; j++) v[j] = to_f32(raw[j]);
+                head_norm_rope<HD>(v, q_gain, a.qk_eps, cos_t, sin_t, pos, lane);
+#pragma unroll
+                for (int j = 0; j < EPL; j++) o[j] = __float2bfloat16_rn(v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < EPL; j++) o[j] = __float2bfloat16_rn(0.f);
+            }
+            if (EPL == 4) *reinterpret_cast<uint2*>(q_s + h * QLD + lane * EPL) = *reinterpret_cast<const uint2*>(o);
+            else *reinterpret_cast<uint32_t*>(q_s + h * QLD + lane * EPL) = *reinterpret_cast<const uint32_t*>(o);
+        }
+        // ---- the new position's k and v, by the CTA that has its page: to the cache and into the tiles
+        if (r_new >= 0 && warp == WARPS - 1) {
+            float kv[EPL];
+            bf16 kraw[EPL], vraw[EPL], ko[EPL];
+            const bf16* ksrc = qrow + (size_t)(a.H + g) * HD + lane * EPL;
+            const bf16* vsrc = qrow + (size_t)(a.H + a.KV + g) * HD + lane * EPL;
+            if (EPL == 4) {
+                *reinterpret_cast<uint2*>(kraw) = *reinterpret_cast<const uint2*>(ksrc);
+                *reinterpret_cast<uint2*>(vraw) = *reinterpret_cast<const uint2*>(vsrc);
+            } else {
+                *reinterpret_cast<uint32_t*>(kraw) = *reinterpret_cast<const uint32_t*>(ksrc);
+                *reinterpret_cast<uint32_t*>(vraw) = *reinterpret_cast<const uint32_t*>(vsrc);
+            }
+#pragma unroll
+            for (int j = 0; j < EPL; j++) kv[j] = to_f32(kraw[j]);
+            head_norm_rope<HD>(kv, k_gain, a.qk_eps, cos_t, sin_t, pos, lane);
+#pragma unroll
+            for (int j = 0; j < EPL; j++) ko[j] = __float2bfloat16_rn(kv[j]);
+            const int d = lane * EPL;                 // EPL elements stay inside one 16-byte chunk
+            bf16* kg = k_cache + tile + (size_t)r_new * HD + d;
+            bf16* vg = v_cache + tile + (size_t)r_new * HD + d;
+            unsigned char* ks = k_s + swz<CH>(r_new, d / 8) + (d % 8) * 2;
+            unsigned char* vs = v_s + swz<CH>(r_new, d / 8) + (d % 8) * 2;
+            if (EPL == 4) {
+                *reinterpret_cast<uint2*>(kg) = *reinterpret_cast<const uint2*>(ko);
+                *reinterpret_cast<uint2*>(vg) = *reinterpret_cast<const uint2*>(vraw);
+                *reinterpret_cast<uint2*>(ks) = *reinterpret_cast<const uint2*>(ko);
+                *reinterpret_cast<uint2*>(vs) = *reinterpret_cast<const uint2*>(vraw);
+            } else {
+                *reinterpret_cast<uint32_t*>(kg) = *reinterpret_cast<const uint32_t*>(ko);
+                *reinterpret_cast<uint32_t*>(vg) = *reinterpret_cast<const uint32_t*>(vraw);
+                *reinterpret_cast<uint32_t*>(ks) = *reinterpret_cast<const uint32_t*>(ko);
+                *reinterpret_cast<uint32_t*>(vs) = *reinterpret_cast<const uint32_t*>(vraw);
+            }
+        }
+        cp_async_wait<1>();                           // K has landed (V may still be in flight)
+        __syncthreads();
+
+        uint32_t qa[KSTEPS][4];
+        {
+            const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                const int col = ks * 16 + c0;
+                qa[ks][0] = *reinterpret_cast<const uint32_t*>(q_s + r0 * QLD + col);
+                qa[ks][1] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * QLD + col);
+                qa[ks][2] = *reinterpret_cast<const uint32_t*>(q_s + r0 * QLD + col + 8);
+                qa[ks][3] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * QLD + col + 8);
+            }
+        }
+        float sc[2][4] = {};
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+            const int key = warp * 16 + (mat >> 1) * 8 + rr;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ks++) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, k_base + swz<CH>(key, ks * 2 + (mat & 1)));
+                mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
+                mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
+            }
+        }
+        const int hrow = lane >> 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int t = 0; t < 2; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = warp * 16 + t * 8 + (lane & 3) * 2 + (e & 1);
+                const bool vis = key >= k_first && key <= k_last;
+                sc[t][e] = vis ? sc[t][e] * a.scale : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sc[t][e]);
+            }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 1));
+            mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 2));
+        }
+        if ((lane & 3) == 0) {
+            red_m[warp][hrow] = mx[0];
+            red_m[warp][hrow + 8] = mx[1];
+        }
+        __syncthreads();
+        float m[2], l[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int h = hrow + 8 * j;
+            m[j] = fmaxf(fmaxf(red_m[0][h], red_m[1][h]), fmaxf(red_m[2][h], red_m[3][h]));
+        }
+#pragma unroll
+        for (int t = 0; t < 2; t++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const float p0 = expf(sc[t][2 * j] - m[j]), p1 = expf(sc[t][2 * j + 1] - m[j]);
+                l[j] += p0 + p1;
+                const int h = hrow + 8 * j, key = warp * 16 + t * 8 + (lane & 3) * 2;
+                *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<unsigned char*>(p_s) + swz<8>(h, key >> 3) + (key & 7) * 2) =
+                    __floats2bfloat162_rn(p0, p1);
+            }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            l[j] += __shfl_xor_sync(0xffffffffu, l[j], 1);
+            l[j] += __shfl_xor_sync(0xffffffffu, l[j], 2);
+        }
+        if ((lane & 3) == 0) {
+            red_l[warp][hrow] = l[0];
+            red_l[warp][hrow + 8] = l[1];
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+
+        float oc[NT][4] = {};
+        {
+            const uint32_t p_base = smem_u32(p_s);
+            const int mat = lane >> 3, rr = lane & 7;
+#pragma unroll
+            for (int ks = 0; ks < KEYS / 16; ks++) {
+                uint32_t pa[4];
+                ldmatrix_x4(pa, p_base + swz<8>((mat & 1) * 8 + rr, ks * 2 + (mat >> 1)));
+#pragma unroll
+                for (int nt = 0; nt < NT; nt += 2) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, v_base + swz<CH>(ks * 16 + (mat & 1) * 8 + rr, warp * (HD / 32) + nt + (mat >> 1)));
+                    mma_bf16(oc[nt], pa, vb[0], vb[1]);
+                    mma_bf16(oc[nt + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int h = hrow + 8 * j;
+            if (h < G) {
+                float* o = part_o + (row0 + (size_t)h * a.S) * HD;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    *reinterpret_cast<float2*>(o + warp * (HD / 4) + nt * 8 + (lane & 3) * 2) = make_float2(oc[nt][2 * j], oc[nt][2 * j + 1]);
+            }
+        }
+        if (tid < G) {
+            part_ml[(row0 + (size_t)tid * a.S) * 2] =
+                fmaxf(fmaxf(red_m[0][tid], red_m[1][tid]), fmaxf(red_m[2][tid], red_m[3][tid]));
+            part_ml[(row0 + (size_t)tid * a.S) * 2 + 1] = (red_l[0][tid] + red_l[1][tid]) + (red_l[2][tid] + red_l[3][tid]);
+        }
+    }
+
+    // ---- the CTA that finishes this (sequence, kv head) last merges the pages
+    __syncthreads();                                  // the CTA's partial is written ...
+    if (tid == 0) {
+        unsigned old;                                 // ... and released with the count (the fence is cumulative)
+        asm volatile("atom.add.acq_rel.gpu.u32 %0, [%1], 1;\n" : "=r"(old) : "l"(counters + (size_t)b * a.KV + g) : "memory");
+        last_flag = old == gridDim.x - 1;
+        if (last_flag) counters[(size_t)b * a.KV + g] = 0;
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    merge_pages<HD>(part_o, part_ml, out + (size_t)b * a.ldo + (size_t)g * G * HD, ((size_t)b * a.H + (size_t)g * G) * a.S,
+                    G, a.S, n_vis, reinterpret_cast<float*>(k_s), reinterpret_cast<float*>(v_s), red_m[0]);
 }
 
 }  // namespace
@@ -323,8 +642,47 @@ MYNAH_API int mynah_attn_decode_tc(
         mynah_launch(attn_decode_tc_kernel<64>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                                    kv_len, pt, a, part_o, part_ml, status);
     if (mynah_check_launch("attn_decode_tc")) return -1;
-    const int threads = HD >= 128 ? 128 : 64;
-    mynah_launch(attn_decode_combine_fast_kernel<bf16>, dim3(H, B), dim3(threads), n_splits * sizeof(float), stream,
-        part_o, part_ml, (bf16*)out, kv_len, window, H, HD, n_splits, ldo);
-    return mynah_check_launch("attn_decode_combine");
+    const size_t dyn = (size_t)n_splits * sizeof(float);
+    MYNAH_REQUIRE(dyn <= MERGE_MAX_BYTES, "attn_decode_tc: %d pages a sequence exceed what the merge holds", n_splits);
+    if (HD == 128)
+        mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+    else
+        mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+    return mynah_check_launch("attn_decode_merge");
+}
+
+// The fused decode attention: q, k, v rows [B, (H + 2 KV) * HD] as the projection left them (with write_kv = 0
+// only the q columns are read and the cache is taken as complete); gains may be null (no per-head norm), the
+// tables may be null (no rotation; else the whole head is rotated). `counters`: B * KV words, zero before the
+// first call. Scratch as mynah_attn_decode.
+MYNAH_API int mynah_attn_decode_fused(
+    const void* qkv, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* q_gain, const void* k_gain, int gain_dtype, float qk_eps,
+    const float* cos_t, const float* sin_t, int n_pos, const int* tok_pos,
+    void* k_cache, void* v_cache, int write_kv, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream) {
+    if (B == 0) return 0;
+    MYNAH_REQUIRE(mynah_attn_decode_tc_supported(H, KV, HD), "attn_decode_fused: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
+    MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0, "attn_decode_fused: row strides %d, %d must be multiples of 8", ldq, ldo);
+    MYNAH_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 65535 && KV <= 65535, "attn_decode_fused: launch too large");
+    MYNAH_REQUIRE(scratch != nullptr && counters != nullptr, "attn_decode_fused: no scratch memory given");
+    MYNAH_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "attn_decode_fused: the two rotation tables go together");
+    MYNAH_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attn_decode_fused: the two gains go together");
+    MYNAH_REQUIRE((size_t)(H / KV) * n_splits * sizeof(float) <= MERGE_MAX_BYTES,
+                  "attn_decode_fused: %d pages a sequence exceed what the merge holds", n_splits);
+    const size_t dyn = 0;
+    const FusedArgs a{H, KV, ldq, ldo, window, n_splits, n_pos, write_kv, 1.0f / sqrtf((float)HD), qk_eps};
+    const PageTable pt{page_indptr, page_ids, page_base, n_pages};
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)B * H * n_splits * HD;
+    const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    const dim3 grid(n_splits, KV, B);
+    if (HD == 128)
+        mynah_launch(attn_decode_fused_kernel<128>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+                     kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
+    else
+        mynah_launch(attn_decode_fused_kernel<64>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+                     kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
+    return mynah_check_launch("attn_decode_fused");
 }

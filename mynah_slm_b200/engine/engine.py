@@ -63,15 +63,32 @@ class Runtime:
         self.tables: dict = {}
         self.status = torch.zeros((1,), dtype=torch.int32, device=device)
         self._scratch: Optional[torch.Tensor] = None
+        self._counters: Optional[torch.Tensor] = None
+        # Buffers that were outgrown stay alive: a captured graph may still hold their address.
+        self._retired: list[torch.Tensor] = []
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+
+    def _no_capture(self, what: str) -> None:
+        if torch.cuda.is_current_stream_capturing():
+            raise EngineError(f"{what} would have to grow during graph capture")
 
     def attn_scratch(self, B: int, H: int, HD: int, splits: int) -> torch.Tensor:
         need = B * H * splits * (HD + 2)
         if self._scratch is None or self._scratch.numel() < need:
-            if torch.cuda.is_current_stream_capturing():
-                raise EngineError("attention scratch would have to grow during graph capture")
+            self._no_capture("attention scratch")
+            if self._scratch is not None:
+                self._retired.append(self._scratch)
             self._scratch = torch.empty((need,), dtype=torch.float32, device=self.device)
         return self._scratch
+
+    def attn_counters(self, n: int) -> torch.Tensor:
+        """Zeroed words that the fused decode attention counts finished pages in (it leaves them zero)."""
+        if self._counters is None or self._counters.numel() < n:
+            self._no_capture("attention counters")
+            if self._counters is not None:
+                self._retired.append(self._counters)
+            self._counters = torch.zeros((max(n, 1024),), dtype=torch.int32, device=self.device)
+        return self._counters
 
 
 class _Staging:

@@ -7,6 +7,8 @@ rounding.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels
@@ -22,12 +24,32 @@ def prefill(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
                                  ctx.cu_q, ctx.kv_len, pages, window, ctx.status)
 
 
+# The one-launch decode attention (norm, rotation, cache write, pages, merge) saves two launches but repeats
+# the query's preparation in every page's CTA, so it pays while a step has few CTAs. Both routes give a
+# sequence the same bits, so the choice may depend on the batch. 0 switches it off.
+FUSED_DECODE_MAX_CTAS = int(os.environ.get("MYNAH_FUSED_ATTN_MAX_CTAS", "1100"))
+# Floats of shared memory that the merge of a (sequence, kv head) has for its pages' weights.
+_MERGE_FLOATS = 2048
+
+
+def _tc_fits(H: int, KV: int, n_splits: int) -> bool:
+    return (H // KV) * n_splits <= _MERGE_FLOATS
+
+
+def decode_fused_ok(dtype: torch.dtype, H: int, KV: int, HD: int, rotary_dim: int, cos, B: int, n_splits: int) -> bool:
+    """Whether the one-launch decode attention takes this layer in this step: the tensor-core sizes, a rotation
+    of the whole head or none, and few enough CTAs."""
+    if B * KV * n_splits > FUSED_DECODE_MAX_CTAS or not kernels.attn_decode_tc_supported(dtype, H, KV, HD):
+        return False
+    return _tc_fits(H, KV, n_splits) and (cos is None or rotary_dim == HD)
+
+
 def decode(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, k_cache: torch.Tensor,
            v_cache: torch.Tensor, pages, window: int, scratch: torch.Tensor) -> None:
     """One query per sequence. Both kernels split a sequence page by page and
     combine in page order, so either gives a sequence the same bits whatever
     the batch."""
-    if kernels.attn_decode_tc_supported(qkv.dtype, H, KV, HD):
+    if kernels.attn_decode_tc_supported(qkv.dtype, H, KV, HD) and _tc_fits(H, KV, ctx.decode_splits):
         kernels.attn_decode_tc(qkv, out, ctx.B, H, KV, HD, k_cache, v_cache, ctx.kv_len, pages, window,
                                ctx.decode_splits, scratch, ctx.status)
     else:

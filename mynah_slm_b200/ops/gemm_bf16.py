@@ -23,8 +23,9 @@ ROUTES: list[Callable[..., Optional[torch.Tensor]]] = []
 USE_TCGEN05 = True
 # The SwiGLU epilogue of the tcgen05 product.
 USE_TCGEN05_SWIGLU = True
-# Rows from which the tcgen05 tiles (128 rows each) are worth their launch.
-TCGEN05_MIN_ROWS = 17
+# Rows from which the tcgen05 tiles (128 rows each) are worth their launch: with one tile of rows or less a
+# product has N / 128 CTAs (8 for the narrow matrices), and the library's split-K kernels are faster.
+TCGEN05_MIN_ROWS = 129
 
 _STATUS: dict = {}
 

@@ -331,6 +331,33 @@ def attn_decode_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int
          window or 0, n_splits, ptr(scratch), ptr(status), stream_ptr())
 
 
+def attn_decode_fused(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,
+                      q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], qk_eps: float,
+                      cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], tok_pos: torch.Tensor,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, write_kv: bool, kv_len: torch.Tensor,
+                      pages: PageTableView, window: int, n_splits: int, scratch: torch.Tensor,
+                      counters: torch.Tensor, status: torch.Tensor) -> None:
+    """Per-head norm, rotation, cache write and attention of a decode step in one launch (bfloat16, head_dim 64
+    or 128, whole-head rotation or none). `qkv` holds the projection's rows; with write_kv False only q is read."""
+    _chk(qkv, "qkv", torch.bfloat16, 2)
+    _chk(out, "attention output", torch.bfloat16, 2)
+    _chk(scratch, "scratch", torch.float32)
+    _chk(counters, "counters", torch.int32)
+    need = B * H * n_splits * (HD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode_fused: scratch holds {scratch.numel()} floats, {need} are needed")
+    if counters.numel() < B * KV:
+        raise KernelError(f"attn_decode_fused: {counters.numel()} counters, {B * KV} are needed")
+    if cos is not None and cos.shape[1] * 2 != HD:
+        raise KernelError("attn_decode_fused: the rotation must cover the whole head")
+    call("mynah_attn_decode_fused", ptr(qkv), ptr(out), B, H, KV, HD, qkv.shape[1], out.shape[1],
+         ptr(q_gain), ptr(k_gain), code(q_gain.dtype) if q_gain is not None else 0, float(qk_eps),
+         ptr(cos), ptr(sin), cos.shape[0] if cos is not None else 0, ptr(tok_pos),
+         ptr(k_cache), ptr(v_cache), 1 if write_kv else 0, ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, n_splits, ptr(scratch), ptr(counters), ptr(status), stream_ptr())
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _chk(logits, "logits", torch.float32, 2)
     B, V = logits.shape

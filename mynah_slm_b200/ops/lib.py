@@ -54,6 +54,12 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P,
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
+    "mynah_attn_decode_fused": [P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                P, P, c_int, c_float,
+                                P, P, c_int, P,
+                                P, P, c_int, P,
+                                P, P, P, c_int,
+                                c_int, c_int, P, P, P, P],
     "mynah_gemv_decode": [P, c_int, c_int, c_int, P, P, P, P, P, c_int, c_float, P, c_int, c_int, c_int, P],
     "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],

@@ -91,8 +91,21 @@ class GQAttention(Mixer):
         writes = cache.writes
         qkv = kernels.linear(h, self.w_qkv if writes else self.w_q)
         pages = ctx.pages[cache.group]
+        from ..ops import attention_dispatch
+        out = torch.empty((T, H * HD), dtype=qkv.dtype, device=qkv.device)
         if self.position.fusable:
             cos, sin, rot = self.position.fused_tables()
+            if ctx.is_decode and attention_dispatch.decode_fused_ok(qkv.dtype, H, KV, HD, rot, cos,
+                                                                    ctx.B, ctx.decode_splits):
+                # norm, rotation, cache write and attention in one launch
+                gains_dtype_ok = self.q_gain is None or self.q_gain.dtype == self.k_gain.dtype
+                if gains_dtype_ok:
+                    kernels.attn_decode_fused(
+                        qkv, out, ctx.B, H, KV, HD, self.q_gain, self.k_gain, self.qk_eps, cos, sin, ctx.tok_pos,
+                        cache.k, cache.v, writes, ctx.kv_len, pages, self.window or 0, ctx.decode_splits,
+                        self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits),
+                        self.runtime.attn_counters(ctx.B * KV), ctx.status)
+                    return kernels.linear(out, self.w_o)
         else:
             q_view = qkv[:, : H * HD].view(T, H, HD)
             k_view = qkv[:, H * HD: (H + KV) * HD].view(T, KV, HD) if writes else None
@@ -103,8 +116,6 @@ class GQAttention(Mixer):
             qkv, H, KV, HD, self.q_gain, self.k_gain, self.qk_eps, cos, sin, rot,
             ctx.tok_seq, ctx.tok_pos, pages,
             cache.k if writes else None, cache.v if writes else None, ctx.status)
-        out = torch.empty((T, H * HD), dtype=qkv.dtype, device=qkv.device)
-        from ..ops import attention_dispatch
         if ctx.is_decode:
             attention_dispatch.decode(qkv, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0,
                                       self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits))
