@@ -1,0 +1,363 @@
+// Prompt attention on the fifth-generation tensor cores, for bfloat16 and head sizes 64 and 128.
+//
+// Same contract as attn_prefill_generic: a ragged batch of prompts (or of pieces of prompts that continue what
+// the cache holds), causal, optionally windowed, grouped-query, K and V read from the paged cache, which already
+// holds this step's keys and values. One CTA takes 128 consecutive queries of one (sequence, head) and walks
+// over the visible keys in tiles of 128 (two pages):
+//
+//   warp 0     one lane brings Q once and then each tile's K and V pages into shared memory with TMA
+//              (cp.async.bulk.tensor, 128-byte swizzle); a page is one box per 64 columns of the head;
+//   warp 1     one lane issues tcgen05.mma: S = Q.K^T (both operands K-major in shared memory) into tensor
+//              memory, and O += P.V with P read from tensor memory and V from shared memory as an MN-major
+//              operand (V is stored [key][dim], which is what the product needs as its B matrix);
+//   warps 2-5  the softmax: each thread owns one query row (one lane of tensor memory). Pass one reads the
+//              scores and finds the row maximum; if the running maximum moved, the row of O is rescaled in
+//              tensor memory; pass two reads the scores again, exponentiates (fp32, base 2 with the scale
+//              folded in), adds up, and writes the probabilities back as bf16 over the scores they came from.
+//
+// Hand-over is by mbarriers: TMA completes transactions on q_full / k_full / v_full; tcgen05.commit arrives on
+// s_full (scores ready, K tile free) and o_done (O updated, V tile free); the softmax warps arrive on p_full.
+// K and V are single tiles: the next K is loaded while the softmax and the second product run, the next V
+// while the next scores and softmax run, and two CTAs per SM cover each other's serial stretches.
+//
+// Keys that a row must not see (later positions, positions before its window, the unused tail of the last
+// page) are masked by selecting -inf for their scores, so whatever the tile holds there cannot reach a result;
+// the rows of V beyond the sequence's end are zeroed in shared memory before the second product, because a
+// probability of zero times a stale NaN would still be NaN.
+//
+// score = dot * (1/sqrtf(head_dim)), maximum subtracted (mynah-slm src/kernels.c:228-250, :207-220).
+// Every wait is bounded (2 s); a wait that runs out sets MYNAH_ST_TIMEOUT, and the CTA drains its copies, frees
+// its tensor memory and returns.
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace tc5;
+
+constexpr int BQ = 128;               // queries per CTA (the lanes of tensor memory)
+constexpr int BKV = 128;              // keys per tile
+constexpr int THREADS = 192;
+constexpr int HALF_BYTES = 128 * 128; // 128 rows of 128 bytes: one 64-column half of a tile
+
+struct PfArgs {
+    int H, KV, ldo;
+    int window;
+    float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e)
+};
+
+// K-major operand, 128-byte swizzle, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand, 128-byte swizzle: a row of 128 bytes holds 64 consecutive MN elements of one k; groups of
+// 8 k 1024 bytes apart (stride offset), the next 64 MN elements `lbo` bytes further on (leading offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// fp32 accumulator, bf16 operands, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t idesc(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+// A wait that all lanes of a warp agree on, so that the warp-wide instructions after it keep all their lanes.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 2)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ cu_q,
+                            const int* __restrict__ kv_len, PageTable pt, PfArgs a, bf16* __restrict__ out,
+                            int* __restrict__ status) {
+    constexpr int HALVES = HD / 64;
+    constexpr int TILE_BYTES = HALVES * HALF_BYTES;            // Q, K and V tiles: 128 rows x HD
+    constexpr int PAGE_BYTES = PAGE_TOKENS * 128;              // one page in one half: 64 rows of 128 bytes
+    constexpr int TMEM_COLS = 256;                             // scores 128 + output HD, rounded to a power of two
+    constexpr int O_COL = 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* k_s = q_s + TILE_BYTES;
+    unsigned char* v_s = k_s + TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + TILE_BYTES);
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 2);
+    const uint32_t s_full = smem_u32(bars + 3), p_full = smem_u32(bars + 4), o_done = smem_u32(bars + 5);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // long tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int q_begin = cu_q[b], n_q = cu_q[b + 1] - q_begin;
+    const int q0 = qt * BQ;
+    if (q0 >= n_q) return;                                     // the whole CTA: nothing is set up yet
+    const int kvl = kv_len[b], past = kvl - n_q;
+    const int rows_valid = min(BQ, n_q - q0);
+    const int kt_hi = (past + q0 + rows_valid - 1) / BKV;      // tile of the last key that the last row sees
+    const int kt_lo = a.window > 0 ? max(0, past + q0 - a.window + 1) / BKV : 0;
+    const int n_tiles = kt_hi - kt_lo + 1;
+    const int kvh = h / (a.H / a.KV);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(v_full, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 4);                                  // one arrival per softmax warp
+        mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {                                       // ---- TMA producer
+            mbar_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+            for (int hf = 0; hf < HALVES; hf++)
+                tma_load_2d(smem_u32(q_s + hf * HALF_BYTES), &map_q, h * HD + hf * 64, q_begin + q0, q_full);
+            int k_issued = 0, v_issued = 0;
+            bool ok = true;
+            for (int j = 0; j < n_tiles && ok; j++) {
+                const int key0 = (kt_lo + j) * BKV;
+                const int p0 = page_of(pt, b, key0);
+                const int p1 = key0 + PAGE_TOKENS < kvl ? page_of(pt, b, key0 + PAGE_TOKENS) : -1;
+                if (p0 < 0 || (key0 + PAGE_TOKENS < kvl && p1 < 0)) {
+                    atomicOr(status, MYNAH_ST_PAGE_RANGE);
+                    break;
+                }
+                const uint32_t bytes = (p1 >= 0 ? 2 : 1) * HALVES * PAGE_BYTES;
+                if (j > 0 && !mbar_wait(s_full, (j - 1) & 1)) {             // the scores of the tile before are done: K is free
+                    atomicOr(status, MYNAH_ST_TIMEOUT);
+                    break;
+                }
+                mbar_expect_tx(k_full, bytes);
+#pragma unroll
+                for (int hf = 0; hf < HALVES; hf++) {
+                    tma_load_2d(smem_u32(k_s + hf * HALF_BYTES), &map_k, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, k_full);
+                    if (p1 >= 0) tma_load_2d(smem_u32(k_s + hf * HALF_BYTES + PAGE_BYTES), &map_k, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, k_full);
+                }
+                k_issued++;
+                if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) {             // the second product of the tile before: V is free
+                    atomicOr(status, MYNAH_ST_TIMEOUT);
+                    break;
+                }
+                mbar_expect_tx(v_full, bytes);
+#pragma unroll
+                for (int hf = 0; hf < HALVES; hf++) {
+                    tma_load_2d(smem_u32(v_s + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full);
+                    if (p1 >= 0) tma_load_2d(smem_u32(v_s + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, v_full);
+                }
+                v_issued++;
+            }
+            // whatever was started still lands in this CTA's shared memory: wait for it before leaving (bounded)
+            mbar_wait(q_full, 0);
+            if (k_issued > 0) mbar_wait(k_full, (k_issued - 1) & 1);
+            if (v_issued > 0) mbar_wait(v_full, (v_issued - 1) & 1);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                       // ---- MMA issuer
+            constexpr uint32_t idesc_s = idesc(BKV, false), idesc_o = idesc(HD, true);
+            const uint32_t t_s = tmem_base, t_o = tmem_base + O_COL;
+            const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+            auto scores = [&]() {
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++) {
+                    const uint32_t off = (k / 4) * HALF_BYTES + (k % 4) * 32;
+                    tc_mma(t_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, k != 0);
+                }
+                tc_commit(s_full);
+            };
+            bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
+            if (ok) {
+                tc_fence_after();
+                scores();
+            }
+            for (int j = 0; j < n_tiles && ok; j++) {
+                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full, j & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < BKV / 16; k++)             // 16 keys a step: 8 columns of packed probabilities, 16 rows of V
+                    tc_mma_ts(t_o, t_s + k * 8, desc_mn_major(v_addr + k * 16 * 128, HALF_BYTES), idesc_o, (j | k) != 0);
+                tc_commit(o_done);
+                if (j + 1 < n_tiles) {
+                    ok = mbar_wait(k_full, (j + 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    scores();
+                }
+            }
+            if (!ok) atomicOr(status, MYNAH_ST_TIMEOUT);
+        }
+    } else {                                                   // ---- softmax: warps 2..5 -> lane quadrants 2,3,0,1
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int qpos = past + q0 + row;
+        const int lo_r = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+        const uint32_t t_s = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s + O_COL;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            const int key0 = (kt_lo + j) * BKV;
+            if (!warp_wait(s_full, j & 1)) { ok = false; break; }
+            tc_fence_after();
+            // does any row of the tile have a key it must not see?
+            const bool need_mask = key0 + BKV - 1 > past + q0 || key0 + BKV > kvl ||
+                                   (a.window > 0 && key0 < past + q0 + BQ - a.window);
+            auto visible = [&](int key) { return key <= qpos && key >= lo_r && key < kvl; };
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                uint32_t r[32];
+                tc_ld32(t_s + c * 32, r);
+                if (need_mask) {
+#pragma unroll
+                    for (int e = 0; e < 32; e++) mx = fmaxf(mx, visible(key0 + c * 32 + e) ? __uint_as_float(r[e]) : -INFINITY);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e++) mx = fmaxf(mx, __uint_as_float(r[e]));
+                }
+            }
+            const float m_new = fmaxf(m, mx * a.scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen nothing yet
+            const float alpha = ex2(m - m_use);                        // 0 while m is -inf
+            if (j > 0) {
+                if (!warp_wait(o_done, (j - 1) & 1)) { ok = false; break; }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {          // the running maximum moved: rescale O's rows
+#pragma unroll 1
+                    for (int c = 0; c < HD / 32; c++) {
+                        uint32_t r[32];
+                        tc_ld32(t_o + c * 32, r);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                        tc_st32(t_o + c * 32, r);
+                    }
+                    tc_wait_st();
+                }
+            }
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BKV / 32; c++) {
+                uint32_t r[32], pk[16];
+                tc_ld32(t_s + c * 32, r);
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+                    if (need_mask) {
+                        s0 = visible(key0 + c * 32 + e) ? s0 : -INFINITY;
+                        s1 = visible(key0 + c * 32 + e + 1) ? s1 : -INFINITY;
+                    }
+                    const float p0 = ex2(fmaf(s0, a.scale_log2, -m_use)), p1 = ex2(fmaf(s1, a.scale_log2, -m_use));   // 2^-inf = 0
+                    sum += p0 + p1;
+                    pk[e >> 1] = pack2(p0, p1);
+                }
+                tc_st16(t_s + c * 16, pk);                     // over scores that have been read already
+            }
+            tc_wait_st();
+            l = l * alpha + sum;
+            m = m_new;
+            if (key0 + BKV > kvl) {                            // the sequence ends inside this tile: zero V beyond its end
+                if (!warp_wait(v_full, j & 1)) { ok = false; break; }
+                if (row >= kvl - key0) {
+#pragma unroll
+                    for (int hf = 0; hf < HALVES; hf++) {
+                        uint4* dst = reinterpret_cast<uint4*>(v_s + hf * HALF_BYTES + row * 128);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                fence_async_smem();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok && !warp_wait(o_done, (n_tiles - 1) & 1)) ok = false;
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* o_row = out + (size_t)(q_begin + q0 + row) * a.ldo + (size_t)h * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; c++) {
+                uint32_t r[32];
+                tc_ld32(t_o + c * 32, r);
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        reinterpret_cast<uint4*>(o_row + c * 32)[i] =
+                            make_uint4(pack2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
+                                       pack2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
+                                       pack2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
+                                       pack2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv));
+                }
+            }
+        } else if (lane == 0) {
+            atomicOr(status, MYNAH_ST_TIMEOUT);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int B, int max_q_len, const int* cu_q,
+           const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
+    constexpr size_t smem = 3 * (size_t)(HD / 64) * HALF_BYTES + 256 + 1024;
+    auto kern = attn_prefill_tcgen05_kernel<HD>;
+    static bool opted = false;
+    if (!opted) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return mynah_fail("attn_prefill_tcgen05: %s", cudaGetErrorString(e));
+        opted = true;
+    }
+    const dim3 grid(ceil_div(max_q_len, BQ), a.H, B);
+    kern<<<grid, THREADS, smem, stream>>>(mq, mk, mv, cu_q, kv_len, pt, a, out, status);
+    return mynah_check_launch("attn_prefill_tcgen05");
+}
+
+}  // namespace
+
+MYNAH_API int mynah_attn_prefill_tcgen05_supported(int H, int KV, int HD) {
+    return (HD == 64 || HD == 128) && KV > 0 && H % KV == 0;
+}
+
+// q: [n_tokens, ldq] bf16 with head h in columns [h * HD, (h + 1) * HD); out: [n_tokens, ldo]; the cache tensors
+// are [n_pages, KV, 64, HD] bf16. Otherwise the arguments of mynah_attn_prefill_generic.
+MYNAH_API int mynah_attn_prefill_tcgen05(
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int* status, cudaStream_t stream) {
+    if (B == 0 || max_q_len == 0 || n_tokens == 0) return 0;
+    MYNAH_REQUIRE(mynah_attn_prefill_tcgen05_supported(H, KV, HD), "attn_prefill_tcgen05: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
+    MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                  ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
+                  "attn_prefill_tcgen05: rows must be 16-byte aligned (strides %d, %d)", ldq, ldo);
+    MYNAH_REQUIRE(B <= 65535 && H <= 65535 && (long long)n_pages * KV * PAGE_TOKENS < (1ll << 31), "attn_prefill_tcgen05: launch too large");
+    MYNAH_REQUIRE(status != nullptr, "attn_prefill_tcgen05: a status word is required");
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_tokens, (long long)H * HD, ldq, BQ, 64)) return -1;
+    if (make_map(&mk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
+    if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
+    const PfArgs a{H, KV, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
+    const PageTable pt{page_indptr, page_ids, page_base, n_pages};
+    if (HD == 128) return launch<128>(mq, mk, mv, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    return launch<64>(mq, mk, mv, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+}

@@ -14,8 +14,16 @@ import torch
 from . import kernels
 
 
+# Switch for the tcgen05 prompt attention (tests compare it with the mma.sync kernel).
+USE_TCGEN05_PREFILL = os.environ.get("MYNAH_TCGEN05_ATTN", "1") != "0"
+
+
 def prefill(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
             k_cache: torch.Tensor, v_cache: torch.Tensor, pages, window: int) -> None:
+    if USE_TCGEN05_PREFILL and kernels.attn_prefill_tcgen05_supported(qkv.dtype, H, KV, HD):
+        kernels.attn_prefill_tcgen05(qkv, out, ctx.B, ctx.max_q_len, H, KV, HD, k_cache, v_cache,
+                                     ctx.cu_q, ctx.kv_len, pages, window, ctx.status)
+        return
     if kernels.attn_prefill_tc_supported(qkv.dtype, H, KV, HD):
         kernels.attn_prefill_tc(qkv, out, ctx.B, ctx.max_q_len, H, KV, HD, k_cache, v_cache,
                                 ctx.cu_q, ctx.kv_len, pages, window, ctx.status)

@@ -292,6 +292,25 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len: int
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
 
 
+def attn_prefill_tcgen05_supported(dtype: torch.dtype, H: int, KV: int, HD: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib.load().mynah_attn_prefill_tcgen05_supported(H, KV, HD))
+
+
+def attn_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len: int, H: int, KV: int, HD: int,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                         pages: PageTableView, window: int, status: torch.Tensor) -> None:
+    """The prompt attention on tcgen05 (bfloat16, head_dim 64 or 128); same contract as attn_prefill_generic."""
+    _chk(qkv, "q", torch.bfloat16, 2)
+    _chk(out, "attention output", torch.bfloat16, 2)
+    _chk(k_cache, "K cache", torch.bfloat16)
+    _chk(v_cache, "V cache", torch.bfloat16)
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError("attn_prefill_tcgen05: the cache tensors must be contiguous")
+    call("mynah_attn_prefill_tcgen05", ptr(qkv), ptr(out), qkv.shape[0], B, max_q_len, H, KV, HD, qkv.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
+
+
 def attn_decode_scratch_floats(B: int, H: int, HD: int, n_splits: int) -> int:
     return int(lib.load().mynah_attn_decode_scratch_floats(B, H, HD, n_splits))
 

@@ -54,6 +54,10 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P,
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
+    "mynah_attn_prefill_tcgen05": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   P, P, P, P,
+                                   P, P, P, c_int,
+                                   c_int, P, P],
     "mynah_attn_decode_fused": [P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                                 P, P, c_int, c_float,
                                 P, P, c_int, P,
@@ -93,6 +97,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_attn_prefill_tc_supported.restype = c_int
     lib.mynah_attn_prefill_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_attn_prefill_tcgen05_supported.restype = c_int
+    lib.mynah_attn_prefill_tcgen05_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_gemm_tcgen05_supported.restype = c_int
     lib.mynah_gemm_tcgen05_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int

@@ -673,14 +673,17 @@ def test_fused_decode_path_equals_the_unfused_one(tmp_path):
     assert rel_err(outs[1], outs[0]) < 1e-2
 
 
-@pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (4, 1, 64, 0), (6, 2, 128, 100), (8, 8, 64, 33)])
-def test_attn_prefill_tensor_cores(H, KV, HD, window):
-    """The tensor-core prompt kernel against the plain attention: a ragged
+@pytest.mark.parametrize("which", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (4, 1, 64, 0), (6, 2, 128, 100), (8, 8, 64, 33), (2, 1, 128, 300)])
+def test_attn_prefill_tensor_cores(H, KV, HD, window, which):
+    """The two tensor-core prompt kernels against the plain attention: a ragged
     batch, prompts that continue earlier ones, a window, NaN in unused page tails."""
     k = _k()
     assert k.attn_prefill_tc_supported(torch.bfloat16, H, KV, HD) and not k.attn_prefill_tc_supported(torch.bfloat16, 4, 2, 48)
+    assert k.attn_prefill_tcgen05_supported(torch.bfloat16, H, KV, HD) and not k.attn_prefill_tcgen05_supported(torch.float32, H, KV, HD)
+    kernel = k.attn_prefill_tc if which == "mma_sync" else k.attn_prefill_tcgen05
     rng = np.random.default_rng(18)
-    lens_q, past = [7, 1, 130, 70, 64, 200], [0, 0, 100, 64, 0, 313]
+    lens_q, past = [7, 1, 130, 70, 64, 200, 515], [0, 0, 100, 64, 0, 313, 0]
     seqs = _attn_case(rng, lens_q, past, H, KV, HD, "bf16")
     n_pages = sum(-(-(p + n) // 64) for p, n in zip(past, lens_q)) + 3
     free = list(np.random.default_rng(20).permutation(n_pages))
@@ -702,7 +705,7 @@ def test_attn_prefill_tensor_cores(H, KV, HD, window):
     cu = torch.tensor(np.cumsum([0] + lens_q), dtype=torch.int32, device=DEV)
     kvl = torch.tensor([p + n for p, n in zip(past, lens_q)], dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    k.attn_prefill_tc(qkv, out, len(seqs), max(lens_q), H, KV, HD, kc, vc, cu, kvl, pt, window, status)
+    kernel(qkv, out, len(seqs), max(lens_q), H, KV, HD, kc, vc, cu, kvl, pt, window, status)
     assert status.item() == 0
     got = out.float().cpu().numpy()
     assert np.isfinite(got).all()
@@ -722,9 +725,9 @@ def test_attn_prefill_tensor_cores(H, KV, HD, window):
         lst = [[6, 0, 5, 1, 4, 2, 3]]
         kc2, vc2 = _paged(kk, lst[0], 7, "bf16"), _paged(vv, lst[0], 7, "bf16")
         o2 = torch.zeros((2, H * HDk), dtype=torch.bfloat16, device=DEV)
-        k.attn_prefill_tc(torch.from_numpy(q.reshape(2, -1)).to(torch.bfloat16).to(DEV), o2, 1, 2, H, KV, HDk, kc2, vc2,
-                          torch.tensor([0, 2], dtype=torch.int32, device=DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
-                          _page_table(lst)(7), win, status)
+        kernel(torch.from_numpy(q.reshape(2, -1)).to(torch.bfloat16).to(DEV), o2, 1, 2, H, KV, HDk, kc2, vc2,
+               torch.tensor([0, 2], dtype=torch.int32, device=DEV), torch.tensor([n], dtype=torch.int32, device=DEV),
+               _page_table(lst)(7), win, status)
         hit = np.abs(o2.float().cpu().numpy()[1, :HDk] - vv[target, 0]).max() < 0.05
         assert hit == visible, (win, target)
 
