@@ -10,15 +10,16 @@
 //   warp 1     one lane issues tcgen05.mma: S = Q.K^T (both operands K-major in shared memory) into tensor
 //              memory, and O += P.V with P read from tensor memory and V from shared memory as an MN-major
 //              operand (V is stored [key][dim], which is what the product needs as its B matrix);
-//   warps 2-5  the softmax: each thread owns one query row (one lane of tensor memory). Pass one reads the
-//              scores and finds the row maximum; if the running maximum moved, the row of O is rescaled in
-//              tensor memory; pass two reads the scores again, exponentiates (fp32, base 2 with the scale
-//              folded in), adds up, and writes the probabilities back as bf16 over the scores they came from.
+//   warps 2-5  the softmax: each thread owns one query row (one lane of tensor memory). It reads the row's
+//              scores, finds the maximum, rescales the row of O in tensor memory if the reference maximum
+//              moved, exponentiates (fp32, base 2 with the scale folded in), adds up, and writes the
+//              probabilities back as bf16 over the scores they came from.
 //
 // Hand-over is by mbarriers: TMA completes transactions on q_full / k_full / v_full; tcgen05.commit arrives on
 // s_full (scores ready, K tile free) and o_done (O updated, V tile free); the softmax warps arrive on p_full.
-// K and V are single tiles: the next K is loaded while the softmax and the second product run, the next V
-// while the next scores and softmax run, and two CTAs per SM cover each other's serial stretches.
+// K, V and the scores have two buffers each: the scores of tile j+1 are computed and its K and V loaded while the
+// softmax works on tile j. A thread keeps its row of 128 scores in registers. The maximum that the sums are
+// scaled by follows the row's true maximum lazily (only when it grows by more than 2^8), so O is rarely rescaled.
 //
 // Keys that a row must not see (later positions, positions before its window, the unused tail of the last
 // page) are masked by selecting -inf for their scores, so whatever the tile holds there cannot reach a result;
@@ -69,7 +70,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ cu_q,
                             const int* __restrict__ kv_len, PageTable pt, PfArgs a, bf16* __restrict__ out,
@@ -77,17 +78,18 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALVES = HD / 64;
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;            // Q, K and V tiles: 128 rows x HD
     constexpr int PAGE_BYTES = PAGE_TOKENS * 128;              // one page in one half: 64 rows of 128 bytes
-    constexpr int TMEM_COLS = 256;                             // scores 128 + output HD, rounded to a power of two
-    constexpr int O_COL = 128;
+    constexpr int TMEM_COLS = 512;                             // two score buffers of 128 columns, the output at 256
+    constexpr int O_COL = 256;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
-    unsigned char* k_s = q_s + TILE_BYTES;
-    unsigned char* v_s = k_s + TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + TILE_BYTES);
-    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 2);
-    const uint32_t s_full = smem_u32(bars + 3), p_full = smem_u32(bars + 4), o_done = smem_u32(bars + 5);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    unsigned char* k_s = q_s + TILE_BYTES;                     // two stages
+    unsigned char* v_s = k_s + 2 * TILE_BYTES;                 // two stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
+    const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 3);   // [2] each, 8 bytes apart
+    const uint32_t s_full = smem_u32(bars + 5), v_free = smem_u32(bars + 7);
+    const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 10);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // long tiles first
@@ -104,9 +106,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        mbar_init(k_full, 1);
-        mbar_init(v_full, 1);
-        mbar_init(s_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(k_full + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1);
+            mbar_init(v_free + 8 * i, 1);
+        }
         mbar_init(p_full, 4);                                  // one arrival per softmax warp
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -121,6 +126,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Tile j uses stage j & 1 of K, V and the scores; its barriers are in their (j >> 1)-th use.
     if (warp == 0) {
         if (lane == 0) {                                       // ---- TMA producer
             mbar_expect_tx(q_full, TILE_BYTES);
@@ -128,8 +134,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int hf = 0; hf < HALVES; hf++)
                 tma_load_2d(smem_u32(q_s + hf * HALF_BYTES), &map_q, h * HD + hf * 64, q_begin + q0, q_full);
             int k_issued = 0, v_issued = 0;
-            bool ok = true;
-            for (int j = 0; j < n_tiles && ok; j++) {
+            for (int j = 0; j < n_tiles; j++) {
+                const int st = j & 1;
+                const uint32_t prev_use = ((j >> 1) & 1) ^ 1;  // parity of the stage's use before this one
                 const int key0 = (kt_lo + j) * BKV;
                 const int p0 = page_of(pt, b, key0);
                 const int p1 = key0 + PAGE_TOKENS < kvl ? page_of(pt, b, key0 + PAGE_TOKENS) : -1;
@@ -138,66 +145,73 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     break;
                 }
                 const uint32_t bytes = (p1 >= 0 ? 2 : 1) * HALVES * PAGE_BYTES;
-                if (j > 0 && !mbar_wait(s_full, (j - 1) & 1)) {             // the scores of the tile before are done: K is free
+                if (j >= 2 && !mbar_wait(s_full + 8 * st, prev_use)) {      // the scores of tile j-2 are done: its K is free
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
                 }
-                mbar_expect_tx(k_full, bytes);
+                unsigned char* kd = k_s + st * TILE_BYTES;
+                mbar_expect_tx(k_full + 8 * st, bytes);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; hf++) {
-                    tma_load_2d(smem_u32(k_s + hf * HALF_BYTES), &map_k, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, k_full);
-                    if (p1 >= 0) tma_load_2d(smem_u32(k_s + hf * HALF_BYTES + PAGE_BYTES), &map_k, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, k_full);
+                    tma_load_2d(smem_u32(kd + hf * HALF_BYTES), &map_k, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
+                    if (p1 >= 0) tma_load_2d(smem_u32(kd + hf * HALF_BYTES + PAGE_BYTES), &map_k, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
                 }
-                k_issued++;
-                if (j > 0 && !mbar_wait(o_done, (j - 1) & 1)) {             // the second product of the tile before: V is free
+                k_issued = j + 1;
+                if (j >= 2 && !mbar_wait(v_free + 8 * st, prev_use)) {      // the second product of tile j-2 is done: its V is free
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
                 }
-                mbar_expect_tx(v_full, bytes);
+                unsigned char* vd = v_s + st * TILE_BYTES;
+                mbar_expect_tx(v_full + 8 * st, bytes);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; hf++) {
-                    tma_load_2d(smem_u32(v_s + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full);
-                    if (p1 >= 0) tma_load_2d(smem_u32(v_s + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, v_full);
+                    tma_load_2d(smem_u32(vd + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
+                    if (p1 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
                 }
-                v_issued++;
+                v_issued = j + 1;
             }
             // whatever was started still lands in this CTA's shared memory: wait for it before leaving (bounded)
             mbar_wait(q_full, 0);
-            if (k_issued > 0) mbar_wait(k_full, (k_issued - 1) & 1);
-            if (v_issued > 0) mbar_wait(v_full, (v_issued - 1) & 1);
+            for (int j = max(0, k_issued - 2); j < k_issued; j++) mbar_wait(k_full + 8 * (j & 1), (j >> 1) & 1);
+            for (int j = max(0, v_issued - 2); j < v_issued; j++) mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {                                       // ---- MMA issuer
             constexpr uint32_t idesc_s = idesc(BKV, false), idesc_o = idesc(HD, true);
-            const uint32_t t_s = tmem_base, t_o = tmem_base + O_COL;
+            const uint32_t t_o = tmem_base + O_COL;
             const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-            auto scores = [&]() {
+            auto scores = [&](int j) {                         // S[j & 1] = Q . K_j^T
+                const int st = j & 1;
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t off = (k / 4) * HALF_BYTES + (k % 4) * 32;
-                    tc_mma(t_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s, k != 0);
+                    tc_mma(tmem_base + st * BKV, desc_k_major(q_addr + off), desc_k_major(k_addr + st * TILE_BYTES + off), idesc_s, k != 0);
                 }
-                tc_commit(s_full);
+                tc_commit(s_full + 8 * st);
             };
             bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
             if (ok) {
                 tc_fence_after();
-                scores();
+                scores(0);
             }
             for (int j = 0; j < n_tiles && ok; j++) {
-                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full, j & 1);
+                const int st = j & 1;
+                if (j + 1 < n_tiles) {                         // the next tile's scores, while the softmax works on this one.
+                    // Their buffer held the probabilities of tile j-1; the product that read them was issued before.
+                    ok = mbar_wait(k_full + 8 * (st ^ 1), ((j + 1) >> 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    scores(j + 1);
+                }
+                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full + 8 * st, (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++)             // 16 keys a step: 8 columns of packed probabilities, 16 rows of V
-                    tc_mma_ts(t_o, t_s + k * 8, desc_mn_major(v_addr + k * 16 * 128, HALF_BYTES), idesc_o, (j | k) != 0);
+                    tc_mma_ts(t_o, tmem_base + st * BKV + k * 8, desc_mn_major(v_addr + st * TILE_BYTES + k * 16 * 128, HALF_BYTES),
+                              idesc_o, (j | k) != 0);
+                tc_commit(v_free + 8 * st);
                 tc_commit(o_done);
-                if (j + 1 < n_tiles) {
-                    ok = mbar_wait(k_full, (j + 1) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
-                    scores();
-                }
             }
             if (!ok) atomicOr(status, MYNAH_ST_TIMEOUT);
         }
@@ -206,37 +220,47 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int row = quad * 32 + lane;
         const int qpos = past + q0 + row;
         const int lo_r = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
-        const uint32_t t_s = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_s + O_COL;
-        float m = -INFINITY, l = 0.f;
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_row + O_COL;
+        float m_ref = -INFINITY, l = 0.f;                      // the maximum that the sums are scaled by, and the row sum
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
+            const int st = j & 1;
             const int key0 = (kt_lo + j) * BKV;
-            if (!warp_wait(s_full, j & 1)) { ok = false; break; }
+            const uint32_t t_s = t_row + st * BKV;
+            if (!warp_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
             tc_fence_after();
+            float s[BKV];
+#pragma unroll
+            for (int c = 0; c < BKV / 32; c++) tc_ld32_nowait(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+#pragma unroll
+            for (int c = 0; c < BKV / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
             // does any row of the tile have a key it must not see?
             const bool need_mask = key0 + BKV - 1 > past + q0 || key0 + BKV > kvl ||
                                    (a.window > 0 && key0 < past + q0 + BQ - a.window);
-            auto visible = [&](int key) { return key <= qpos && key >= lo_r && key < kvl; };
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BKV / 32; c++) {
-                uint32_t r[32];
-                tc_ld32(t_s + c * 32, r);
-                if (need_mask) {
+            if (need_mask) {
 #pragma unroll
-                    for (int e = 0; e < 32; e++) mx = fmaxf(mx, visible(key0 + c * 32 + e) ? __uint_as_float(r[e]) : -INFINITY);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; e++) mx = fmaxf(mx, __uint_as_float(r[e]));
+                for (int e = 0; e < BKV; e++) {
+                    const int key = key0 + e;
+                    s[e] = (key <= qpos && key >= lo_r && key < kvl) ? s[e] : -INFINITY;
                 }
             }
-            const float m_new = fmaxf(m, mx * a.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen nothing yet
-            const float alpha = ex2(m - m_use);                        // 0 while m is -inf
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < BKV; e++) mx = fmaxf(mx, s[e]);
+            const float m_new = mx * a.scale_log2;
+            // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
+            // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
+            // bf16 products carry without loss).
+            float alpha = 1.0f;
+            if (m_new > m_ref + 8.0f || (m_ref == -INFINITY && m_new != -INFINITY)) {
+                alpha = ex2(m_ref - m_new);                    // 0 for the first visible key
+                m_ref = m_new;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;      // a row that has seen nothing yet
             if (j > 0) {
                 if (!warp_wait(o_done, (j - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {          // the running maximum moved: rescale O's rows
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; c++) {
                         uint32_t r[32];
@@ -249,32 +273,26 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             float sum = 0.f;
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < BKV / 32; c++) {
-                uint32_t r[32], pk[16];
-                tc_ld32(t_s + c * 32, r);
+                uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
-                    if (need_mask) {
-                        s0 = visible(key0 + c * 32 + e) ? s0 : -INFINITY;
-                        s1 = visible(key0 + c * 32 + e + 1) ? s1 : -INFINITY;
-                    }
-                    const float p0 = ex2(fmaf(s0, a.scale_log2, -m_use)), p1 = ex2(fmaf(s1, a.scale_log2, -m_use));   // 2^-inf = 0
+                    const float p0 = ex2(fmaf(s[c * 32 + e], a.scale_log2, -m_use));       // 2^-inf = 0
+                    const float p1 = ex2(fmaf(s[c * 32 + e + 1], a.scale_log2, -m_use));
                     sum += p0 + p1;
                     pk[e >> 1] = pack2(p0, p1);
                 }
-                tc_st16(t_s + c * 16, pk);                     // over scores that have been read already
+                tc_st16(t_s + c * 16, pk);                     // over the scores, which are in registers by now
             }
             tc_wait_st();
             l = l * alpha + sum;
-            m = m_new;
             if (key0 + BKV > kvl) {                            // the sequence ends inside this tile: zero V beyond its end
-                if (!warp_wait(v_full, j & 1)) { ok = false; break; }
+                if (!warp_wait(v_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
                 if (row >= kvl - key0) {
 #pragma unroll
                     for (int hf = 0; hf < HALVES; hf++) {
-                        uint4* dst = reinterpret_cast<uint4*>(v_s + hf * HALF_BYTES + row * 128);
+                        uint4* dst = reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + hf * HALF_BYTES + row * 128);
 #pragma unroll
                         for (int i = 0; i < 8; i++) dst[i] = make_uint4(0u, 0u, 0u, 0u);
                     }
@@ -319,7 +337,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int B, int max_q_len, const int* cu_q,
            const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
-    constexpr size_t smem = 3 * (size_t)(HD / 64) * HALF_BYTES + 256 + 1024;
+    constexpr size_t smem = 5 * (size_t)(HD / 64) * HALF_BYTES + 256 + 1024;
     auto kern = attn_prefill_tcgen05_kernel<HD>;
     static bool opted = false;
     if (!opted) {
