@@ -120,104 +120,152 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
 
 // The same pass for head sizes that are a multiple of 32 with the whole head rotated: a lane keeps
 // head_dim/32 consecutive elements in registers, its rotation partner is the lane 16 further on, so
-// nothing goes through shared memory and every access is a vector.
+// nothing goes through shared memory and every access is a vector. A warp takes `hpw` consecutive heads of
+// one token, four at a time with their loads in flight together; the token's position, page, rotation
+// row and the gains are fetched once for all of them.
+template <typename T, int EPL>
+struct HeadVec {
+    T raw[EPL];
+    __device__ __forceinline__ void load(const T* p) {
+        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(p);
+        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(p);
+        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(p);
+        else {
+#pragma unroll
+            for (int j = 0; j < EPL; j++) raw[j] = p[j];
+        }
+    }
+    __device__ __forceinline__ void store(T* p) const {
+        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(raw);
+        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(raw);
+        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(raw);
+        else {
+#pragma unroll
+            for (int j = 0; j < EPL; j++) p[j] = raw[j];
+        }
+    }
+};
+
 template <typename T, int EPL>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                PageTable pt, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                               QkvArgs a, int* __restrict__ status) {
+                               QkvArgs a, int hpw, int* __restrict__ status) {
     griddep_launch();
     griddep_wait();
     constexpr int HD = EPL * 32;
+    constexpr int BATCH = 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = k_cache != nullptr ? a.H + 2 * a.KV : a.H;
+    const int groups = (heads + hpw - 1) / hpw;
     const long long unit = (long long)blockIdx.x * WARPS + warp;
-    if (unit >= (long long)a.T * heads) return;
-    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    if (unit >= (long long)a.T * groups) return;
+    const int t = (int)(unit / groups), h0 = (int)(unit % groups) * hpw, h1 = min(heads, h0 + hpw);
     const int seq = tok_seq[t];
     if (seq < 0) return;
     const int pos = tok_pos[t];
-    const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
-    const int kvh = is_q ? 0 : (is_k ? h - a.H : h - a.H - a.KV);
-    T* src = qkv + (size_t)t * a.ld + (size_t)h * HD + lane * EPL;
-    T* dst = src;
-    if (!is_q) {
+    T* row = qkv + (size_t)t * a.ld + lane * EPL;
+    // the first batch's loads go out before anything that depends on the position
+    HeadVec<T, EPL> in[BATCH];
+#pragma unroll
+    for (int i = 0; i < BATCH; i++)
+        if (h0 + i < h1) in[i].load(row + (size_t)(h0 + i) * HD);
+    const bool rotate = cos_t != nullptr;
+    if (rotate && (pos < 0 || pos >= a.n_pos)) {
+        if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+        return;
+    }
+    float c[EPL], sn[EPL], qg[EPL], kg[EPL];
+    if (rotate) {
+        // lanes 0-15 hold the first half of the head, lanes 16-31 the second
+        const int i0 = (lane & 15) * EPL;
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            c[j] = cos_t[(size_t)pos * (HD / 2) + i0 + j];
+            sn[j] = sin_t[(size_t)pos * (HD / 2) + i0 + j];
+        }
+    }
+    const bool has_gain = q_gain.p != nullptr;
+    if (has_gain) {
+#pragma unroll
+        for (int j = 0; j < EPL; j++) {
+            qg[j] = q_gain.at(lane * EPL + j);
+            kg[j] = k_gain.at(lane * EPL + j);
+        }
+    }
+    size_t cache_row = 0;
+    if (h1 > a.H) {                                        // some head of this warp goes to the cache
         const int page = page_of(pt, seq, pos);
         if (page < 0) {
             if (lane == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
             return;
         }
-        dst = (is_k ? k_cache : v_cache) + (((size_t)page * a.KV + kvh) * PAGE_TOKENS + pos % PAGE_TOKENS) * HD + lane * EPL;
+        cache_row = (size_t)page * a.KV * PAGE_TOKENS + pos % PAGE_TOKENS;
     }
-    T raw[EPL];
-    if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
-    else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
-    else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
-    else {
+    for (int hb = h0; hb < h1; hb += BATCH) {
+        HeadVec<T, EPL> nxt[BATCH];
 #pragma unroll
-        for (int j = 0; j < EPL; j++) raw[j] = src[j];
-    }
-    if (!is_q && !is_k) {                                  // V: copy
-        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(raw);
-        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(raw);
-        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(raw);
-        else {
+        for (int i = 0; i < BATCH; i++)
+            if (hb + BATCH + i < h1) nxt[i].load(row + (size_t)(hb + BATCH + i) * HD);
 #pragma unroll
-            for (int j = 0; j < EPL; j++) dst[j] = raw[j];
+        for (int i = 0; i < BATCH; i++) {
+            const int h = hb + i;
+            if (h >= h1) break;
+            const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
+            const int kvh = is_q ? 0 : (is_k ? h - a.H : h - a.H - a.KV);
+            T* dst = is_q ? row + (size_t)h * HD
+                          : (is_k ? k_cache : v_cache) + (cache_row + (size_t)kvh * PAGE_TOKENS) * HD + lane * EPL;
+            if (!is_q && !is_k) {                          // V: copy
+                in[i].store(dst);
+                continue;
+            }
+            float v[EPL];
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < EPL; j++) {
+                v[j] = to_f32(in[i].raw[j]);
+                ss += v[j] * v[j];
+            }
+            if (has_gain) {
+                ss = warp_sum(ss);
+                const float sc = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+                for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * (is_q ? qg[j] : kg[j]));
+            }
+            if (rotate) {
+#pragma unroll
+                for (int j = 0; j < EPL; j++) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+                    v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
+                }
+            }
+            HeadVec<T, EPL> o;
+#pragma unroll
+            for (int j = 0; j < EPL; j++) o.raw[j] = from_f32<T>(v[j]);
+            o.store(dst);
         }
-        return;
-    }
-    float v[EPL];
-    float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < EPL; j++) {
-        v[j] = to_f32(raw[j]);
-        ss += v[j] * v[j];
-    }
-    const VecRef gain = is_q ? q_gain : k_gain;
-    if (gain.p != nullptr) {
-        ss = warp_sum(ss);
-        const float sc = 1.0f / sqrtf(ss / (float)HD + a.eps);
-#pragma unroll
-        for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * gain.at(lane * EPL + j));
-    }
-    if (cos_t != nullptr) {
-        if (pos < 0 || pos >= a.n_pos) {
-            if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
-            return;
-        }
-        // lanes 0-15 hold the first half of the head, lanes 16-31 the second
-        const int i0 = (lane & 15) * EPL;
-        const float* c = cos_t + (size_t)pos * (HD / 2) + i0;
-        const float* sn = sin_t + (size_t)pos * (HD / 2) + i0;
-#pragma unroll
-        for (int j = 0; j < EPL; j++) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-            v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
-        }
-    }
-    T o[EPL];
-#pragma unroll
-    for (int j = 0; j < EPL; j++) o[j] = from_f32<T>(v[j]);
-    if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
-    else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(o);
-    else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(o);
-    else {
-#pragma unroll
-        for (int j = 0; j < EPL; j++) dst[j] = o[j];
+        for (int i = 0; i < BATCH; i++) in[i] = nxt[i];
     }
 }
 
 template <typename T>
-bool launch_fast(int HD, unsigned blocks, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, const float* cos_t,
+bool launch_fast(int HD, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, const float* cos_t,
                  const float* sin_t, const int* tok_seq, const int* tok_pos, PageTable pt, T* kc, T* vc, QkvArgs a, int* status) {
+    // heads per warp: one while the step is small (latency matters), up to eight when there are many tokens
+    const int heads = kc != nullptr ? a.H + 2 * a.KV : a.H;
+    const long long units1 = (long long)a.T * heads;
+    int hpw = 1;
+    while (hpw < 8 && units1 / hpw > 148 * 16) hpw *= 2;
+    const int groups = (heads + hpw - 1) / hpw;
+    const unsigned blocks = (unsigned)ceil_div_ll((long long)a.T * groups, WARPS);
     switch (HD) {
-        case 32: mynah_launch(qk_norm_rope_store_fast_kernel<T, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
-        case 64: mynah_launch(qk_norm_rope_store_fast_kernel<T, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
-        case 128: mynah_launch(qk_norm_rope_store_fast_kernel<T, 4>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
-        case 256: mynah_launch(qk_norm_rope_store_fast_kernel<T, 8>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, status); return true;
+        case 32: mynah_launch(qk_norm_rope_store_fast_kernel<T, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        case 64: mynah_launch(qk_norm_rope_store_fast_kernel<T, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        case 128: mynah_launch(qk_norm_rope_store_fast_kernel<T, 4>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        case 256: mynah_launch(qk_norm_rope_store_fast_kernel<T, 8>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
         default: return false;
     }
 }
@@ -257,10 +305,10 @@ MYNAH_API int mynah_qk_norm_rope_store(
     // the register-only kernel: the whole head rotated (or none of it), rows 16-byte aligned
     const bool fast_ok = (cos_t == nullptr || rotary_dim == HD) && ld % 8 == 0;
     if (fast_ok && dtype == MYNAH_F32 &&
-        launch_fast<float>(HD, blocks, stream, (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status))
+        launch_fast<float>(HD, stream, (float*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status))
         return mynah_check_launch("qk_norm_rope_store");
     if (fast_ok && dtype == MYNAH_BF16 &&
-        launch_fast<bf16>(HD, blocks, stream, (bf16*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status))
+        launch_fast<bf16>(HD, stream, (bf16*)qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status))
         return mynah_check_launch("qk_norm_rope_store");
     if (dtype == MYNAH_F32)
         mynah_launch(qk_norm_rope_store_kernel<float, float>, dim3(blocks), dim3(WARPS * 32), 0, stream,
