@@ -88,12 +88,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
     const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 3);   // [2] each, 8 bytes apart
     const uint32_t s_full = smem_u32(bars + 5), v_free = smem_u32(bars + 7);
-    const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 10);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 11);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;       // long tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // CTAs start in the order x, y, z: all heads of the last (longest) query tile first, then the tile before, ...
+    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+    const int h = blockIdx.x, b = blockIdx.z;
     const int q_begin = cu_q[b], n_q = cu_q[b + 1] - q_begin;
     const int q0 = qt * BQ;
     if (q0 >= n_q) return;                                     // the whole CTA: nothing is set up yet
@@ -111,8 +112,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(v_full + 8 * i, 1);
             mbar_init(s_full + 8 * i, 1);
             mbar_init(v_free + 8 * i, 1);
+            mbar_init(p_full + 8 * i, 4);                      // one arrival per softmax warp
         }
-        mbar_init(p_full, 4);                                  // one arrival per softmax warp
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -203,7 +204,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tc_fence_after();
                     scores(j + 1);
                 }
-                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full + 8 * st, (j >> 1) & 1);
+                ok = mbar_wait(p_full + 8 * st, (j >> 1) & 1) && mbar_wait(v_full + 8 * st, (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
@@ -257,10 +258,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 m_ref = m_new;
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;      // a row that has seen nothing yet
-            if (j > 0) {
+            // O is touched only when some row of the warp has to be rescaled; then the product of the tile before
+            // must have finished. (A wait that is skipped is not missed later: o_done can be at most one phase
+            // ahead of the tile whose probabilities have not been handed over yet.)
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
                 if (!warp_wait(o_done, (j - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                {
 #pragma unroll 1
                     for (int c = 0; c < HD / 32; c++) {
                         uint32_t r[32];
@@ -301,7 +305,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full + 8 * st);
         }
         if (ok && !warp_wait(o_done, (n_tiles - 1) & 1)) ok = false;
         if (ok) {
@@ -345,7 +349,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return mynah_fail("attn_prefill_tcgen05: %s", cudaGetErrorString(e));
         opted = true;
     }
-    const dim3 grid(ceil_div(max_q_len, BQ), a.H, B);
+    const dim3 grid(a.H, ceil_div(max_q_len, BQ), B);
     kern<<<grid, THREADS, smem, stream>>>(mq, mk, mv, cu_q, kv_len, pt, a, out, status);
     return mynah_check_launch("attn_prefill_tcgen05");
 }
@@ -368,7 +372,7 @@ MYNAH_API int mynah_attn_prefill_tcgen05(
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                   ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
                   "attn_prefill_tcgen05: rows must be 16-byte aligned (strides %d, %d)", ldq, ldo);
-    MYNAH_REQUIRE(B <= 65535 && H <= 65535 && (long long)n_pages * KV * PAGE_TOKENS < (1ll << 31), "attn_prefill_tcgen05: launch too large");
+    MYNAH_REQUIRE(B <= 65535 && ceil_div(max_q_len, BQ) <= 65535 && (long long)n_pages * KV * PAGE_TOKENS < (1ll << 31), "attn_prefill_tcgen05: launch too large");
     MYNAH_REQUIRE(status != nullptr, "attn_prefill_tcgen05: a status word is required");
     CUtensorMap mq, mk, mv;
     if (make_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_tokens, (long long)H * HD, ldq, BQ, 64)) return -1;
