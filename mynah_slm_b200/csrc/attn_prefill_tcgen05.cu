@@ -10,15 +10,16 @@
 //   warp 1     one lane issues tcgen05.mma: S = Q.K^T (both operands K-major in shared memory) into tensor
 //              memory, and O += P.V with P read from tensor memory and V from shared memory as an MN-major
 //              operand (V is stored [key][dim], which is what the product needs as its B matrix);
-//   warps 2-5  the softmax: each thread owns one query row (one lane of tensor memory). It reads the row's
-//              scores, finds the maximum, rescales the row of O in tensor memory if the reference maximum
-//              moved, exponentiates (fp32, base 2 with the scale folded in), adds up, and writes the
-//              probabilities back as bf16 over the scores they came from.
+//   warps 2-9  the softmax: two threads share a query row (one lane of tensor memory), one for each half of a
+//              tile's keys. A thread reads its 64 scores, the two exchange their maxima through shared memory,
+//              rescale their halves of the row of O in tensor memory if the reference maximum moved,
+//              exponentiate (fp32, base 2 with the scale folded in), add up, and write the probabilities back
+//              as bf16 over the scores they came from.
 //
 // Hand-over is by mbarriers: TMA completes transactions on q_full / k_full / v_full; tcgen05.commit arrives on
 // s_full (scores ready, K tile free) and o_done (O updated, V tile free); the softmax warps arrive on p_full.
 // K, V and the scores have two buffers each: the scores of tile j+1 are computed and its K and V loaded while the
-// softmax works on tile j. A thread keeps its row of 128 scores in registers. The maximum that the sums are
+// softmax works on tile j. A thread keeps its 64 scores in registers. The maximum that the sums are
 // scaled by follows the row's true maximum lazily (only when it grows by more than 2^8), so O is rarely rescaled.
 //
 // Keys that a row must not see (later positions, positions before its window, the unused tail of the last
@@ -37,7 +38,7 @@ using namespace tc5;
 
 constexpr int BQ = 128;               // queries per CTA (the lanes of tensor memory)
 constexpr int BKV = 128;              // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 constexpr int HALF_BYTES = 128 * 128; // 128 rows of 128 bytes: one 64-column half of a tile
 
 struct PfArgs {
@@ -88,8 +89,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
     const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 3);   // [2] each, 8 bytes apart
     const uint32_t s_full = smem_u32(bars + 5), v_free = smem_u32(bars + 7);
-    const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 11);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 11), x_full = smem_u32(bars + 12);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    float* xch = reinterpret_cast<float*>(bars + 16);          // [2 buffers][2 groups][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // CTAs start in the order x, y, z: all heads of the last (longest) query tile first, then the tile before, ...
@@ -112,7 +114,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mbar_init(v_full + 8 * i, 1);
             mbar_init(s_full + 8 * i, 1);
             mbar_init(v_free + 8 * i, 1);
-            mbar_init(p_full + 8 * i, 4);                      // one arrival per softmax warp
+            mbar_init(p_full + 8 * i, 8);                      // one arrival per softmax warp
+            mbar_init(x_full + 8 * i, 8);
         }
         mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -216,42 +219,55 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             if (!ok) atomicOr(status, MYNAH_ST_TIMEOUT);
         }
-    } else {                                                   // ---- softmax: warps 2..5 -> lane quadrants 2,3,0,1
+    } else {
+        // ---- softmax: warps 2..5 take the first 64 keys of a tile, warps 6..9 the other 64; a warp reads the lane
+        // quadrant (warp % 4) of tensor memory, so two threads, one in each group, share a query row.
+        const int grp = (warp - 2) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int qpos = past + q0 + row;
         const int lo_r = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
-        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16), t_o = t_row + O_COL;
-        float m_ref = -INFINITY, l = 0.f;                      // the maximum that the sums are scaled by, and the row sum
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t t_o = t_row + O_COL + grp * (HD / 2);   // this thread's half of the row of O
+        constexpr int HALF_KEYS = BKV / 2;
+        float m_ref = -INFINITY, l = 0.f;                      // the maximum that the sums are scaled by; the sum over this thread's keys
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
             const int st = j & 1;
-            const int key0 = (kt_lo + j) * BKV;
+            const uint32_t use = (j >> 1) & 1;
+            const int key0 = (kt_lo + j) * BKV + grp * HALF_KEYS;     // this thread's first key
             const uint32_t t_s = t_row + st * BKV;
-            if (!warp_wait(s_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
+            if (!warp_wait(s_full + 8 * st, use)) { ok = false; break; }
             tc_fence_after();
-            float s[BKV];
+            float s[HALF_KEYS];
 #pragma unroll
-            for (int c = 0; c < BKV / 32; c++) tc_ld32_nowait(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+            for (int c = 0; c < HALF_KEYS / 32; c++) tc_ld32_nowait(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
 #pragma unroll
-            for (int c = 0; c < BKV / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
-            // does any row of the tile have a key it must not see?
-            const bool need_mask = key0 + BKV - 1 > past + q0 || key0 + BKV > kvl ||
+            for (int c = 0; c < HALF_KEYS / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+            // does any row of the tile have a key, among this group's, that it must not see?
+            const bool need_mask = key0 + HALF_KEYS - 1 > past + q0 || key0 + HALF_KEYS > kvl ||
                                    (a.window > 0 && key0 < past + q0 + BQ - a.window);
             if (need_mask) {
 #pragma unroll
-                for (int e = 0; e < BKV; e++) {
+                for (int e = 0; e < HALF_KEYS; e++) {
                     const int key = key0 + e;
                     s[e] = (key <= qpos && key >= lo_r && key < kvl) ? s[e] : -INFINITY;
                 }
             }
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < BKV; e++) mx = fmaxf(mx, s[e]);
-            const float m_new = mx * a.scale_log2;
+            for (int e = 0; e < HALF_KEYS; e++) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+            const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the row's maximum over both groups, through shared memory (two buffers: a value is read before the
+            // barrier of the next tile, and overwritten only after it)
+            xch[(st * 2 + grp) * BQ + row] = mx_own;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_full + 8 * st);
+            if (!warp_wait(x_full + 8 * st, use)) { ok = false; break; }
+            const float m_new = fmaxf(mx_own, xch[(st * 2 + (grp ^ 1)) * BQ + row]) * a.scale_log2;
             // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
             // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
-            // bf16 products carry without loss).
+            // bf16 products carry without loss). Both threads of a row take the same decision.
             float alpha = 1.0f;
             if (m_new > m_ref + 8.0f || (m_ref == -INFINITY && m_new != -INFINITY)) {
                 alpha = ex2(m_ref - m_new);                    // 0 for the first visible key
@@ -264,38 +280,33 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
                 if (!warp_wait(o_done, (j - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                {
 #pragma unroll 1
-                    for (int c = 0; c < HD / 32; c++) {
-                        uint32_t r[32];
-                        tc_ld32(t_o + c * 32, r);
+                for (int c = 0; c < HD / 64; c++) {
+                    uint32_t r[32];
+                    tc_ld32(t_o + c * 32, r);
 #pragma unroll
-                        for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-                        tc_st32(t_o + c * 32, r);
-                    }
-                    tc_wait_st();
+                    for (int e = 0; e < 32; e++) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                    tc_st32(t_o + c * 32, r);
                 }
+                tc_wait_st();
             }
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pk[HALF_KEYS / 2];
 #pragma unroll
-            for (int c = 0; c < BKV / 32; c++) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const float p0 = ex2(fmaf(s[c * 32 + e], a.scale_log2, -m_use));       // 2^-inf = 0
-                    const float p1 = ex2(fmaf(s[c * 32 + e + 1], a.scale_log2, -m_use));
-                    sum += p0 + p1;
-                    pk[e >> 1] = pack2(p0, p1);
-                }
-                tc_st16(t_s + c * 16, pk);                     // over the scores, which are in registers by now
+            for (int e = 0; e < HALF_KEYS; e += 2) {
+                const float p0 = ex2(fmaf(s[e], a.scale_log2, -m_use));           // 2^-inf = 0
+                const float p1 = ex2(fmaf(s[e + 1], a.scale_log2, -m_use));
+                sum4[(e >> 1) & 3] += p0 + p1;
+                pk[e >> 1] = pack2(p0, p1);
             }
+            // over the scores: both groups have theirs in registers since the exchange above
+            tc_st32(t_s + grp * (HALF_KEYS / 2), pk);
             tc_wait_st();
-            l = l * alpha + sum;
-            if (key0 + BKV > kvl) {                            // the sequence ends inside this tile: zero V beyond its end
-                if (!warp_wait(v_full + 8 * st, (j >> 1) & 1)) { ok = false; break; }
-                if (row >= kvl - key0) {
-#pragma unroll
-                    for (int hf = 0; hf < HALVES; hf++) {
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            if ((kt_lo + j) * BKV + BKV > kvl) {               // the sequence ends inside this tile: zero V beyond its end
+                if (!warp_wait(v_full + 8 * st, use)) { ok = false; break; }
+                if (row >= kvl - (kt_lo + j) * BKV) {
+                    for (int hf = grp; hf < HALVES; hf += 2) {
                         uint4* dst = reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + hf * HALF_BYTES + row * 128);
 #pragma unroll
                         for (int i = 0; i < 8; i++) dst[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -307,13 +318,22 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * st);
         }
+        // the row sum over both groups, through the same exchange (its barriers are in use n_tiles by now)
+        if (ok) {
+            const int st = n_tiles & 1;
+            xch[(st * 2 + grp) * BQ + row] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_full + 8 * st);
+            if (!warp_wait(x_full + 8 * st, (n_tiles >> 1) & 1)) ok = false;
+            else l += xch[(st * 2 + (grp ^ 1)) * BQ + row];
+        }
         if (ok && !warp_wait(o_done, (n_tiles - 1) & 1)) ok = false;
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            bf16* o_row = out + (size_t)(q_begin + q0 + row) * a.ldo + (size_t)h * HD;
+            bf16* o_row = out + (size_t)(q_begin + q0 + row) * a.ldo + (size_t)h * HD + grp * (HD / 2);
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; c++) {
+            for (int c = 0; c < HD / 64; c++) {
                 uint32_t r[32];
                 tc_ld32(t_o + c * 32, r);
                 if (row < rows_valid) {
@@ -341,7 +361,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int B, int max_q_len, const int* cu_q,
            const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
-    constexpr size_t smem = 5 * (size_t)(HD / 64) * HALF_BYTES + 256 + 1024;
+    constexpr size_t smem = 5 * (size_t)(HD / 64) * HALF_BYTES + 128 + 2 * 2 * BQ * sizeof(float) + 1024;
     auto kern = attn_prefill_tcgen05_kernel<HD>;
     static bool opted = false;
     if (!opted) {

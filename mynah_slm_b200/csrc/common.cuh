@@ -108,7 +108,11 @@ __device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
 // griddep_launch() lets the next kernel begin its own preamble. Both are
 // no-ops for a kernel launched the ordinary way.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#ifdef MYNAH_PDL_EARLY
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#else
+__device__ __forceinline__ void griddep_launch() {}
+#endif
 
 // 1: launch the decode-path kernels with the programmatic-serialization attribute.
 int mynah_pdl_enabled();
