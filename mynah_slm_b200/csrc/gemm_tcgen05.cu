@@ -45,9 +45,14 @@ enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, M = m, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// Stages of the operand ring: what fits beside the staging tiles.
+__host__ __device__ constexpr int ring_stages(int bn, int ctas) {
+    return (227 * 1024 - 4 * 2 * STAGING_BYTES - 2048) / (A_BYTES + bn * BK * 2 / ctas) > 8
+               ? 8 : (227 * 1024 - 4 * 2 * STAGING_BYTES - 2048) / (A_BYTES + bn * BK * 2 / ctas);
 }
 
 __device__ __forceinline__ float sigmoid_stable(float v) {
@@ -58,16 +63,21 @@ __device__ __forceinline__ float sigmoid_stable(float v) {
 struct GemmShape {
     int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
     int up_offset;
-    int m_tiles, n_tiles;
+    int m_tiles, n_tiles; // m_tiles: tiles of 128 rows (one CTA) or 256 rows (a pair of CTAs)
 };
 
-template <int BN, int EPI>
+// CTAS = 2: two CTAs of a cluster share a tile of 256 x BN. Each brings its own 128 rows of A and half of the
+// BN rows of W (for SwiGLU: one the gate rows, the other the up rows), the even CTA issues
+// tcgen05.mma.cta_group::2 for both, and each reads its 128 rows of the accumulator out of its own tensor
+// memory. A CTA then loads 16 + BN/8 KB a k-block instead of 16 + BN/4, which is what the ring's depth and
+// the L2's bandwidth have to cover.
+template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status) {
-    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int B_BYTES = BN * BK * 2 / CTAS;                      // this CTA's rows of W
     constexpr int STAGE = A_BYTES + B_BYTES;
-    constexpr int STAGES = BN == 256 ? 4 : 6;
+    constexpr int STAGES = ring_stages(BN, CTAS);
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : BN;           // output columns of a tile
     constexpr int CHUNK = EPI == EPI_F32 ? 32 : 64;                  // output columns per staged store (128 bytes per row)
     extern __shared__ unsigned char smem_raw[];
@@ -82,6 +92,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (g.K + BK - 1) / BK;
     const int total_tiles = g.m_tiles * g.n_tiles;
+    const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;         // 0 leads
+    const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;  // a unit walks over tiles: a CTA or a pair
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -90,18 +102,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full0 + 8 * b, 1);
-            mbar_init(acc_empty0 + 8 * b, 4);                        // one arrival per epilogue warp
+            mbar_init(acc_empty0 + 8 * b, 4 * CTAS);                 // one arrival per epilogue warp (of both CTAs, on the leader's)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CTAS == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();                               // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -109,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {                                             // ---- TMA producer
             int it = 0;                                              // k-blocks issued, over all tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
                 const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
                 for (int kb = 0; kb < nk; kb++, it++) {
                     const int s = it % STAGES;
@@ -121,6 +139,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     const uint32_t a_dst = smem_u32(smem + s * STAGE), b_dst = a_dst + A_BYTES;
+                    if (CTAS == 2) {
+                        // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
+                        if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);
+                        tma_load_2d_pair(a_dst, &map_a, kb * BK, (m_tile * 2 + rank) * BM, full0 + 8 * s);
+                        const int w_row = EPI == EPI_SWIGLU ? (rank == 0 ? n_tile * 128 : g.up_offset + n_tile * 128)
+                                                            : n_tile * BN + rank * (BN / 2);
+                        tma_load_2d_pair(b_dst, &map_b, kb * BK, w_row, full0 + 8 * s);
+                        continue;
+                    }
                     mbar_expect_tx(full0 + 8 * s, STAGE);
                     tma_load_2d(a_dst, &map_a, kb * BK, m_tile * BM, full0 + 8 * s);
                     if (EPI == EPI_SWIGLU) {                         // 128 gate rows, then their 128 up rows
@@ -133,17 +160,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
-            if (!ok) {
-                // copies that were started still land in this CTA's shared memory: wait for them (bounded)
+            if (!ok && rank == 0) {
+                // copies that were started still land in shared memory: wait for them (bounded)
                 for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {                                             // ---- MMA issuer
-            constexpr uint32_t idesc = umma_idesc(BN);
+        if (lane == 0 && rank == 0) {                                // ---- MMA issuer (of the pair: the leader's)
+            constexpr uint32_t idesc = umma_idesc(BM * CTAS, BN);
             int it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+            for (int tile = unit; tile < total_tiles && ok; tile += n_units, local++) {
                 const int buf = local & 1;
                 const uint32_t use = (local >> 1) & 1;
                 if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1) || *abort_flag) {   // the epilogue has read this buffer out
@@ -165,18 +192,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + s * STAGE), b_addr = a_addr + A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++)
-                        tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
-                    tc_commit(empty0 + 8 * s);                       // the stage is free once these have read it
+                    for (int k = 0; k < BK / 16; k++) {
+                        if (CTAS == 2) tc_mma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+                        else tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+                    }
+                    // the stage is free (in both CTAs) once these have read it
+                    if (CTAS == 2) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
-                tc_commit(acc_full0 + 8 * buf);                      // arrives when the tile is accumulated
+                // arrives when the tile is accumulated
+                if (CTAS == 2) tc_commit_pair(acc_full0 + 8 * buf); else tc_commit(acc_full0 + 8 * buf);
             }
         }
     } else {                                                         // ---- epilogue: warps 2..5 -> lane quadrants 2,3,0,1
         const int quad = warp & 3;
         unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
         int local = 0, n_store = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, local++) {
+        for (int tile = unit; tile < total_tiles; tile += n_units, local++) {
             const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
             const int buf = local & 1;
             const uint32_t use = (local >> 1) & 1;
@@ -189,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tc_fence_after();
             const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
-            const int row0 = m_tile * BM + quad * 32;
+            const int row0 = (m_tile * CTAS + rank) * BM + quad * 32;
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += CHUNK, n_store++) {
                 unsigned char* st = my_stage + (n_store & 1) * STAGING_BYTES;
@@ -248,24 +279,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // this warp has read its quadrant of the buffer out
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+            if (lane == 0) {
+                if (CTAS == 2) mbar_arrive_leader(acc_empty0 + 8 * buf); else mbar_arrive(acc_empty0 + 8 * buf);
+            }
         }
         if (lane == 0) tma_store_wait_all();
     }
     tc_fence_before();
     __syncthreads();
+    if (CTAS == 2) cluster_sync_all();                               // neither CTA leaves while the other may still touch it
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        if (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int CTAS>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
                 int sm_count, int* status, cudaStream_t stream) {
-    constexpr int STAGES = BN == 256 ? 4 : 6;
-    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 4 * 2 * STAGING_BYTES + 256 + 1024;
-    auto kern = gemm_tcgen05_kernel<BN, EPI>;
+    constexpr int STAGES = ring_stages(BN, CTAS);
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2 / CTAS) + 4 * 2 * STAGING_BYTES + 256 + 1024;
+    auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS>;
     static bool opted = false;
     if (!opted) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -274,13 +309,37 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     }
     GemmShape g;
     g.M = M; g.N = N; g.K = K; g.up_offset = up_offset;
-    g.m_tiles = ceil_div(M, BM);
+    g.m_tiles = ceil_div(M, BM * CTAS);
     g.n_tiles = EPI == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, BN);
     const long long tiles = (long long)g.m_tiles * g.n_tiles;
     MYNAH_REQUIRE(tiles < (1ll << 30), "gemm_tcgen05: too many tiles");
-    const int ctas = (int)(tiles < sm_count ? tiles : sm_count);
-    kern<<<ctas, THREADS, smem, stream>>>(ma, mb, mc, g, status);
+    const int max_units = sm_count / CTAS;
+    const int units = (int)(tiles < max_units ? tiles : max_units);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units * CTAS);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CTAS == 2 ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, g, status);
+    if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
     return mynah_check_launch("gemm_tcgen05");
+}
+
+// 1 (default): products of 256 rows or more run on pairs of CTAs (cta_group::2). MYNAH_GEMM_PAIR=0 keeps single CTAs.
+bool pair_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MYNAH_GEMM_PAIR");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 }  // namespace
@@ -302,20 +361,27 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
                   "gemm_tcgen05: operands must be 16-byte aligned and the output pitch a multiple of 16 bytes");
     MYNAH_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
     if (sm_count <= 0) sm_count = 148;
+    // Pairs pay once a unit has tiles to run one after the other (the ring then stays full across tiles); with
+    // one tile a unit, as for a 2,048-token prompt of a small model, single CTAs measured the same or better.
+    const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * (epilogue == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, 256));
+    const bool pair = pair_enabled() && M >= 2 * BM && sm_count >= 2 && pair_tiles >= 2 * (sm_count / 2);
+    // wide tiles unless they would leave most SMs idle
+    const long long units = pair ? sm_count / 2 : sm_count;
+    const bool wide = epilogue == EPI_SWIGLU || (long long)ceil_div(N, 256) * ceil_div(M, pair ? 2 * BM : BM) * 10 >= units * 8 || N > 4096;
+    const int w_box_rows = pair ? (wide ? 128 : 64) : 128;           // rows of W that one copy brings
     CUtensorMap ma, mb, mc;
     if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
-    if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, epilogue == EPI_SWIGLU ? 2LL * N : N, K, K, 128, BK)) return -1;
+    if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, epilogue == EPI_SWIGLU ? 2LL * N : N, K, K, w_box_rows, BK)) return -1;
     if (epilogue == EPI_F32) {
         if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32)) return -1;
     } else {
         if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
     }
-    if (epilogue == EPI_SWIGLU) return launch_gemm<256, EPI_SWIGLU>(ma, mb, mc, M, N, K, N, sm_count, status, stream);
-    // narrow tiles when wide ones would leave most SMs idle
-    const bool wide = (long long)ceil_div(N, 256) * ceil_div(M, BM) >= 120 || N > 4096;
-    if (epilogue == EPI_F32)
-        return wide ? launch_gemm<256, EPI_F32>(ma, mb, mc, M, N, K, 0, sm_count, status, stream)
-                    : launch_gemm<128, EPI_F32>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
-    return wide ? launch_gemm<256, EPI_BF16>(ma, mb, mc, M, N, K, 0, sm_count, status, stream)
-                : launch_gemm<128, EPI_BF16>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
+#define MYNAH_GEMM_GO(BN_, EPI_) \
+    (pair ? launch_gemm<BN_, EPI_, 2>(ma, mb, mc, M, N, K, epilogue == EPI_SWIGLU ? N : 0, sm_count, status, stream) \
+          : launch_gemm<BN_, EPI_, 1>(ma, mb, mc, M, N, K, epilogue == EPI_SWIGLU ? N : 0, sm_count, status, stream))
+    if (epilogue == EPI_SWIGLU) return MYNAH_GEMM_GO(256, EPI_SWIGLU);
+    if (epilogue == EPI_F32) return wide ? MYNAH_GEMM_GO(256, EPI_F32) : MYNAH_GEMM_GO(128, EPI_F32);
+    return wide ? MYNAH_GEMM_GO(256, EPI_BF16) : MYNAH_GEMM_GO(128, EPI_BF16);
+#undef MYNAH_GEMM_GO
 }
