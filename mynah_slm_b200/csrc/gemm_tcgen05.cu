@@ -55,10 +55,15 @@ __host__ __device__ constexpr int ring_stages(int bn, int ctas) {
                ? 8 : (227 * 1024 - 4 * 2 * STAGING_BYTES - 2048) / (A_BYTES + bn * BK * 2 / ctas);
 }
 
+// The stable form of the reference's sigmoid (mynah-slm src/kernels.c:193-205: e^-|v| never overflows), on the
+// hardware's base-2 exponential and reciprocal: a relative error of a few 2^-23 in a value that is rounded to
+// bf16 right after. The accurate library forms cost four times the instructions and left the epilogue warps,
+// not the tensor cores, as the kernel's limit.
 __device__ __forceinline__ float sigmoid_stable(float v) {
-    // e^-|v| never overflows; the select keeps both branches of the reference's stable form exact
-    const float e = expf(-fabsf(v));
-    return (v >= 0.f ? 1.0f : e) / (1.0f + e);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-fabsf(v) * 1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return (v >= 0.f ? 1.0f : e) * r;
 }
 struct GemmShape {
     int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
