@@ -39,6 +39,13 @@ QWEN3_0_6B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hi
                   vocab_size=151936, rope_theta=1000000, rms_norm_eps=1e-6, tie_word_embeddings=True,
                   max_position_embeddings=40960, hidden_act="silu", attention_bias=False, rope_scaling=None,
                   use_sliding_window=False, sliding_window=None, eos_token_id=151645)
+# Other layer sizes, for the short single-phase runs (--only) that check and profile the kernels at further sizes
+SHAPES = {
+    "0.6b": {},
+    "4b": dict(num_hidden_layers=36, hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, intermediate_size=9728),
+    "8b": dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, intermediate_size=12288,
+               tie_word_embeddings=False),
+}
 PROMPT_LEN, CTX_LEN, PREFILL_TOKENS = 2048, 4096, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -134,6 +141,7 @@ def main() -> int:
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one small phase and print a short line (for profiling a kernel on a small case)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
+    ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -158,6 +166,8 @@ def main() -> int:
     from mynah_slm_b200.weights.random_init import write_random_model
 
     cfg = dict(QWEN3_0_6B)
+    if args.only:
+        cfg.update(SHAPES[args.shape])
     layers_model = cfg["num_hidden_layers"]
     layers = args.layers or layers_model
     cfg["num_hidden_layers"] = layers
@@ -218,14 +228,14 @@ def main() -> int:
     if args.only == "decode":
         ms, launches, mean_ctx = device_decode(B, K, W)
         gbs = decode_bytes(cfg, layers, B, mean_ctx) / (ms / K / 1e3) / 1e9
-        print(json.dumps({"only": "decode", "batch": B, "layers": layers, "prompt_len": prompt_len, "steps": K,
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": B, "layers": layers, "prompt_len": prompt_len, "steps": K,
                           "ms_per_step": round(ms / K, 4), "tokens_per_s": round(B * K / (ms / 1e3), 1),
                           "GBps": round(gbs, 1), "launches": launches}))
         return 0
     if args.only == "prefill":
         pre_ms = time_prefill(max(1, K))
         fl = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
-        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+        print(json.dumps({"only": "prefill", "shape": args.shape, "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                           "tokens_per_s": round(PREFILL_TOKENS / (pre_ms / 1e3), 1),
                           "TFLOPs": round(fl / (pre_ms / 1e3) / 1e12, 1)}))
         return 0

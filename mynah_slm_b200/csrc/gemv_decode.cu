@@ -215,7 +215,8 @@ template <int EPI, bool NORM>
 int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
     auto kern = gemv_decode_kernel<EPI, NORM>;
     static int allowed = 0;                           // per instantiation: the largest size opted in to so far
-    if (smem > 48 * 1024 && (int)smem > allowed) {
+    // dynamic plus the kernel's static shared memory (up to 9 KB) must stay under 48 KB unless opted in
+    if (smem > 36 * 1024 && (int)smem > allowed) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return mynah_fail("gemv_decode: %s", cudaGetErrorString(e));
         allowed = (int)smem;

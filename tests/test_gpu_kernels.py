@@ -598,7 +598,8 @@ def test_attn_decode_fused_is_norm_rope_store_and_attention(H, KV, HD, window, w
     assert int(counters.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 30000, 1024), (2, 20, 64)])
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 30000, 1024), (2, 20, 64),
+                                   (8, 328, 2560), (2, 264, 9728)])      # rows of 41 KB: just under the opt-in limit; long rows
 def test_gemv_decode_fused_kernels(M, N, K):
     """The decode products with their fusions: plain rows, fp32 rows, the norm
     prologue with the residual add, and the SwiGLU epilogue."""
