@@ -59,9 +59,16 @@ __device__ __forceinline__ float stable_sigmoid_f(float v) {
     return (v >= 0.f ? 1.0f : e) / (1.0f + e);
 }
 
-template <int EPI, bool NORM>
+// MODE: how the input rows reach the tensor cores. ROWS_DIRECT: each lane loads its fragments straight from global
+// memory (no shared memory, any K); ROWS_STAGED: the CTA copies the rows into shared memory first (a little faster
+// while they are small); ROWS_NORM: the norm prologue computes them into shared memory.
+enum RowsMode : int { ROWS_DIRECT = 0, ROWS_STAGED = 1, ROWS_NORM = 2 };
+
+template <int EPI, int MODE>
 __global__ void __launch_bounds__(THREADS)
 gemv_decode_kernel(GemvArgs a) {
+    constexpr bool NORM = MODE == ROWS_NORM;
+    constexpr bool STAGED = MODE != ROWS_DIRECT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* xs = reinterpret_cast<bf16*>(smem_raw);                    // [MAX_M or 8][K + XPAD]
     __shared__ float red[WARPS][32][EPI == EPI_SWIGLU ? 8 : 4];
@@ -74,6 +81,16 @@ gemv_decode_kernel(GemvArgs a) {
     // ---- the first weights of this CTA, before anything an earlier kernel wrote is touched: the
     // weights are never written, so their loads may run while the kernel before this one finishes
     uint4 wv[4], uv[4];
+    uint4 xa[4], xb[4];                                              // without the norm: the rows' fragments, straight from global memory
+    auto load_rows = [&](int kb0) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int kb = kb0 + u * WARPS;
+            const bool ok = kb < nkb;
+            xa[u] = ok && g < M ? *reinterpret_cast<const uint4*>(a.x_bf16 + (size_t)g * K + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+            xb[u] = ok && g + 8 < M ? *reinterpret_cast<const uint4*>(a.x_bf16 + (size_t)(g + 8) * K + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        }
+    };
     auto load_weights = [&](int n0, int kb0) {
         const int row = n0 + g;
         const bool row_ok = row < a.N;
@@ -130,17 +147,19 @@ gemv_decode_kernel(GemvArgs a) {
                     xs[m * ldx + i] = __float2bfloat16_rn((v * s) * a.gain.at(i));
                 }
         }
-    } else {
+    } else if (STAGED) {
         for (int i = tid; i < M * (K / 8); i += THREADS) {
             const int m = i / (K / 8), c = i % (K / 8);
             *reinterpret_cast<uint4*>(xs + m * ldx + c * 8) = *reinterpret_cast<const uint4*>(a.x_bf16 + (size_t)m * K + c * 8);
         }
     }
-    for (int i = tid; i < (rows_x - M) * (K / 8); i += THREADS) {   // rows beyond the batch are zero
-        const int m = M + i / (K / 8), c = i % (K / 8);
-        *reinterpret_cast<uint4*>(xs + m * ldx + c * 8) = make_uint4(0, 0, 0, 0);
+    if (STAGED) {
+        for (int i = tid; i < (rows_x - M) * (K / 8); i += THREADS) {   // rows beyond the batch are zero
+            const int m = M + i / (K / 8), c = i % (K / 8);
+            *reinterpret_cast<uint4*>(xs + m * ldx + c * 8) = make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
     }
-    __syncthreads();
 
     for (int gi = 0; gi < a.groups_per_cta; gi++) {
         const int n0 = (blockIdx.x * a.groups_per_cta + gi) * 8;
@@ -148,15 +167,21 @@ gemv_decode_kernel(GemvArgs a) {
         float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
         for (int kb0 = warp; kb0 < nkb; kb0 += WARPS * 4) {
             if (gi != 0 || kb0 != warp) load_weights(n0, kb0);       // the first batch is already here
+            if (!STAGED) load_rows(kb0);                             // (from L1 after the CTA's first group of rows)
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const int kb = kb0 + u * WARPS;
                 if (kb < nkb) {                                      // uniform over the warp
-                    const uint4 xa = *reinterpret_cast<const uint4*>(xs + g * ldx + kb * 32 + t * 8);
-                    uint4 xb = make_uint4(0, 0, 0, 0);
-                    if (rows_x == 16) xb = *reinterpret_cast<const uint4*>(xs + (g + 8) * ldx + kb * 32 + t * 8);
-                    const uint32_t a1[4] = {xa.x, xb.x, xa.y, xb.y};   // k-permuted: both operands use the same order
-                    const uint32_t a2[4] = {xa.z, xb.z, xa.w, xb.w};
+                    uint4 xa_u, xb_u = make_uint4(0, 0, 0, 0);
+                    if (STAGED) {
+                        xa_u = *reinterpret_cast<const uint4*>(xs + g * ldx + kb * 32 + t * 8);
+                        if (rows_x == 16) xb_u = *reinterpret_cast<const uint4*>(xs + (g + 8) * ldx + kb * 32 + t * 8);
+                    } else {
+                        xa_u = xa[u];
+                        xb_u = xb[u];
+                    }
+                    const uint32_t a1[4] = {xa_u.x, xb_u.x, xa_u.y, xb_u.y};   // k-permuted: both operands use the same order
+                    const uint32_t a2[4] = {xa_u.z, xb_u.z, xa_u.w, xb_u.w};
                     mma_bf16(c0, a1, wv[u].x, wv[u].y);
                     mma_bf16(c0, a2, wv[u].z, wv[u].w);
                     if (EPI == EPI_SWIGLU) {
@@ -211,9 +236,9 @@ gemv_decode_kernel(GemvArgs a) {
     }
 }
 
-template <int EPI, bool NORM>
+template <int EPI, int MODE>
 int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
-    auto kern = gemv_decode_kernel<EPI, NORM>;
+    auto kern = gemv_decode_kernel<EPI, MODE>;
     static int allowed = 0;                           // per instantiation: the largest size opted in to so far
     // dynamic plus the kernel's static shared memory (up to 9 KB) must stay under 48 KB unless opted in
     if (smem > 36 * 1024 && (int)smem > allowed) {
@@ -229,9 +254,7 @@ int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
 
 // Whether the kernel takes these sizes.
 MYNAH_API int mynah_gemv_decode_supported(int M, int N, int K) {
-    if (M < 1 || M > MAX_M || N < 1 || K < 32 || K % 32 != 0) return 0;
-    const size_t smem = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
-    return smem <= 200 * 1024;
+    return M >= 1 && M <= MAX_M && N >= 1 && K >= 32 && K % 32 == 0;
 }
 
 // epilogue: 0 bf16 rows [M, N]; 1 SwiGLU: W holds N gate rows then N up rows, out is [M, N] bf16; 2 fp32 rows.
@@ -253,14 +276,21 @@ MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* 
     const int target = (sm_count > 0 ? sm_count : 148) * 2;          // about two CTAs per SM
     a.groups_per_cta = groups <= target ? 1 : ceil_div(groups, target);
     const int n_ctas = ceil_div(groups, a.groups_per_cta);
-    const size_t smem = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
     const bool norm = x_res != nullptr;
-    switch (epilogue * 2 + (norm ? 1 : 0)) {
-        case 0: return launch<EPI_BF16, false>(a, n_ctas, smem, stream);
-        case 1: return launch<EPI_BF16, true>(a, n_ctas, smem, stream);
-        case 2: return launch<EPI_SWIGLU, false>(a, n_ctas, smem, stream);
-        case 3: return launch<EPI_SWIGLU, true>(a, n_ctas, smem, stream);
-        case 4: return launch<EPI_F32, false>(a, n_ctas, smem, stream);
-        default: return launch<EPI_F32, true>(a, n_ctas, smem, stream);
+    const size_t rows_bytes = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
+    MYNAH_REQUIRE(!norm || rows_bytes <= 200 * 1024, "gemv_decode: rows of K=%d do not fit shared memory for the norm prologue", K);
+    // staged while the rows need no opt-in (several CTAs fit an SM); beyond that, straight from global memory
+    const int mode = norm ? ROWS_NORM : (rows_bytes <= 36 * 1024 ? ROWS_STAGED : ROWS_DIRECT);
+    const size_t smem = mode == ROWS_DIRECT ? 0 : rows_bytes;
+    switch (epilogue * 3 + mode) {
+        case 0: return launch<EPI_BF16, ROWS_DIRECT>(a, n_ctas, smem, stream);
+        case 1: return launch<EPI_BF16, ROWS_STAGED>(a, n_ctas, smem, stream);
+        case 2: return launch<EPI_BF16, ROWS_NORM>(a, n_ctas, smem, stream);
+        case 3: return launch<EPI_SWIGLU, ROWS_DIRECT>(a, n_ctas, smem, stream);
+        case 4: return launch<EPI_SWIGLU, ROWS_STAGED>(a, n_ctas, smem, stream);
+        case 5: return launch<EPI_SWIGLU, ROWS_NORM>(a, n_ctas, smem, stream);
+        case 6: return launch<EPI_F32, ROWS_DIRECT>(a, n_ctas, smem, stream);
+        case 7: return launch<EPI_F32, ROWS_STAGED>(a, n_ctas, smem, stream);
+        default: return launch<EPI_F32, ROWS_NORM>(a, n_ctas, smem, stream);
     }
 }

@@ -129,7 +129,7 @@ def gemv_decode_supported(M: int, N: int, K: int) -> bool:
 def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """x: bf16 rows [M, K] or a NormedInput. epilogue 0: bf16, 1: SwiGLU (w holds N gate rows then N up rows), 2: fp32."""
     K = w.shape[1]
-    if isinstance(x, NormedInput) and x._h is None and x.shape[0] > FUSED_NORM_MAX_ROWS:
+    if isinstance(x, NormedInput) and x._h is None and (x.shape[0] > FUSED_NORM_MAX_ROWS or K > FUSED_NORM_MAX_K):
         x.materialize()
     if isinstance(x, NormedInput) and x._h is None:
         st = x.stream
@@ -165,6 +165,7 @@ def _fusable(x, w: torch.Tensor, N: int) -> bool:
 
 
 FUSED_NORM_MAX_ROWS = 2     # beyond this every CTA recomputing the norm costs more than a separate kernel
+FUSED_NORM_MAX_K = 12288    # the norm prologue keeps its rows in shared memory
 GEMV_MAX_OUT_ROWS = 32768   # wider products (the output head) stream better through the library for now
 
 
