@@ -262,11 +262,97 @@ __device__ int block_argmax(const float* __restrict__ row, int V, Shared& sh, fl
     return bi == 0x7fffffff ? 0 : bi;
 }
 
+// The first maximum of a row in two steps, for vocabularies that one CTA reads too slowly: ARGMAX_PARTS CTAs
+// each take a contiguous piece of the row, then the sampling CTA reduces their results. Ties go to the lowest
+// index in both steps, so the result is the one-CTA result.
+constexpr int ARGMAX_PARTS = 32;
+constexpr int PART_THREADS = 256;
+
+__device__ __forceinline__ void take_first_max(float& bv, int& bi, float v, int i) {
+    if (v > bv || (v == bv && i < bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+
+__global__ void __launch_bounds__(PART_THREADS)
+argmax_partial_kernel(const float* __restrict__ logits, int V, int ld, const int* __restrict__ slots,
+                      float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float red_f[PART_THREADS / 32];
+    __shared__ int red_i[PART_THREADS / 32];
+    griddep_launch();
+    griddep_wait();
+    const int c = blockIdx.x, b = blockIdx.y;
+    if (slots != nullptr && slots[b] < 0) return;          // padding row: the sampling CTA does not look
+    const float* row = logits + (size_t)b * ld;
+    const int chunk = ((V + ARGMAX_PARTS - 1) / ARGMAX_PARTS + 3) & ~3;
+    const int i0 = c * chunk, i1 = min(V, i0 + chunk);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int n4 = (i1 - i0) / 4;
+        const float4* r4 = reinterpret_cast<const float4*>(row + i0);
+        for (int j = threadIdx.x; j < n4; j += PART_THREADS) {
+            const float4 v = r4[j];
+            const int i = i0 + 4 * j;
+            take_first_max(bv, bi, v.x, i);
+            take_first_max(bv, bi, v.y, i + 1);
+            take_first_max(bv, bi, v.z, i + 2);
+            take_first_max(bv, bi, v.w, i + 3);
+        }
+        for (int i = i0 + 4 * n4 + threadIdx.x; i < i1; i += PART_THREADS) take_first_max(bv, bi, row[i], i);
+    } else {
+        for (int i = i0 + threadIdx.x; i < i1; i += PART_THREADS) take_first_max(bv, bi, row[i], i);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        take_first_max(bv, bi, v2, i2);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        red_f[warp] = bv;
+        red_i[warp] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < PART_THREADS / 32; w++) take_first_max(bv, bi, red_f[w], red_i[w]);
+        part_val[(size_t)b * ARGMAX_PARTS + c] = bv;
+        part_idx[(size_t)b * ARGMAX_PARTS + c] = bi;
+    }
+}
+
+// The row's first maximum from the pieces' results (every thread of the CTA gets it).
+__device__ int argmax_from_parts(const float* __restrict__ part_val, const int* __restrict__ part_idx, int b, Shared& sh, float* max_out) {
+    if (threadIdx.x < 32) {
+        float bv = part_val[(size_t)b * ARGMAX_PARTS + threadIdx.x];
+        int bi = part_idx[(size_t)b * ARGMAX_PARTS + threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float v2 = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+            take_first_max(bv, bi, v2, i2);
+        }
+        if (threadIdx.x == 0) {
+            sh.red_f[0] = bv;
+            sh.red_i[0] = bi;
+        }
+    }
+    __syncthreads();
+    const float bv = sh.red_f[0];
+    const int bi = sh.red_i[0];
+    __syncthreads();
+    *max_out = bv;
+    return bi == 0x7fffffff ? 0 : bi;
+}
+
 // One CTA per row. The row of logits is overwritten with probabilities when
 // the temperature is positive (the reference's sampler also works in place).
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict__ params,
-              unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out) {
+              unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out,
+              const float* __restrict__ part_val, const int* __restrict__ part_idx) {
     __shared__ Shared sh;
     griddep_launch();
     griddep_wait();
@@ -279,7 +365,7 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
         return;
     }
     float mx;
-    const int best = block_argmax(row, V, sh, &mx);
+    const int best = part_val != nullptr ? argmax_from_parts(part_val, part_idx, b, sh, &mx) : block_argmax(row, V, sh, &mx);
     if (sp.temp <= 0.f) {
         if (threadIdx.x == 0) out[b] = best;
         return;
@@ -421,14 +507,24 @@ MYNAH_API int mynah_argmax(const float* logits, int B, int V, int ld, int* out, 
 // captured step serves every setting. rng: one 64-bit generator state per
 // slot; slots [B] maps rows to slots (null: row b is slot b; a negative slot
 // marks a padding row). out [B] receives the token ids.
+// part_val, part_idx: scratch of B * mynah_argmax_parts() entries each for the two-step maximum, or null.
 MYNAH_API int mynah_sample(float* logits, int B, int V, int ld, const float* params,
-                           unsigned long long* rng, const int* slots, int* out, cudaStream_t stream) {
+                           unsigned long long* rng, const int* slots, int* out,
+                           float* part_val, int* part_idx, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && V > 0 && ld >= V, "sample: bad sizes B=%d V=%d ld=%d", B, V, ld);
     MYNAH_REQUIRE(params != nullptr && rng != nullptr, "sample: parameters and generator states are required");
-    mynah_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out);
+    MYNAH_REQUIRE((part_val == nullptr) == (part_idx == nullptr) && B <= 65535, "sample: bad scratch or too many rows");
+    if (part_val != nullptr) {
+        mynah_launch(argmax_partial_kernel, dim3(ARGMAX_PARTS, B), dim3(PART_THREADS), 0, stream, (const float*)logits, V, ld, slots, part_val, part_idx);
+        if (mynah_check_launch("argmax_partial")) return -1;
+    }
+    mynah_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out,
+                 (const float*)part_val, (const int*)part_idx);
     return mynah_check_launch("sample");
 }
+
+MYNAH_API int mynah_argmax_parts() { return ARGMAX_PARTS; }
 
 MYNAH_API int mynah_apply_penalties(float* logits, int B, int V, int ld, const int* ring, const int* ring_n,
                                     int window, const int* slots, const float* params, cudaStream_t stream) {

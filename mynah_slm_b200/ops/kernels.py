@@ -397,8 +397,28 @@ def sample(logits: torch.Tensor, params: torch.Tensor, rng: torch.Tensor, slots:
     B, V = logits.shape
     if out is None:
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    call("mynah_sample", ptr(logits), B, V, V, ptr(params), ptr(rng), ptr(slots), ptr(out), stream_ptr())
+    pv = pi = None
+    if V >= SAMPLE_TWO_STEP_MIN_VOCAB:
+        pv, pi = _sample_scratch(logits.device, B)
+    call("mynah_sample", ptr(logits), B, V, V, ptr(params), ptr(rng), ptr(slots), ptr(out), ptr(pv), ptr(pi), stream_ptr())
     return out
+
+
+# From this vocabulary size on a row's maximum is found by several CTAs first (one CTA reads a long row slowly).
+SAMPLE_TWO_STEP_MIN_VOCAB = 16384
+_SAMPLE_SCRATCH: dict = {}
+
+
+def _sample_scratch(device, B: int):
+    """Scratch of the two-step maximum, kept for the life of the process (a captured step holds its address)."""
+    key = (str(device), B)
+    if key not in _SAMPLE_SCRATCH:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("sample: scratch memory must exist before graph capture")
+        n = B * int(lib.load().mynah_argmax_parts())
+        _SAMPLE_SCRATCH[key] = (torch.empty((n,), dtype=torch.float32, device=device),
+                                torch.empty((n,), dtype=torch.int32, device=device))
+    return _SAMPLE_SCRATCH[key]
 
 
 def apply_penalties(logits: torch.Tensor, ring: torch.Tensor, ring_n: torch.Tensor, slots: Optional[torch.Tensor],

@@ -68,7 +68,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_set_pdl": [c_int],
-    "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P],
+    "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P, P, P],
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
     "mynah_decode_advance": [P, P, P, P, P, c_int, P],
     "mynah_sampler_accept": [P, c_int, P, P, P, c_int, P, P, P],
@@ -95,6 +95,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_attn_decode_tc_supported.restype = c_int
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_argmax_parts.restype = c_int
+    lib.mynah_argmax_parts.argtypes = []
     lib.mynah_attn_prefill_tc_supported.restype = c_int
     lib.mynah_attn_prefill_tc_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_attn_prefill_tcgen05_supported.restype = c_int
