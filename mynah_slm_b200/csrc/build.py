@@ -141,5 +141,47 @@ def _build(out: str, lib: str, verbose: bool) -> None:
     _say(f"built {LIB_NAME} in {time.time() - t0:.0f}s")
 
 
+# ---------------------------------------------------------------- the host-side runtime (no CUDA)
+HOST_LIB_NAME = "libmynah_slm_b200_host.so"
+HOST_SOURCES = [os.path.join("host", "runtime.cpp")]
+HOST_HEADERS = [os.path.join(os.pardir, "include", "mynah_slm_b200_host.h")]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+
+
+def _find_cxx() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++): the host runtime of "
+                     "mynah_slm_b200 cannot be built")
+
+
+def host_library_path() -> str:
+    """Path of the up-to-date host runtime (page books, step packing), building it first if need be.
+    It needs a C++ compiler only, no GPU and no nvcc."""
+    out = build_dir()
+    lib = os.path.join(out, HOST_LIB_NAME)
+    stamp_file = os.path.join(out, "host_stamp")
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    for f in HOST_SOURCES + HOST_HEADERS:
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(fh.read())
+    stamp = h.hexdigest()
+    if os.path.isfile(lib) and os.path.isfile(stamp_file):
+        with open(stamp_file) as f:
+            if f.read().strip() == stamp:
+                return lib
+    tmp = lib + f".tmp{os.getpid()}"
+    cmd = [_find_cxx(), *HOST_FLAGS, "-o", tmp, *[os.path.join(HERE, f) for f in HOST_SOURCES]]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"compiling the host runtime failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib)
+    with open(stamp_file, "w") as f:
+        f.write(stamp)
+    return lib
+
+
 if __name__ == "__main__":
+    print(host_library_path())
     print(library_path(verbose="-v" in sys.argv))

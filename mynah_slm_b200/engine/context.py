@@ -51,6 +51,12 @@ class StepLayout:
                 self.off[name] = (off, n)
                 off += _pad4(max(n, 1))
         self.size = off
+        # the same offsets as arrays, for the native packing routine (cache/pages.py: fill_step)
+        names = ["tokens", "tok_seq", "tok_pos", "cu_q", "kv_len", "slots", "want"]
+        for g in range(len(self.ids_cap)):
+            names += [f"indptr{g}", f"base{g}", f"ids{g}"]
+        self.offsets_array = np.array([self.off[n][0] for n in names], dtype=np.int32)
+        self.ids_cap_array = np.array(list(self.ids_cap) or [0], dtype=np.int32)
 
     def view(self, buf, name: str):
         o, n = self.off[name]

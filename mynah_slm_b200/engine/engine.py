@@ -224,56 +224,12 @@ class Engine:
         return max(1, -(-max_kv // PAGE_TOKENS))
 
     def _fill(self, buf_np: np.ndarray, layout: StepLayout, entries: Sequence[StepEntry], with_want: bool = True):
-        """Write the batch description into a host buffer. Returns
+        """Write the batch description into a host buffer (packed by the native host runtime). Returns
         (max_q_len, want_count)."""
-        pages = self.cache.pages
-        v = lambda name: layout.view(buf_np, name)
-        tokens, tok_seq, tok_pos = v("tokens"), v("tok_seq"), v("tok_pos")
-        cu_q, kv_len, slots, want = v("cu_q"), v("kv_len"), v("slots"), v("want")
-        row = 0
-        wi = 0
-        max_q = 0
-        cu_q[0] = 0
-        for b, e in enumerate(entries):
-            n = len(e.tokens)
-            past = pages.length[e.slot]
-            tokens[row:row + n] = e.tokens
-            tok_seq[row:row + n] = b
-            tok_pos[row:row + n] = np.arange(past, past + n, dtype=np.int32)
-            for w in (e.want if with_want else ()):
-                want[wi] = row + int(w)
-                wi += 1
-            row += n
-            cu_q[b + 1] = row
-            kv_len[b] = past + n
-            slots[b] = e.slot
-            max_q = max(max_q, n)
-        B = len(entries)
-        if layout.B > B:                                  # padding sequences and rows
-            cu_q[B + 1:] = row
-            kv_len[B:] = 0
-            slots[B:] = -1
-        if layout.T > row:
-            tokens[row:] = 0
-            tok_seq[row:] = -1
-            tok_pos[row:] = 0
-        for g in range(self.n_groups):
-            indptr, base, ids = v(f"indptr{g}"), v(f"base{g}"), v(f"ids{g}")
-            n_ids = 0
-            indptr[0] = 0
-            for b, e in enumerate(entries):
-                held, first = pages.held(e.slot, g)
-                k = len(held)
-                if n_ids + k > len(ids):
-                    raise EngineError("the page lists of this step outgrow their buffer")
-                ids[n_ids:n_ids + k] = held
-                n_ids += k
-                indptr[b + 1] = n_ids
-                base[b] = first
-            if layout.B > B:
-                indptr[B + 1:] = n_ids
-                base[B:] = 0
-        return max_q, wi
+        return self.cache.pages.fill_step(
+            buf_np, layout.offsets_array, layout.T, layout.B, layout.W, layout.ids_cap_array,
+            [e.slot for e in entries], [e.tokens for e in entries],
+            [e.want for e in entries] if with_want else None)
 
     # ------------------------------------------------------------- forward
     def _forward(self, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
