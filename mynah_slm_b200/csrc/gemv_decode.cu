@@ -64,7 +64,9 @@ __device__ __forceinline__ float stable_sigmoid_f(float v) {
 // while they are small); ROWS_NORM: the norm prologue computes them into shared memory.
 enum RowsMode : int { ROWS_DIRECT = 0, ROWS_STAGED = 1, ROWS_NORM = 2 };
 
-template <int EPI, int MODE>
+// U: 16-byte loads of a weight row that a lane keeps in flight (per operand); 8 for long rows, so that a warp's
+// share of K is one or two round trips to memory instead of two or three.
+template <int EPI, int MODE, int U>
 __global__ void __launch_bounds__(THREADS)
 gemv_decode_kernel(GemvArgs a) {
     constexpr bool NORM = MODE == ROWS_NORM;
@@ -80,11 +82,11 @@ gemv_decode_kernel(GemvArgs a) {
 
     // ---- the first weights of this CTA, before anything an earlier kernel wrote is touched: the
     // weights are never written, so their loads may run while the kernel before this one finishes
-    uint4 wv[4], uv[4];
-    uint4 xa[4], xb[4];                                              // without the norm: the rows' fragments, straight from global memory
+    uint4 wv[U], uv[EPI == EPI_SWIGLU ? U : 1];
+    uint4 xa[MODE == ROWS_DIRECT ? U : 1], xb[MODE == ROWS_DIRECT ? U : 1];                                              // without the norm: the rows' fragments, straight from global memory
     auto load_rows = [&](int kb0) {
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < (MODE == ROWS_DIRECT ? U : 0); u++) {
             const int kb = kb0 + u * WARPS;
             const bool ok = kb < nkb;
             xa[u] = ok && g < M ? *reinterpret_cast<const uint4*>(a.x_bf16 + (size_t)g * K + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
@@ -97,12 +99,12 @@ gemv_decode_kernel(GemvArgs a) {
         const bf16* w_gate = a.W + (size_t)(row_ok ? row : 0) * K;
         const bf16* w_up = EPI == EPI_SWIGLU ? a.W + (size_t)((row_ok ? row : 0) + a.N) * K : nullptr;
 #pragma unroll
-        for (int u = 0; u < 4; u++) {                                // up to 8 x 16 bytes in flight per lane
+        for (int u = 0; u < U; u++) {                                // U (2U with the up rows) x 16 bytes in flight per lane
             const int kb = kb0 + u * WARPS;
             const bool ok = kb < nkb && row_ok;
             wv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_gate + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
             if (EPI == EPI_SWIGLU)
-                uv[u] = ok ? __ldg(reinterpret_cast<const uint4*>(w_up + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
+                uv[EPI == EPI_SWIGLU ? u : 0] = ok ? __ldg(reinterpret_cast<const uint4*>(w_up + kb * 32 + t * 8)) : make_uint4(0, 0, 0, 0);
         }
     };
     const int n_first = blockIdx.x * a.groups_per_cta * 8;
@@ -165,11 +167,11 @@ gemv_decode_kernel(GemvArgs a) {
         const int n0 = (blockIdx.x * a.groups_per_cta + gi) * 8;
         if (n0 >= a.N) break;                                        // uniform over the CTA
         float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kb0 = warp; kb0 < nkb; kb0 += WARPS * 4) {
+        for (int kb0 = warp; kb0 < nkb; kb0 += WARPS * U) {
             if (gi != 0 || kb0 != warp) load_weights(n0, kb0);       // the first batch is already here
             if (!STAGED) load_rows(kb0);                             // (from L1 after the CTA's first group of rows)
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < U; u++) {
                 const int kb = kb0 + u * WARPS;
                 if (kb < nkb) {                                      // uniform over the warp
                     uint4 xa_u, xb_u = make_uint4(0, 0, 0, 0);
@@ -177,16 +179,16 @@ gemv_decode_kernel(GemvArgs a) {
                         xa_u = *reinterpret_cast<const uint4*>(xs + g * ldx + kb * 32 + t * 8);
                         if (rows_x == 16) xb_u = *reinterpret_cast<const uint4*>(xs + (g + 8) * ldx + kb * 32 + t * 8);
                     } else {
-                        xa_u = xa[u];
-                        xb_u = xb[u];
+                        xa_u = xa[MODE == ROWS_DIRECT ? u : 0];
+                        xb_u = xb[MODE == ROWS_DIRECT ? u : 0];
                     }
                     const uint32_t a1[4] = {xa_u.x, xb_u.x, xa_u.y, xb_u.y};   // k-permuted: both operands use the same order
                     const uint32_t a2[4] = {xa_u.z, xb_u.z, xa_u.w, xb_u.w};
                     mma_bf16(c0, a1, wv[u].x, wv[u].y);
                     mma_bf16(c0, a2, wv[u].z, wv[u].w);
                     if (EPI == EPI_SWIGLU) {
-                        mma_bf16(c1, a1, uv[u].x, uv[u].y);
-                        mma_bf16(c1, a2, uv[u].z, uv[u].w);
+                        mma_bf16(c1, a1, uv[EPI == EPI_SWIGLU ? u : 0].x, uv[EPI == EPI_SWIGLU ? u : 0].y);
+                        mma_bf16(c1, a2, uv[EPI == EPI_SWIGLU ? u : 0].z, uv[EPI == EPI_SWIGLU ? u : 0].w);
                     }
                 }
             }
@@ -236,9 +238,9 @@ gemv_decode_kernel(GemvArgs a) {
     }
 }
 
-template <int EPI, int MODE>
-int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
-    auto kern = gemv_decode_kernel<EPI, MODE>;
+template <int EPI, int MODE, int U>
+int launch_u(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
+    auto kern = gemv_decode_kernel<EPI, MODE, U>;
     static int allowed = 0;                           // per instantiation: the largest size opted in to so far
     // dynamic plus the kernel's static shared memory (up to 9 KB) must stay under 48 KB unless opted in
     if (smem > 36 * 1024 && (int)smem > allowed) {
@@ -248,6 +250,13 @@ int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
     }
     mynah_launch(kern, dim3(n_ctas), dim3(THREADS), smem, stream, a);
     return mynah_check_launch("gemv_decode");
+}
+
+template <int EPI, int MODE>
+int launch(const GemvArgs& a, int n_ctas, size_t smem, cudaStream_t stream) {
+    // long rows without the up rows: eight loads a lane in flight (a warp's share of K = 2,048 is then one batch)
+    if (EPI != EPI_SWIGLU && a.K >= 2048) return launch_u<EPI, MODE, 8>(a, n_ctas, smem, stream);
+    return launch_u<EPI, MODE, 4>(a, n_ctas, smem, stream);
 }
 
 }  // namespace
@@ -273,7 +282,7 @@ MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* 
     a.x_bf16 = (const bf16*)x_bf16; a.x_res = x_res; a.delta = (const bf16*)delta; a.x_res_out = x_res_out;
     a.gain = VecRef{gain, gain_dtype}; a.eps = eps; a.out = out; a.ldo = ldo;
     const int groups = ceil_div(N, 8);
-    const int target = (sm_count > 0 ? sm_count : 148) * 2;          // about two CTAs per SM
+    const int target = (sm_count > 0 ? sm_count : 148) * 4;          // one group of rows a CTA while that gives at most four CTAs an SM (their registers fill it)
     a.groups_per_cta = groups <= target ? 1 : ceil_div(groups, target);
     const int n_ctas = ceil_div(groups, a.groups_per_cta);
     const bool norm = x_res != nullptr;
