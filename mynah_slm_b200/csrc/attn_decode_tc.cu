@@ -260,14 +260,40 @@ __device__ __forceinline__ void merge_pages(const float* __restrict__ part_o, co
                                             float* w_s, float* acc_s, float* inv_s) {
     // (G may also be 1 with r0g and out_row pointing at one head: a head's arithmetic does not involve the others.)
     constexpr int LPR = HD / 4, NS = WARPS * 32 / LPR;
+    constexpr int AHEAD = 8;                          // output rows a thread fetches before it has their weights
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ld4 = tid % LPR, slot = tid / LPR;
+    // the first head's output rows are on their way while the weights are worked out
+    float4 o_first[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; k++) {
+        const int s2 = slot + k * NS;
+        o_first[k] = s2 < n_vis ? __ldcg(reinterpret_cast<const float4*>(part_o + (r0g + s2) * HD) + ld4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int i = warp; i < G; i += WARPS) {
         const size_t r0h = r0g + (size_t)i * S;
+        // a lane keeps the pages' (maximum, sum) pairs it has read: up to 4 of them (128 pages), else it reads again
+        float2 ml_r[4];
         float mmax = -INFINITY;
-        for (int s2 = lane; s2 < n_vis; s2 += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (r0h + s2) * 2));
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int s2 = lane + 32 * k;
+            ml_r[k] = s2 < n_vis ? __ldcg(reinterpret_cast<const float2*>(part_ml + (r0h + s2) * 2)) : make_float2(-INFINITY, 0.f);
+            mmax = fmaxf(mmax, ml_r[k].x);
+        }
+        for (int s2 = lane + 128; s2 < n_vis; s2 += 32) mmax = fmaxf(mmax, __ldcg(part_ml + (r0h + s2) * 2));
         mmax = warp_max(mmax);
         float ls = 0.f;
-        for (int s2 = lane; s2 < n_vis; s2 += 32) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int s2 = lane + 32 * k;
+            if (s2 < n_vis) {
+                const float w = ml_r[k].x == -INFINITY ? 0.f : expf(ml_r[k].x - mmax);
+                w_s[i * S + s2] = w;
+                ls = fmaf(ml_r[k].y, w, ls);
+            }
+        }
+        for (int s2 = lane + 128; s2 < n_vis; s2 += 32) {
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (r0h + s2) * 2));
             const float w = ml.x == -INFINITY ? 0.f : expf(ml.x - mmax);
             w_s[i * S + s2] = w;
@@ -277,19 +303,24 @@ __device__ __forceinline__ void merge_pages(const float* __restrict__ part_o, co
         if (lane == 0) inv_s[i] = ls > 0.f ? 1.0f / ls : 0.f;
     }
     __syncthreads();
-    const int ld4 = tid % LPR, slot = tid / LPR;
     for (int i = 0; i < G; i++) {
         const size_t r0h = r0g + (size_t)i * S;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (int s2 = slot; s2 < n_vis; s2 += NS) {
-            const float w = w_s[i * S + s2];
-            const float4 o = __ldcg(reinterpret_cast<const float4*>(part_o + (r0h + s2) * HD) + ld4);
+        auto add = [&](const float4& o, float w) {
             if (w != 0.f) {                           // a page without visible keys wrote no output row
                 acc.x = fmaf(o.x, w, acc.x); acc.y = fmaf(o.y, w, acc.y);
                 acc.z = fmaf(o.z, w, acc.z); acc.w = fmaf(o.w, w, acc.w);
             }
+        };
+        int s2 = slot;
+        if (i == 0) {
+#pragma unroll
+            for (int k = 0; k < AHEAD; k++, s2 += NS)
+                if (s2 < n_vis) add(o_first[k], w_s[s2]);
         }
+#pragma unroll 8
+        for (; s2 < n_vis; s2 += NS)
+            add(__ldcg(reinterpret_cast<const float4*>(part_o + (r0h + s2) * HD) + ld4), w_s[i * S + s2]);
         reinterpret_cast<float4*>(acc_s + slot * HD)[ld4] = acc;
         __syncthreads();
         for (int d = tid; d < HD; d += WARPS * 32) {
