@@ -8,6 +8,8 @@ CUDA.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Optional
 
@@ -164,7 +166,11 @@ def _fusable(x, w: torch.Tensor, N: int) -> bool:
     return K == w.shape[1] and N <= GEMV_MAX_OUT_ROWS and gemv_decode_supported(M, N, K)
 
 
-FUSED_NORM_MAX_ROWS = 2     # beyond this every CTA recomputing the norm costs more than a separate kernel
+# Rows up to which the norm runs as the product's prologue. 0: never. Since the products spread over up to four
+# CTAs an SM, every CTA recomputing the norm costs as much as the separate norm kernel at one row (0.985 vs
+# 0.980 ms a step at batch 1) and more from two rows on (1.155 vs 1.045 ms at batch 2), so it is off; the
+# prologue stays in the kernel and in the tests.
+FUSED_NORM_MAX_ROWS = int(os.environ.get("MYNAH_FUSED_NORM_MAX_ROWS", "0"))
 FUSED_NORM_MAX_K = 12288    # the norm prologue keeps its rows in shared memory
 GEMV_MAX_OUT_ROWS = 32768   # wider products (the output head) stream better through the library for now
 

@@ -629,11 +629,26 @@ def test_gemv_decode_fused_kernels(M, N, K):
     normed = k.NormedInput(stream, torch.from_numpy(delta).to(torch.bfloat16).to(DEV),
                            torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps, torch.bfloat16)
     old_x = stream.x
-    got = k.linear(normed, wd, out_dtype=torch.float32).cpu().numpy()
+    saved_rows = k.FUSED_NORM_MAX_ROWS
+    k.FUSED_NORM_MAX_ROWS = 16                     # the prologue for every row count the kernel takes (the engine's default is lower)
+    try:
+        got = k.linear(normed, wd, out_dtype=torch.float32).cpu().numpy()
+    finally:
+        k.FUSED_NORM_MAX_ROWS = saved_rows
     assert rel_err(h_ref.astype(np.float64) @ w.astype(np.float64).T, got) < 5e-3      # h may round the other way here and there
     assert np.array_equal(stream.x.cpu().numpy(), res + delta)
-    if M <= k.FUSED_NORM_MAX_ROWS:                 # fused: the updated residual is a new buffer, the input rows are left alone
-        assert stream.x is not old_x and np.array_equal(old_x.cpu().numpy(), res)
+    # fused: the updated residual is a new buffer, the input rows are left alone
+    assert stream.x is not old_x and np.array_equal(old_x.cpu().numpy(), res)
+    # the unfused route (norm kernel, then the product) through the same handle
+    stream2 = Residual(torch.from_numpy(res.copy()).to(DEV))
+    normed2 = k.NormedInput(stream2, torch.from_numpy(delta).to(torch.bfloat16).to(DEV),
+                            torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps, torch.bfloat16)
+    k.FUSED_NORM_MAX_ROWS = 0
+    try:
+        got2 = k.linear(normed2, wd, out_dtype=torch.float32).cpu().numpy()
+    finally:
+        k.FUSED_NORM_MAX_ROWS = saved_rows
+    assert rel_err(got2, got) < 5e-3 and np.array_equal(stream2.x.cpu().numpy(), res + delta)
     # the same through the separate norm kernel gives the same rounding points
     h_dev = k.rmsnorm(torch.from_numpy(res.copy()).to(DEV), torch.from_numpy(gain).to(torch.bfloat16).to(DEV), eps,
                       torch.bfloat16, delta=torch.from_numpy(delta).to(torch.bfloat16).to(DEV))
