@@ -127,6 +127,31 @@ class _DecodeGraph:
     graphs: dict = field(default_factory=dict)     # mode -> (CUDAGraph, output tensor, kernels per replay)
 
 
+@dataclass
+class _PromptGraph:
+    """A captured prompt step for one padded shape: rows, sequences, wanted rows, page-list capacity."""
+    layout: StepLayout
+    meta: torch.Tensor                 # static device copy of the batch description
+    ctx: StepContext
+    graph: object = None               # torch.cuda.CUDAGraph once captured
+    logits: Optional[torch.Tensor] = None
+    n_kernels: int = 0
+    last_use: int = 0
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+def _prompt_rows_bucket(T: int) -> int:
+    """Rows of a prompt step, padded so that a few graphs serve many lengths and at most an eighth is padding."""
+    if T <= 256:
+        return _round_up(T, 32)
+    if T <= 1024:
+        return _round_up(T, 128)
+    return _round_up(T, 256)
+
+
 class Engine:
     def __init__(self, spec: ModelSpec, checkpoint: Checkpoint, dtype="bfloat16", max_tokens: int = 4096,
                  max_seqs: Optional[int] = None, device="cuda:0", use_graphs: bool = True,
@@ -164,6 +189,11 @@ class Engine:
         self.fused = _fd.plan(self.model, self.cache, self.runtime) if fused_decode else None
         self._staging = _Staging()
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        # prompt steps: a shape is captured the second time it comes; a handful of graphs are kept
+        self._prompt_graphs: dict[tuple, _PromptGraph] = {}
+        self._prompt_seen: dict[tuple, int] = {}
+        self._prompt_clock = 0
+        self.max_prompt_graphs = 6
         self.launches = 0                          # kernels of this package launched (see count_launches)
         self.vocab_size = spec.vocab_size
 
@@ -260,10 +290,74 @@ class Engine:
             else:
                 out = logits[torch.tensor(rows, dtype=torch.int64, device=self.device)]
         else:
-            out = self._eager_step(entries, is_decode)
+            out = None
+            if not is_decode and self.use_graphs and self.graph_safe and self.dtype == torch.bfloat16:
+                out = self._prompt_graph_step(entries)
+            if out is None:
+                out = self._eager_step(entries, is_decode)
         for e in entries:
             pages.commit(e.slot, len(e.tokens))
         return out
+
+    # --------------------------------------------------------- prompt graphs
+    def _prompt_graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A prompt step replayed from a captured graph, or None when this shape has no graph (yet). Rows,
+        sequences, wanted rows and page lists are padded to the graph's capacities; padding rows belong to no
+        sequence (tok_seq -1), padding sequences have no rows."""
+        wants = [(b, int(w)) for b, e in enumerate(entries) for w in e.want]
+        if not wants:
+            return None
+        B = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        need_ids = [sum(self.cache.pages.n_held(e.slot, g) for e in entries) for g in range(self.n_groups)]
+        key = (_prompt_rows_bucket(T), self._bucket(B), self._bucket(len(wants)),
+               tuple(max(4, self._bucket(n)) for n in need_ids))
+        g = self._prompt_graphs.get(key)
+        if g is None:
+            seen = self._prompt_seen.get(key, 0)
+            self._prompt_seen[key] = seen + 1
+            if seen == 0:
+                return None                                   # once: run as it is; twice: worth a graph
+            layout = StepLayout(T=key[0], B=key[1], W=key[2], ids_cap=list(key[3]))
+            meta = torch.zeros((layout.size,), dtype=torch.int32, device=self.device)
+            ctx = device_context(layout, meta, [self.n_pages] * self.n_groups, key[0], False, 1, self.runtime.status, self.dtype)
+            g = _PromptGraph(layout, meta, ctx)
+            if len(self._prompt_graphs) >= self.max_prompt_graphs:
+                oldest = min(self._prompt_graphs, key=lambda k: self._prompt_graphs[k].last_use)
+                del self._prompt_graphs[oldest]
+            self._prompt_graphs[key] = g
+        self._prompt_clock += 1
+        g.last_use = self._prompt_clock
+        layout = g.layout
+        host, hi = self._staging.get(layout.size)
+        _, n_want = self._fill(host.numpy(), layout, entries)
+        want_view = layout.view(host.numpy(), "want")
+        uniq, inverse = np.unique(want_view[:n_want], return_inverse=True)
+        want_view[:len(uniq)] = uniq
+        want_view[len(uniq):] = uniq[0]                       # padding: a row that is wanted anyway
+        g.meta.copy_(host[:layout.size], non_blocking=True)
+        self._staging.sent(hi)
+        self._host_fields(g.ctx, entries)
+        from ..ops import lib
+        if g.graph is None:
+            # run once for real (sizes scratch memory, warms the library), then record the same launches
+            n0 = lib.launch_count()
+            out = self._forward(g.ctx, g.ctx.want)
+            g.n_kernels = lib.launch_count() - n0
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g.logits = self._forward(g.ctx, g.ctx.want)
+            lib.add_launches(-g.n_kernels)                    # recorded, not run
+            g.graph = graph
+            logits = out
+        else:
+            g.graph.replay()
+            lib.add_launches(g.n_kernels)
+            logits = g.logits
+        if len(uniq) == n_want and np.array_equal(inverse, np.arange(n_want)):
+            return logits[:n_want].clone()                    # the graph's output buffer is reused by the next replay
+        return logits[torch.from_numpy(inverse.astype(np.int64)).to(self.device)]
 
     def _eager_step(self, entries: Sequence[StepEntry], is_decode: bool) -> torch.Tensor:
         B = len(entries)

@@ -207,6 +207,39 @@ def test_trace_run_program(folders, plain_models, tmp_path, name, dtype, wdt):
     assert_close(rb[8:9], load(3), tol(dtype), "trace step 3")
 
 
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
+def test_prompt_steps_replayed_from_graphs(tmp_path, name):
+    """A prompt step's shape is captured the second time it comes and replayed from then on, with rows,
+    sequences and wanted rows padded to the graph's capacities. Batches of different prompts and lengths that
+    share a padded shape go through the same graph; every logit row is compared with the plain implementation,
+    and slots and pages are used again in between."""
+    folder = make_folder(tmp_path, name, torch.bfloat16)       # D and E take the tensor-core attention kernels
+    eng = _engine(folder, "bfloat16", 1024)
+    plain = PlainQwen3.from_folder(folder)
+    assert eng.use_graphs and eng.graph_safe
+    for rnd, lens in enumerate([[40, 7, 70], [33, 20, 75], [1, 64, 37], [60, 60, 8], [150], [129], [140]]):
+        prompts = prompts_for(name, lens, seed=40 + rnd)
+        slots = [eng.open_sequence() for _ in prompts]
+        wants = [(0, n - 1) if n > 1 else (0,) for n in lens]
+        got = eng.step([_entry(s, p, w) for s, p, w in zip(slots, prompts, wants)]).cpu().numpy()
+        eng.check_status()
+        row = 0
+        for p, w in zip(prompts, wants):
+            ref = plain.forward(p)
+            for j in w:
+                assert_close(ref[j:j + 1], got[row:row + 1], BF16_REL, f"round {rnd}, prompt of {len(p)}, place {j}")
+                row += 1
+        # one decoded token each on top of what the replayed step wrote into the cache
+        nxt = [int(np.argmax(plain.forward(p)[-1])) for p in prompts]
+        got = eng.step([_entry(s, [t], (0,)) for s, t in zip(slots, nxt)]).cpu().numpy()
+        for b, (p, t) in enumerate(zip(prompts, nxt)):
+            assert_close(plain.forward(p + [t])[-1:], got[b:b + 1], BF16_REL, f"round {rnd}, decode after prompt {b}")
+        for s in slots:
+            eng.close_sequence(s)
+    captured = [g for g in eng._prompt_graphs.values() if g.graph is not None]
+    assert len(captured) >= 2, "the repeated shapes were not captured"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_padding_and_company_change_nothing(folders, dtype):
     """A decode step's logits for one sequence have the same bits whether its
