@@ -240,7 +240,9 @@ class SequencePages:
         ip = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
         slot_a = np.asarray(slots, dtype=np.int32)
         n_tok = np.fromiter((len(t) for t in token_lists), dtype=np.int32, count=n)
-        toks = np.fromiter((int(x) for t in token_lists for x in t), dtype=np.int32, count=int(n_tok.sum()))
+        arrays = [np.asarray(t, dtype=np.int32) for t in token_lists]
+        toks = arrays[0] if n == 1 else (np.concatenate(arrays) if n else np.zeros((0,), dtype=np.int32))
+        toks = np.ascontiguousarray(toks)
         if want_lists is not None:
             n_want = np.fromiter((len(w) for w in want_lists), dtype=np.int32, count=n)
             want = np.fromiter((int(x) for w in want_lists for x in w), dtype=np.int32, count=int(n_want.sum()))
