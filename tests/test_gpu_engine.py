@@ -240,6 +240,37 @@ def test_prompt_steps_replayed_from_graphs(tmp_path, name):
     assert len(captured) >= 2, "the repeated shapes were not captured"
 
 
+@pytest.mark.parametrize("name,window", [("D", None), ("E", 700)])
+def test_a_long_context(tmp_path, name, window):
+    """2,300 positions: a prompt step of 18 key tiles (in one piece, and a second sequence in two pieces), then
+    decode steps over 36 and more pages, with a window whose edge lies far back; against the plain
+    implementation at the positions where a fault of a far tile or page would show."""
+    cfg = dict(TINY[name], max_position_embeddings=4096)
+    if window is not None:
+        cfg["sliding_window"] = window
+    folder = make_folder(tmp_path, name, torch.bfloat16, config=cfg)
+    plain = PlainQwen3.from_folder(folder)
+    rng = np.random.default_rng(77)
+    n = 2300
+    toks = rng.integers(0, cfg["vocab_size"], size=n + 3).tolist()
+    ref = plain.forward(toks)                                          # [n + 3, V], whole sequence, no cache
+    eng = _engine(folder, "bfloat16", 3 * 2560)
+    a, b = eng.open_sequence(), eng.open_sequence()
+    places = (0, 63, 64, 127, 128, 1000, 2047, 2048, n - 1)
+    got = eng.step([_entry(a, toks[:n], places)]).cpu().numpy()
+    eng.check_status()
+    for i, j in enumerate(places):
+        assert_close(ref[j:j + 1], got[i:i + 1], BF16_REL, f"whole prompt, place {j}")
+    eng.step([_entry(b, toks[:1111], ())])                             # the same prompt in two pieces
+    got_b = eng.step([_entry(b, toks[1111:n], (n - 1111 - 1,))]).cpu().numpy()
+    assert_close(ref[n - 1:n], got_b, BF16_REL, "prompt in two pieces")
+    for t in range(3):                                                 # both sequences decode together
+        got = eng.step([_entry(a, [toks[n + t]], (0,)), _entry(b, [toks[n + t]], (0,))]).cpu().numpy()
+        eng.check_status()
+        assert_close(ref[n + t:n + t + 1], got[0:1], BF16_REL, f"decode step {t}")
+        assert_close(ref[n + t:n + t + 1], got[1:2], BF16_REL, f"decode step {t}, the sequence that came in pieces")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_padding_and_company_change_nothing(folders, dtype):
     """A decode step's logits for one sequence have the same bits whether its
