@@ -39,7 +39,7 @@ constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int THREADS = 192;
 constexpr int STAGING_BYTES = 32 * 128;              // 32 rows x 128 bytes per epilogue warp and buffer
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
 
 // Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -65,6 +65,27 @@ __device__ __forceinline__ float sigmoid_stable(float v) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
     return (v >= 0.f ? 1.0f : e) * r;
 }
+// What the q/k/v epilogue needs: the product's rows are tokens, its columns the heads of q, then k, then v.
+// Each epilogue thread has one token's head in registers (fp32, straight from the accumulator), norms it, rotates
+// it and writes it where the attention kernels read it: q rows to q_out, k and v to the token's place in its
+// sequence's page. (Norm before rotation, one gain per head position shared by all heads, v neither normed nor
+// rotated: mynah-slm src/arch_qwen3.c:208-218, src/kernels.c:130-137, :173-189.)
+struct QkvEpilogue {
+    int H, KV;
+    float eps;
+    const float* cos_t;               // [n_pos, HD / 2], or null: no rotation
+    const float* sin_t;
+    int n_pos;
+    VecRef q_gain, k_gain;            // .p null: no per-head norm
+    const int* tok_seq;               // [M], -1: padding row
+    const int* tok_pos;
+    PageTable pt;
+    bf16* q_out;                      // [M, ldq]
+    int ldq;
+    bf16* k_cache;                    // [n_pages, KV, 64, HD], or null: only q is produced
+    bf16* v_cache;
+};
+
 struct GemmShape {
     int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
     int up_offset;
@@ -79,7 +100,9 @@ struct GemmShape {
 template <int BN, int EPI, int CTAS>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status) {
+                    const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status, const QkvEpilogue qe) {
+    constexpr int HD = EPI == EPI_QKV ? 128 : 32;                    // the q/k/v epilogue is built for heads of 128
+    __shared__ float gain_s[EPI == EPI_QKV ? 2 : 1][EPI == EPI_QKV ? HD : 1];
     constexpr int B_BYTES = BN * BK * 2 / CTAS;                      // this CTA's rows of W
     constexpr int STAGE = A_BYTES + B_BYTES;
     constexpr int STAGES = ring_stages(BN, CTAS);
@@ -97,6 +120,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (g.K + BK - 1) / BK;
     const int total_tiles = g.m_tiles * g.n_tiles;
+    if (EPI == EPI_QKV && threadIdx.x < HD) {                        // the gains, once (ones when there is no per-head norm)
+        gain_s[0][threadIdx.x] = qe.q_gain.p != nullptr ? qe.q_gain.at(threadIdx.x) : 1.0f;
+        gain_s[EPI == EPI_QKV ? 1 : 0][threadIdx.x] = qe.k_gain.p != nullptr ? qe.k_gain.at(threadIdx.x) : 1.0f;
+    }
     const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;         // 0 leads
     const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;  // a unit walks over tiles: a CTA or a pair
 
@@ -226,6 +253,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             const int row0 = (m_tile * CTAS + rank) * BM + quad * 32;
+            if (EPI == EPI_QKV) {
+                // ---- a token a thread: its heads of this tile, one after the other
+                const int row = row0 + lane;
+                const int seq = row < g.M ? qe.tok_seq[row] : -1;
+                const int pos = seq >= 0 ? qe.tok_pos[row] : 0;
+                bool live = seq >= 0;
+                if (live && qe.cos_t != nullptr && (pos < 0 || pos >= qe.n_pos)) {
+                    atomicOr(status, MYNAH_ST_POS_RANGE);
+                    live = false;
+                }
+                size_t cache_row = 0;
+                bool paged = false;
+                if (live && qe.k_cache != nullptr) {
+                    const int page = page_of(qe.pt, seq, pos);
+                    if (page < 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+                    else {
+                        paged = true;
+                        cache_row = (size_t)page * qe.KV * PAGE_TOKENS + pos % PAGE_TOKENS;
+                    }
+                }
+#pragma unroll 1
+                for (int hh = 0; hh < BN / HD; hh++) {
+                    const int col0 = n_tile * BN + hh * HD;
+                    if (col0 >= g.N) break;                          // uniform over the warp
+                    const int head = col0 / HD;
+                    const bool is_q = head < qe.H, is_k = !is_q && head < qe.H + qe.KV;
+                    float v[HD];
+                    __syncwarp();                                    // the loads from tensor memory need the whole warp together
+#pragma unroll
+                    for (int c = 0; c < HD / 32; c++) tc_ld32(t_row + hh * HD + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
+                    bf16* dst = nullptr;
+                    if (live) {
+                        if (is_q) dst = qe.q_out + (size_t)row * qe.ldq + (size_t)head * HD;
+                        else if (paged) dst = (is_k ? qe.k_cache : qe.v_cache) + (cache_row + (size_t)(head - qe.H - (is_k ? 0 : qe.KV)) * PAGE_TOKENS) * HD;
+                    }
+                    if (dst != nullptr) {
+                        if (is_q || is_k) {
+                            if (qe.q_gain.p != nullptr) {
+                                float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                                for (int j = 0; j < HD; j++) s4[j & 3] = fmaf(v[j], v[j], s4[j & 3]);
+                                const float sc = 1.0f / sqrtf(((s4[0] + s4[1]) + (s4[2] + s4[3])) / (float)HD + qe.eps);
+                                const float* gn = gain_s[is_q ? 0 : 1];
+#pragma unroll
+                                for (int j = 0; j < HD; j++) v[j] = v[j] * (sc * gn[j]);
+                            }
+                            if (qe.cos_t != nullptr) {
+                                const float4* c4 = reinterpret_cast<const float4*>(qe.cos_t + (size_t)pos * (HD / 2));
+                                const float4* s4p = reinterpret_cast<const float4*>(qe.sin_t + (size_t)pos * (HD / 2));
+#pragma unroll
+                                for (int i4 = 0; i4 < HD / 8; i4++) {
+                                    const float4 c = c4[i4], sn = s4p[i4];
+                                    const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; e++) {
+                                        const int i = i4 * 4 + e;
+                                        const float a0 = v[i], b0 = v[i + HD / 2];
+                                        v[i] = a0 * cc[e] - b0 * ss[e];
+                                        v[i + HD / 2] = b0 * cc[e] + a0 * ss[e];
+                                    }
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < HD / 8; j++)
+                            reinterpret_cast<uint4*>(dst)[j] = make_uint4(pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                                                                          pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7]));
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < OUT_COLS; c0 += CHUNK, n_store++) {
                 unsigned char* st = my_stage + (n_store & 1) * STAGING_BYTES;
@@ -302,7 +399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 template <int BN, int EPI, int CTAS>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
-                int sm_count, int* status, cudaStream_t stream) {
+                int sm_count, int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{}) {
     constexpr int STAGES = ring_stages(BN, CTAS);
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2 / CTAS) + 4 * 2 * STAGING_BYTES + 256 + 1024;
     auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS>;
@@ -332,7 +429,7 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CTAS == 2 ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, g, status);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, g, status, qe);
     if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
     return mynah_check_launch("gemm_tcgen05");
 }
@@ -389,4 +486,45 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     if (epilogue == EPI_F32) return wide ? MYNAH_GEMM_GO(256, EPI_F32) : MYNAH_GEMM_GO(128, EPI_F32);
     return wide ? MYNAH_GEMM_GO(256, EPI_BF16) : MYNAH_GEMM_GO(128, EPI_BF16);
 #undef MYNAH_GEMM_GO
+}
+
+// The q/k/v projection of a prompt step with its epilogue: C = A . W^T as above (W rows: H heads of q, KV of k,
+// KV of v, head_dim 128), then per token and head the per-head RMSNorm (gains may be null), the rotation of the
+// whole head (tables may be null) and the writes: q to q_out [M, ldq], k and v to the token's row of its
+// sequence's page (k_cache null: W holds q only). tok_seq [M] (-1: padding row), tok_pos [M].
+MYNAH_API int mynah_gemm_qkv_rope_supported(int M, int H, int KV, int HD, int K) {
+    return M >= 1 && HD == 128 && H >= 1 && KV >= 1 && K >= 8 && K % 8 == 0;
+}
+
+MYNAH_API int mynah_gemm_qkv_rope(const void* A, const void* W, int M, int H, int KV, int HD, int K,
+                                  const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+                                  const float* cos_t, const float* sin_t, int n_pos,
+                                  const int* tok_seq, const int* tok_pos,
+                                  const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+                                  void* q_out, int ldq, void* k_cache, void* v_cache,
+                                  int sm_count, int* status, cudaStream_t stream) {
+    if (M == 0) return 0;
+    MYNAH_REQUIRE(mynah_gemm_qkv_rope_supported(M, H, KV, HD, K), "gemm_qkv_rope: M=%d H=%d KV=%d head_dim=%d K=%d is not taken", M, H, KV, HD, K);
+    MYNAH_REQUIRE((k_cache == nullptr) == (v_cache == nullptr) && (cos_t == nullptr) == (sin_t == nullptr) &&
+                  (q_gain == nullptr) == (k_gain == nullptr), "gemm_qkv_rope: caches, tables and gains come in pairs");
+    MYNAH_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ldq % 8 == 0 && ldq >= H * HD &&
+                  ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)cos_t & 15) == 0 && ((uintptr_t)sin_t & 15) == 0,
+                  "gemm_qkv_rope: operands must be 16-byte aligned");
+    MYNAH_REQUIRE(status != nullptr, "gemm_qkv_rope: a status word is required");
+    if (sm_count <= 0) sm_count = 148;
+    const int N = (k_cache != nullptr ? H + 2 * KV : H) * HD;
+    QkvEpilogue qe;
+    qe.H = H; qe.KV = KV; qe.eps = eps; qe.cos_t = cos_t; qe.sin_t = sin_t; qe.n_pos = n_pos;
+    qe.q_gain = VecRef{q_gain, gain_dtype}; qe.k_gain = VecRef{k_gain, gain_dtype};
+    qe.tok_seq = tok_seq; qe.tok_pos = tok_pos;
+    qe.pt = PageTable{page_indptr, page_ids, page_base, n_pages};
+    qe.q_out = (bf16*)q_out; qe.ldq = ldq; qe.k_cache = (bf16*)k_cache; qe.v_cache = (bf16*)v_cache;
+    const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * ceil_div(N, 256);
+    const bool pair = pair_enabled() && M >= 2 * BM && sm_count >= 2 && pair_tiles >= 2 * (sm_count / 2);
+    CUtensorMap ma, mb;
+    if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
+    if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, 128, BK)) return -1;
+    // the epilogue stores from registers: the third map is not used
+    if (pair) return launch_gemm<256, EPI_QKV, 2>(ma, mb, ma, M, N, K, 0, sm_count, status, stream, qe);
+    return launch_gemm<256, EPI_QKV, 1>(ma, mb, ma, M, N, K, 0, sm_count, status, stream, qe);
 }

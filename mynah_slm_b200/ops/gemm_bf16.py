@@ -9,6 +9,7 @@ decline it.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Optional
 
 import torch
@@ -73,6 +74,37 @@ def _tcgen05_route(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, out
 
 
 ROUTES.append(_tcgen05_route)
+
+# Switch for the q/k/v product with norm, rotation and cache write in its epilogue. Off: with a token's head of
+# 128 accumulators in a thread's registers the rotation's table reads (32 vectors a head, a different table row
+# in every lane) run one after the other, and the epilogue takes as long as the separate pass it replaces
+# (36.5 us against 19.5 + 15 us for 2,048 tokens of the 0.6B shape). The kernel test covers it.
+USE_QKV_EPILOGUE = os.environ.get("MYNAH_QKV_EPILOGUE", "0") != "0"
+
+
+def qkv_rope_supported(x: torch.Tensor, w: torch.Tensor, H: int, KV: int, HD: int) -> bool:
+    M, K = x.shape
+    return (USE_TCGEN05 and USE_QKV_EPILOGUE and M >= TCGEN05_MIN_ROWS and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous() and w.shape[1] == K
+            and bool(lib.load().mynah_gemm_qkv_rope_supported(M, H, KV, HD, K)))
+
+
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, H: int, KV: int, HD: int, q_gain, k_gain, eps: float,
+                  cos, sin, tok_seq: torch.Tensor, tok_pos: torch.Tensor, pages, k_cache, v_cache) -> torch.Tensor:
+    """q [M, H * HD] (normed, rotated), and k, v written into the paged cache, from one product. `w` holds the
+    q rows, then (with a cache given) the k and v rows. `pages` is the group's PageTableView."""
+    from .lib import code
+    M, K = x.shape
+    q = torch.empty((M, H * HD), dtype=torch.bfloat16, device=x.device)
+    call("mynah_gemm_qkv_rope", ptr(x), ptr(w), M, H, KV, HD, K,
+         ptr(q_gain), ptr(k_gain), code(q_gain.dtype) if q_gain is not None else 0, float(eps),
+         ptr(cos), ptr(sin), cos.shape[0] if cos is not None else 0,
+         ptr(tok_seq), ptr(tok_pos),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         ptr(q), q.shape[1], ptr(k_cache), ptr(v_cache),
+         _sm_count(x.device), ptr(status_word(x.device)), stream_ptr())
+    counters["own"] += 1
+    return q
 
 # Launch count of hand-written matrix-product kernels (read by the benchmark).
 counters = {"own": 0, "library": 0}

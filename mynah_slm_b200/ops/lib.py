@@ -54,6 +54,13 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P,
                              P, P, P, c_int,
                              c_int, c_int, P, P, P],
+    "mynah_gemm_qkv_rope": [P, P, c_int, c_int, c_int, c_int, c_int,
+                            P, P, c_int, c_float,
+                            P, P, c_int,
+                            P, P,
+                            P, P, P, c_int,
+                            P, c_int, P, P,
+                            c_int, P, P],
     "mynah_attn_prefill_tcgen05": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    P, P, P, P,
                                    P, P, P, c_int,
@@ -95,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_attn_decode_tc_supported.restype = c_int
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_gemm_qkv_rope_supported.restype = c_int
+    lib.mynah_gemm_qkv_rope_supported.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mynah_argmax_parts.restype = c_int
     lib.mynah_argmax_parts.argtypes = []
     lib.mynah_attn_prefill_tc_supported.restype = c_int

@@ -89,9 +89,24 @@ class GQAttention(Mixer):
         H, KV, HD = self.H, self.KV, self.HD
         T = h.shape[0]
         writes = cache.writes
-        qkv = kernels.linear(h, self.w_qkv if writes else self.w_q)
         pages = ctx.pages[cache.group]
-        from ..ops import attention_dispatch
+        from ..ops import attention_dispatch, gemm_bf16
+        w_in = self.w_qkv if writes else self.w_q
+        if not ctx.is_decode and self.position.fusable and self.runtime.act_dtype == torch.bfloat16:
+            cos, sin, rot = self.position.fused_tables()
+            x_in = h.materialize() if isinstance(h, kernels.NormedInput) else h
+            same_gains = self.q_gain is None or self.q_gain.dtype == self.k_gain.dtype
+            if ((cos is None or rot == HD) and same_gains and gemm_bf16.qkv_rope_supported(x_in, w_in, H, KV, HD)
+                    and kernels.attn_prefill_tcgen05_supported(x_in.dtype, H, KV, HD)):
+                # a prompt step: norm, rotation and the cache write happen in the projection's epilogue
+                q = gemm_bf16.gemm_qkv_rope(x_in, w_in, H, KV, HD, self.q_gain, self.k_gain, self.qk_eps, cos, sin,
+                                            ctx.tok_seq, ctx.tok_pos, pages,
+                                            cache.k if writes else None, cache.v if writes else None)
+                out = torch.empty((T, H * HD), dtype=q.dtype, device=q.device)
+                attention_dispatch.prefill(q, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0)
+                return kernels.linear(out, self.w_o)
+            h = x_in
+        qkv = kernels.linear(h, w_in)
         out = torch.empty((T, H * HD), dtype=qkv.dtype, device=qkv.device)
         if self.position.fusable:
             cos, sin, rot = self.position.fused_tables()

@@ -796,3 +796,78 @@ def test_gemm_tcgen05_swiglu_epilogue(M, F, K):
     finally:
         gemm_bf16.USE_TCGEN05 = True
     assert rel_err(unfused.float().cpu().numpy(), act.float().cpu().numpy()) < 1e-2
+
+
+@pytest.mark.parametrize("H,KV,K,with_norm,with_rope,with_cache", [(16, 8, 1024, True, True, True), (3, 1, 96, True, True, True),
+                                                                  (4, 2, 64, False, True, True), (5, 5, 128, True, False, False)])
+def test_gemm_qkv_rope_epilogue(H, KV, K, with_norm, with_rope, with_cache):
+    """The q/k/v projection whose epilogue norms, rotates and writes: against the plain parts, on a ragged
+    batch with padding rows and scattered pages, and against the separate product and rope/store pass."""
+    from mynah_slm_b200.ops import gemm_bf16
+    k = _k()
+    HD = 128
+    rng = np.random.default_rng(31)
+    lens, past = [150, 1, 70, 300], [0, 200, 64, 5]               # tokens this step, positions already in the cache
+    T, pad = sum(lens), 23                                          # 23 padding rows at the end
+    M = T + pad
+    heads = H + 2 * KV if with_cache else H
+    x = _round(rng.standard_normal((M, K)), "bf16")
+    w = _round(rng.standard_normal((heads * HD, K)) * (1.0 / np.sqrt(K)), "bf16")
+    qg = _round(1 + 0.1 * rng.standard_normal(HD), "bf16") if with_norm else None
+    kg = _round(1 + 0.1 * rng.standard_normal(HD), "bf16") if with_norm else None
+    dev = lambda a: None if a is None else torch.from_numpy(a).to(torch.bfloat16).to(DEV)
+    eps, theta = 1e-6, 30000.0
+    cos, sin = k.rope_table(700, HD, theta, DEV) if with_rope else (None, None)
+    cr, sr = rope_table(HD, np.arange(700), theta)
+    tok_seq = np.concatenate([[b] * n for b, n in enumerate(lens)] + [[-1] * pad]).astype(np.int32)
+    tok_pos = np.concatenate([np.arange(p, p + n) for p, n in zip(past, lens)] + [np.zeros(pad)]).astype(np.int32)
+    n_pages = 20
+    free = list(np.random.default_rng(32).permutation(n_pages))
+    lists = [[int(free.pop()) for _ in range(-(-(p + n) // 64))] for p, n in zip(past, lens)]
+    pt = _page_table(lists)(n_pages)
+    kc = torch.full((n_pages, KV, 64, HD), 99.0, dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((n_pages, KV, 64, HD), 99.0, dtype=torch.bfloat16, device=DEV)
+    xd, wd = dev(x), dev(w)
+    saved = gemm_bf16.USE_QKV_EPILOGUE
+    gemm_bf16.USE_QKV_EPILOGUE = True
+    try:
+        assert gemm_bf16.qkv_rope_supported(xd, wd, H, KV, HD)
+    finally:
+        gemm_bf16.USE_QKV_EPILOGUE = saved
+    q = gemm_bf16.gemm_qkv_rope(xd, wd, H, KV, HD, dev(qg), dev(kg), eps, cos, sin, torch.from_numpy(tok_seq).to(DEV),
+                                torch.from_numpy(tok_pos).to(DEV), pt, kc if with_cache else None, vc if with_cache else None)
+    assert gemm_bf16.status_word(torch.device(DEV)).item() == 0
+    y = x.astype(np.float64) @ w.astype(np.float64).T             # [M, heads * HD]
+
+    def prep(z, g):                                                # z [n, heads, HD] -> normed, rotated
+        z = rms_norm(z, g, eps) if with_norm else z
+        return rope_apply(z, cr[tok_pos[:T]], sr[tok_pos[:T]]) if with_rope else z
+    got_q = q.float().cpu().numpy()[:T]
+    ref_q = prep(y[:T, :H * HD].reshape(T, H, HD).astype(np.float32), qg).reshape(T, -1)
+    assert rel_err(ref_q, got_q) < 6e-3
+    if with_cache:
+        ref_k = prep(y[:T, H * HD:(H + KV) * HD].reshape(T, KV, HD).astype(np.float32), kg)
+        ref_v = y[:T, (H + KV) * HD:].reshape(T, KV, HD)
+        kc_np, vc_np = kc.float().cpu().numpy(), vc.float().cpu().numpy()
+        written = np.zeros((n_pages, 64), dtype=bool)
+        for t in range(T):
+            pg, off = lists[tok_seq[t]][tok_pos[t] // 64], tok_pos[t] % 64
+            written[pg, off] = True
+            assert rel_err(ref_k[t].reshape(1, -1), kc_np[pg, :, off].reshape(1, -1)) < 6e-3, t
+            assert rel_err(ref_v[t].reshape(1, -1), vc_np[pg, :, off].reshape(1, -1)) < 6e-3, t
+        assert np.all(kc_np.transpose(0, 2, 1, 3)[~written] == 99.0) and np.all(vc_np.transpose(0, 2, 1, 3)[~written] == 99.0)
+        # the separate route: product, then the rope/store pass (it norms the bf16-rounded product: rounding apart)
+        kc2, vc2 = torch.full_like(kc, 99.0), torch.full_like(vc, 99.0)
+        qkv = k.linear(xd, wd)
+        k.qk_norm_rope_store(qkv, H, KV, HD, dev(qg), dev(kg), eps, cos, sin, HD if with_rope else 0, torch.from_numpy(tok_seq).to(DEV),
+                             torch.from_numpy(tok_pos).to(DEV), pt, kc2, vc2, torch.zeros(1, dtype=torch.int32, device=DEV))
+        assert rel_err(qkv.float().cpu().numpy()[:T, :H * HD], got_q) < 1e-2
+        assert rel_err(kc2.float().cpu().numpy().reshape(n_pages, -1), kc_np.reshape(n_pages, -1)) < 1e-2
+        assert torch.equal(vc2, vc)                                # v is the rounded product either way
+    # a position beyond the rotation table is reported, not used
+    if with_rope:
+        gemm_bf16.gemm_qkv_rope(xd, wd, H, KV, HD, dev(qg), dev(kg), eps, cos, sin, torch.from_numpy(tok_seq).to(DEV),
+                                torch.from_numpy(tok_pos + 700).to(DEV), pt, None, None) if not with_cache else None
+        word = gemm_bf16.status_word(torch.device(DEV))
+        assert with_cache or word.item() & 2
+        word.zero_()
