@@ -16,6 +16,7 @@
 // score = dot * (1/sqrtf(head_dim)), maximum subtracted
 // (mynah-slm src/kernels.c:228-250, :207-220).
 #include "layout.cuh"
+#include "head_prep.cuh"
 
 namespace {
 
@@ -369,31 +370,6 @@ struct FusedArgs {
 };
 
 template <int HD>
-__device__ __forceinline__ void head_norm_rope(float (&v)[HD / 32], VecRef gain, float eps, const float* __restrict__ cos_t,
-                                               const float* __restrict__ sin_t, int pos, int lane) {
-    constexpr int EPL = HD / 32;
-    if (gain.p != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < EPL; j++) ss += v[j] * v[j];
-        ss = warp_sum(ss);
-        const float sc = 1.0f / sqrtf(ss / (float)HD + eps);
-#pragma unroll
-        for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * gain.at(lane * EPL + j));
-    }
-    if (cos_t != nullptr) {
-        const int i0 = (lane & 15) * EPL;           // lanes 0-15 hold the first half of the head, 16-31 the second
-        const float* c = cos_t + (size_t)pos * (HD / 2) + i0;
-        const float* sn = sin_t + (size_t)pos * (HD / 2) + i0;
-#pragma unroll
-        for (int j = 0; j < EPL; j++) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-            v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
-        }
-    }
-}
-
-template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -401,7 +377,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, FusedArgs a,
                          float* __restrict__ part_o, float* __restrict__ part_ml, unsigned* __restrict__ counters,
                          bf16* __restrict__ out, int* __restrict__ status) {
-    constexpr int CH = HD / 8, KSTEPS = HD / 16, EPL = HD / 32, NT = HD / 32;
+    constexpr int CH = HD / 8, KSTEPS = HD / 16, NT = HD / 32;
     constexpr int QLD = HD + 8;                       // padded row of the query tile: no bank conflicts on its loads
     __shared__ __align__(128) unsigned char k_s[KEYS * HD * 2];     // reused by the merge for the pages' weights
     __shared__ __align__(128) unsigned char v_s[KEYS * HD * 2];     // reused by the merge for its series
@@ -462,61 +438,44 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
         }
         cp_async_commit();
 
-        // ---- the group's queries: norm, rotation, to shared memory as bf16; rows beyond G are zero
+        // ---- the group's queries: norm, rotation, to shared memory as bf16; rows beyond G are zero.
+        // Heads lie side by side in a warp (head_prep.cuh), as in the rope/store pass, whose bits these are.
+        constexpr int LPH = HeadLanes<HD>::LPH, HPW = HeadLanes<HD>::HPW;
+        const int sub = lane / LPH, li = lane % LPH;
+        const bool rotate = cos_t != nullptr, has_gain = q_gain.p != nullptr;
+        float rc[8], rs[8], qgv[8], kgv[8];
+        if (rotate) load_rotation<HD>(cos_t, sin_t, pos, lane, rc, rs);
+        if (has_gain) {
+            load_gain8(q_gain, li * 8, qgv);
+            load_gain8(k_gain, li * 8, kgv);
+        }
         const bf16* qrow = qkv + (size_t)b * a.ldq;
-        for (int h = warp; h < MAX_G; h += WARPS) {
-            bf16 o[EPL];
-            if (h < G) {
-                float v[EPL];
-                bf16 raw[EPL];
-                const bf16* src = qrow + (size_t)(g * G + h) * HD + lane * EPL;
-                if (EPL == 4) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(src);
-                else *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(src);
+        for (int hbase = warp * HPW; hbase < MAX_G; hbase += WARPS * HPW) {      // uniform over the warp
+            const int h = hbase + sub;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (h < G) load8<bf16>(qrow + (size_t)(g * G + h) * HD + li * 8, v);
+            head_norm_rotate<HD>(v, has_gain, qgv, a.qk_eps, rotate, rc, rs, lane);
+            if (h >= G) {
 #pragma unroll
-                for (int j = 0; j < EPL; j++) v[j] = to_f32(raw[j]);
-                head_norm_rope<HD>(v, q_gain, a.qk_eps, cos_t, sin_t, pos, lane);
-#pragma unroll
-                for (int j = 0; j < EPL; j++) o[j] = __float2bfloat16_rn(v[j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < EPL; j++) o[j] = __float2bfloat16_rn(0.f);
+                for (int j = 0; j < 8; j++) v[j] = 0.f;
             }
-            if (EPL == 4) *reinterpret_cast<uint2*>(q_s + h * QLD + lane * EPL) = *reinterpret_cast<const uint2*>(o);
-            else *reinterpret_cast<uint32_t*>(q_s + h * QLD + lane * EPL) = *reinterpret_cast<const uint32_t*>(o);
+            if (h < MAX_G) store8<bf16>(q_s + h * QLD + li * 8, v);
         }
         // ---- the new position's k and v, by the CTA that has its page: to the cache and into the tiles
         if (r_new >= 0 && warp == WARPS - 1) {
-            float kv[EPL];
-            bf16 kraw[EPL], vraw[EPL], ko[EPL];
-            const bf16* ksrc = qrow + (size_t)(a.H + g) * HD + lane * EPL;
-            const bf16* vsrc = qrow + (size_t)(a.H + a.KV + g) * HD + lane * EPL;
-            if (EPL == 4) {
-                *reinterpret_cast<uint2*>(kraw) = *reinterpret_cast<const uint2*>(ksrc);
-                *reinterpret_cast<uint2*>(vraw) = *reinterpret_cast<const uint2*>(vsrc);
-            } else {
-                *reinterpret_cast<uint32_t*>(kraw) = *reinterpret_cast<const uint32_t*>(ksrc);
-                *reinterpret_cast<uint32_t*>(vraw) = *reinterpret_cast<const uint32_t*>(vsrc);
-            }
+            float kv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (sub == 0) load8<bf16>(qrow + (size_t)(a.H + g) * HD + li * 8, kv);
+            head_norm_rotate<HD>(kv, has_gain, kgv, a.qk_eps, rotate, rc, rs, lane);    // the whole warp; one lane group holds the head
+            if (sub == 0) {
+                const uint4 vraw = *reinterpret_cast<const uint4*>(qrow + (size_t)(a.H + a.KV + g) * HD + li * 8);
+                uint4 ko;
+                __nv_bfloat162* kh = reinterpret_cast<__nv_bfloat162*>(&ko);
 #pragma unroll
-            for (int j = 0; j < EPL; j++) kv[j] = to_f32(kraw[j]);
-            head_norm_rope<HD>(kv, k_gain, a.qk_eps, cos_t, sin_t, pos, lane);
-#pragma unroll
-            for (int j = 0; j < EPL; j++) ko[j] = __float2bfloat16_rn(kv[j]);
-            const int d = lane * EPL;                 // EPL elements stay inside one 16-byte chunk
-            bf16* kg = k_cache + tile + (size_t)r_new * HD + d;
-            bf16* vg = v_cache + tile + (size_t)r_new * HD + d;
-            unsigned char* ks = k_s + swz<CH>(r_new, d / 8) + (d % 8) * 2;
-            unsigned char* vs = v_s + swz<CH>(r_new, d / 8) + (d % 8) * 2;
-            if (EPL == 4) {
-                *reinterpret_cast<uint2*>(kg) = *reinterpret_cast<const uint2*>(ko);
-                *reinterpret_cast<uint2*>(vg) = *reinterpret_cast<const uint2*>(vraw);
-                *reinterpret_cast<uint2*>(ks) = *reinterpret_cast<const uint2*>(ko);
-                *reinterpret_cast<uint2*>(vs) = *reinterpret_cast<const uint2*>(vraw);
-            } else {
-                *reinterpret_cast<uint32_t*>(kg) = *reinterpret_cast<const uint32_t*>(ko);
-                *reinterpret_cast<uint32_t*>(vg) = *reinterpret_cast<const uint32_t*>(vraw);
-                *reinterpret_cast<uint32_t*>(ks) = *reinterpret_cast<const uint32_t*>(ko);
-                *reinterpret_cast<uint32_t*>(vs) = *reinterpret_cast<const uint32_t*>(vraw);
+                for (int j = 0; j < 4; j++) kh[j] = __floats2bfloat162_rn(kv[2 * j], kv[2 * j + 1]);
+                *reinterpret_cast<uint4*>(k_cache + tile + (size_t)r_new * HD + li * 8) = ko;
+                *reinterpret_cast<uint4*>(v_cache + tile + (size_t)r_new * HD + li * 8) = vraw;
+                *reinterpret_cast<uint4*>(k_s + swz<CH>(r_new, li)) = ko;       // a lane's eight elements are one 16-byte chunk
+                *reinterpret_cast<uint4*>(v_s + swz<CH>(r_new, li)) = vraw;
             }
         }
         cp_async_wait<1>();                           // K has landed (V may still be in flight)

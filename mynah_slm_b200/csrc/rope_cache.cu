@@ -13,6 +13,7 @@
 // (src/kernels.c:154-162) and stored as float. Values are rounded to the
 // activation or cache type once, when stored.
 #include "layout.cuh"
+#include "head_prep.cuh"
 
 namespace {
 
@@ -118,35 +119,12 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
     }
 }
 
-// The same pass for head sizes that are a multiple of 32 with the whole head rotated: a lane keeps
-// head_dim/32 consecutive elements in registers, its rotation partner is the lane 16 further on, so
-// nothing goes through shared memory and every access is a vector. A warp takes `hpw` consecutive heads of
-// one token, four at a time with their loads in flight together; the token's position, page, rotation
-// row and the gains are fetched once for all of them.
-template <typename T, int EPL>
-struct HeadVec {
-    T raw[EPL];
-    __device__ __forceinline__ void load(const T* p) {
-        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(p);
-        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(p);
-        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(p);
-        else {
-#pragma unroll
-            for (int j = 0; j < EPL; j++) raw[j] = p[j];
-        }
-    }
-    __device__ __forceinline__ void store(T* p) const {
-        if (sizeof(T) * EPL == 16) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(raw);
-        else if (sizeof(T) * EPL == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(raw);
-        else if (sizeof(T) * EPL == 4) *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(raw);
-        else {
-#pragma unroll
-            for (int j = 0; j < EPL; j++) p[j] = raw[j];
-        }
-    }
-};
-
-template <typename T, int EPL>
+// The same pass for head sizes 32, 64, 128 and 256 with the whole head rotated (or none of it): a head lies
+// across head_dim / 8 lanes, eight consecutive elements a lane, so a warp works on 32 / (head_dim / 8) heads
+// with every instruction, nothing goes through shared memory and every access is a 16-byte vector (two for
+// fp32). A warp takes `hpw` consecutive heads of one token, up to four such passes with their loads in flight
+// together; the token's position, page, rotation row and the gains are fetched once for all of them.
+template <typename T, int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -155,7 +133,7 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
                                QkvArgs a, int hpw, int* __restrict__ status) {
     griddep_launch();
     griddep_wait();
-    constexpr int HD = EPL * 32;
+    constexpr int LPH = HeadLanes<HD>::LPH, HPW = HeadLanes<HD>::HPW;
     constexpr int BATCH = 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = k_cache != nullptr ? a.H + 2 * a.KV : a.H;
@@ -166,34 +144,26 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
     const int seq = tok_seq[t];
     if (seq < 0) return;
     const int pos = tok_pos[t];
-    T* row = qkv + (size_t)t * a.ld + lane * EPL;
-    // the first batch's loads go out before anything that depends on the position
-    HeadVec<T, EPL> in[BATCH];
+    const int sub = lane / LPH, li = lane % LPH;           // which of the warp's heads, and where in it
+    T* row = qkv + (size_t)t * a.ld + li * 8;
+    // the first passes' loads go out before anything that depends on the position
+    Raw8<T> in[BATCH];
 #pragma unroll
-    for (int i = 0; i < BATCH; i++)
-        if (h0 + i < h1) in[i].load(row + (size_t)(h0 + i) * HD);
+    for (int i = 0; i < BATCH; i++) {
+        const int h = h0 + i * HPW + sub;
+        if (h < h1) in[i].load(row + (size_t)h * HD);
+    }
     const bool rotate = cos_t != nullptr;
     if (rotate && (pos < 0 || pos >= a.n_pos)) {
         if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
         return;
     }
-    float c[EPL], sn[EPL], qg[EPL], kg[EPL];
-    if (rotate) {
-        // lanes 0-15 hold the first half of the head, lanes 16-31 the second
-        const int i0 = (lane & 15) * EPL;
-#pragma unroll
-        for (int j = 0; j < EPL; j++) {
-            c[j] = cos_t[(size_t)pos * (HD / 2) + i0 + j];
-            sn[j] = sin_t[(size_t)pos * (HD / 2) + i0 + j];
-        }
-    }
+    float c[8], sn[8], qg[8], kg[8];
+    if (rotate) load_rotation<HD>(cos_t, sin_t, pos, lane, c, sn);
     const bool has_gain = q_gain.p != nullptr;
     if (has_gain) {
-#pragma unroll
-        for (int j = 0; j < EPL; j++) {
-            qg[j] = q_gain.at(lane * EPL + j);
-            kg[j] = k_gain.at(lane * EPL + j);
-        }
+        load_gain8(q_gain, li * 8, qg);
+        load_gain8(k_gain, li * 8, kg);
     }
     size_t cache_row = 0;
     if (h1 > a.H) {                                        // some head of this warp goes to the cache
@@ -204,69 +174,52 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
         }
         cache_row = (size_t)page * a.KV * PAGE_TOKENS + pos % PAGE_TOKENS;
     }
-    for (int hb = h0; hb < h1; hb += BATCH) {
-        HeadVec<T, EPL> nxt[BATCH];
+    for (int hb = h0; hb < h1; hb += BATCH * HPW) {
+        if (hb != h0) {
 #pragma unroll
-        for (int i = 0; i < BATCH; i++)
-            if (hb + BATCH + i < h1) nxt[i].load(row + (size_t)(hb + BATCH + i) * HD);
-#pragma unroll
-        for (int i = 0; i < BATCH; i++) {
-            const int h = hb + i;
-            if (h >= h1) break;
-            const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
-            const int kvh = is_q ? 0 : (is_k ? h - a.H : h - a.H - a.KV);
-            T* dst = is_q ? row + (size_t)h * HD
-                          : (is_k ? k_cache : v_cache) + (cache_row + (size_t)kvh * PAGE_TOKENS) * HD + lane * EPL;
-            if (!is_q && !is_k) {                          // V: copy
-                in[i].store(dst);
-                continue;
+            for (int i = 0; i < BATCH; i++) {
+                const int h = hb + i * HPW + sub;
+                if (h < h1) in[i].load(row + (size_t)h * HD);
             }
-            float v[EPL];
-            float ss = 0.f;
-#pragma unroll
-            for (int j = 0; j < EPL; j++) {
-                v[j] = to_f32(in[i].raw[j]);
-                ss += v[j] * v[j];
-            }
-            if (has_gain) {
-                ss = warp_sum(ss);
-                const float sc = 1.0f / sqrtf(ss / (float)HD + a.eps);
-#pragma unroll
-                for (int j = 0; j < EPL; j++) v[j] = v[j] * (sc * (is_q ? qg[j] : kg[j]));
-            }
-            if (rotate) {
-#pragma unroll
-                for (int j = 0; j < EPL; j++) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
-                    v[j] = lane < 16 ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
-                }
-            }
-            HeadVec<T, EPL> o;
-#pragma unroll
-            for (int j = 0; j < EPL; j++) o.raw[j] = from_f32<T>(v[j]);
-            o.store(dst);
         }
 #pragma unroll
-        for (int i = 0; i < BATCH; i++) in[i] = nxt[i];
+        for (int i = 0; i < BATCH; i++) {
+            if (hb + i * HPW >= h1) break;                 // uniform over the warp
+            const int h = hb + i * HPW + sub;              // this lane group's head (may lie beyond the warp's heads)
+            const bool mine = h < h1;
+            const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
+            float v[8];
+            in[i].to_f32(v);                               // (a lane group without a head works on whatever is there)
+            if (mine && !is_q && !is_k) {                  // V: copy (no shuffles inside)
+                const int kvh = h - a.H - a.KV;
+                store8<T>(v_cache + (cache_row + (size_t)kvh * PAGE_TOKENS) * HD + li * 8, v);
+            }
+            // every lane takes part in the norm and the rotation; what is not a q or k head is dropped afterwards
+            head_norm_rotate<HD>(v, has_gain, is_q ? qg : kg, a.eps, rotate, c, sn, lane);
+            if (mine && is_q) store8<T>(row + (size_t)h * HD, v);
+            else if (mine && is_k) store8<T>(k_cache + (cache_row + (size_t)(h - a.H) * PAGE_TOKENS) * HD + li * 8, v);
+        }
     }
 }
 
 template <typename T>
 bool launch_fast(int HD, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, const float* cos_t,
                  const float* sin_t, const int* tok_seq, const int* tok_pos, PageTable pt, T* kc, T* vc, QkvArgs a, int* status) {
-    // heads per warp: one while the step is small (latency matters), up to eight when there are many tokens
+    if (HD != 32 && HD != 64 && HD != 128 && HD != 256) return false;
+    // heads per warp: one pass while the step is small (latency matters), up to four passes when there are many tokens
     const int heads = kc != nullptr ? a.H + 2 * a.KV : a.H;
-    const long long units1 = (long long)a.T * heads;
-    int hpw = 1;
-    while (hpw < 8 && units1 / hpw > 148 * 16) hpw *= 2;
+    const int per_pass = 32 / (HD / 8);
+    const long long units1 = (long long)a.T * ((heads + per_pass - 1) / per_pass);
+    int passes = 1;
+    while (passes < 4 && units1 / passes > 148 * 16) passes *= 2;
+    const int hpw = per_pass * passes;
     const int groups = (heads + hpw - 1) / hpw;
     const unsigned blocks = (unsigned)ceil_div_ll((long long)a.T * groups, WARPS);
     switch (HD) {
-        case 32: mynah_launch(qk_norm_rope_store_fast_kernel<T, 1>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
-        case 64: mynah_launch(qk_norm_rope_store_fast_kernel<T, 2>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
-        case 128: mynah_launch(qk_norm_rope_store_fast_kernel<T, 4>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
-        case 256: mynah_launch(qk_norm_rope_store_fast_kernel<T, 8>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
-        default: return false;
+        case 32: mynah_launch(qk_norm_rope_store_fast_kernel<T, 32>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        case 64: mynah_launch(qk_norm_rope_store_fast_kernel<T, 64>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        case 128: mynah_launch(qk_norm_rope_store_fast_kernel<T, 128>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
+        default: mynah_launch(qk_norm_rope_store_fast_kernel<T, 256>, dim3(blocks), dim3(WARPS * 32), 0, stream, qkv, qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, kc, vc, a, hpw, status); return true;
     }
 }
 
