@@ -51,6 +51,8 @@ def _lib():
             "mynah_books_commit": (I, [P, I, I]), "mynah_books_held": (I, [P, I, I, IP, I, IP]),
             "mynah_books_live_slots": (I, [P, IP, I]), "mynah_books_pool": (P, [P, I]), "mynah_books_slots": (P, [P]),
             "mynah_step_fill": (I, [P, IP, IP, I, I, I, IP, I, IP, IP, IP, IP, IP, IP]),
+            "mynah_decode_prepare": (I, [P, I, IP, IP, I, I, IP, IP, I, I, I, IP]),
+            "mynah_books_commit_many": (I, [P, I, IP, I]),
         }
         for name, (res, args) in sigs.items():
             fn = getattr(lib, name)
@@ -253,3 +255,17 @@ class SequencePages:
         max_q = _check(_lib().mynah_step_fill(self._h, ip(buf), ip(offsets), T, B, W, ip(ids_cap), n, ip(slot_a), ip(n_tok),
                                               ip(toks) if toks.size else None, nw_p, w_p, ctypes.byref(rows)))
         return max_q, int(rows.value)
+
+    def max_length(self, slots: Sequence[int]) -> int:
+        return max(self.length[s] for s in slots)
+
+    def decode_prepare(self, buf: np.ndarray, offsets: np.ndarray, T: int, B: int, W: int, ids_cap: np.ndarray,
+                       slots: np.ndarray, tokens: np.ndarray, vocab: int, max_positions: int) -> int:
+        """One more token for each of `slots` (int32 arrays): checks, pages and the step's description in one
+        native call. Returns the longest sequence after the step."""
+        ip = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
+        return _check(_lib().mynah_decode_prepare(self._h, len(slots), ip(slots), ip(tokens), int(vocab), int(max_positions),
+                                                  ip(buf), ip(offsets), T, B, W, ip(ids_cap)))
+
+    def commit_many(self, slots: np.ndarray, n_new: int) -> None:
+        _check(_lib().mynah_books_commit_many(self._h, len(slots), slots.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), int(n_new)))

@@ -345,4 +345,31 @@ int mynah_step_fill(const mynah_books* b, int32_t* buf, const int32_t* off, int 
     return max_q;
 }
 
+int mynah_decode_prepare(mynah_books* b, int n, const int32_t* slot, const int32_t* token, int vocab, int max_positions,
+                         int32_t* buf, const int32_t* off, int T, int B, int W, const int32_t* ids_cap) {
+    if (n < 1) return fail("a step needs at least one sequence");
+    int max_kv = 0;
+    for (int i = 0; i < n; i++) {
+        auto it = b->live.find(slot[i]);
+        if (it == b->live.end()) return fail("slot %d is not open", slot[i]);
+        for (int j = 0; j < i; j++)
+            if (slot[j] == slot[i]) return fail("slot %d appears twice in one step", slot[i]);
+        if (token[i] < 0 || token[i] >= vocab) return fail("token id %d lies outside the vocabulary of %d", token[i], vocab);
+        if (it->second.length + 1 > max_positions)
+            return fail("slot %d would grow to %d positions, the model allows %d", slot[i], it->second.length + 1, max_positions);
+        max_kv = std::max(max_kv, it->second.length + 1);
+    }
+    for (int i = 0; i < n; i++)
+        if (mynah_books_reserve(b, slot[i], 1)) return -1;
+    std::vector<int32_t> ones(n, 1);
+    if (mynah_step_fill(b, buf, off, T, B, W, ids_cap, n, slot, ones.data(), token, nullptr, nullptr, nullptr) < 0) return -1;
+    return max_kv;
+}
+
+int mynah_books_commit_many(mynah_books* b, int n, const int32_t* slot, int n_new) {
+    for (int i = 0; i < n; i++)
+        if (mynah_books_commit(b, slot[i], n_new)) return -1;
+    return 0;
+}
+
 }  // extern "C"

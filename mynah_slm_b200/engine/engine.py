@@ -483,17 +483,39 @@ class Engine:
         """One decode step for `slots` with `tokens` as their next inputs;
         samples on the device with the sampler's current parameters and returns
         the int32 tokens [bucket] (device; the first len(slots) rows count)."""
+        pages = self.cache.pages
+        if self.use_graphs and self.graph_safe:
+            # the common case: checks, pages and the step's description in one call of the native host runtime
+            slots_a = np.asarray(slots, dtype=np.int32)
+            toks_a = np.asarray(tokens, dtype=np.int32)
+            if len(slots_a) == 0:
+                raise EngineError("a step needs at least one sequence")
+            try:
+                max_kv = pages.max_length(slots_a.tolist()) + 1
+            except KeyError as e:
+                raise EngineError(f"slot {e.args[0]} is not open") from None
+            g = self._graph_for(len(slots_a), max_kv)
+            host, hi = self._staging.get(g.layout.size)
+            from ..cache import CacheError
+            try:
+                pages.decode_prepare(host.numpy(), g.layout.offsets_array, g.layout.T, g.layout.B, g.layout.W,
+                                     g.layout.ids_cap_array, slots_a, toks_a, self.spec.vocab_size, self.spec.max_positions)
+            except CacheError as e:
+                if "cache is full" in str(e):
+                    raise
+                raise EngineError(str(e)) from None
+            g.meta.copy_(host[:g.layout.size], non_blocking=True)
+            self._staging.sent(hi)
+            out = self._run_graph(g, "sample", 1)
+            pages.commit_many(slots_a, 1)
+            return out
         entries = [StepEntry(s, (int(t),)) for s, t in zip(slots, tokens)]
         self._validate(entries)
-        pages = self.cache.pages
         for e in entries:
             pages.reserve(e.slot, 1)
-        if self.use_graphs and self.graph_safe:
-            out = self._decode_graph_step(entries, "sample")
-        else:
-            logits = self._eager_step([StepEntry(e.slot, e.tokens, (0,)) for e in entries], True)
-            slots_t = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
-            out = self.sampler.sample(logits, slots_t)
+        logits = self._eager_step([StepEntry(e.slot, e.tokens, (0,)) for e in entries], True)
+        slots_t = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+        out = self.sampler.sample(logits, slots_t)
         for e in entries:
             pages.commit(e.slot, 1)
         return out

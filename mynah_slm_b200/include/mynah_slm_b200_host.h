@@ -67,6 +67,14 @@ int mynah_step_fill(const mynah_books*, int32_t* buf, const int32_t* off, int T,
                     int n_entries, const int32_t* slot, const int32_t* n_tok, const int32_t* tokens,
                     const int32_t* n_want, const int32_t* want, int32_t* n_rows);
 
+/* ---- one decoded token for each of n live sequences, in one call: checks (slots open and distinct, token ids below
+ * `vocab`, lengths below `max_positions`), a page for the new position in every group, and the step's description
+ * as mynah_step_fill writes it (no wanted rows: a decode graph returns every row). Returns the longest sequence
+ * after the step. mynah_books_commit_many advances the sequences once the step has been launched. */
+int mynah_decode_prepare(mynah_books*, int n, const int32_t* slot, const int32_t* token, int vocab, int max_positions,
+                         int32_t* buf, const int32_t* off, int T, int B, int W, const int32_t* ids_cap);
+int mynah_books_commit_many(mynah_books*, int n, const int32_t* slot, int n_new);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif
