@@ -23,7 +23,9 @@ from golden_common import CONFIGS, build  # noqa: E402
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and not os.environ.get("MYNAH_REFERENCE"):
+        raise SystemExit("usage: make_golden.py <checkout of mynah-org/mynah-slm>   (or set MYNAH_REFERENCE)")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["MYNAH_REFERENCE"]
     sys.path.insert(0, os.path.join(ref, "tools"))
     from oracle.model import Qwen3Model
     out = {}

@@ -1,4 +1,4 @@
-"""Plain, slow, whole-sequence implementation used as the judge of the engine.
+"""Plain, slow, whole-sequence implementation that the engine is measured against.
 
 Nothing here imports the product package: it has its own config reading, its
 own safetensors reading, its own formulas. It rests on the reference's

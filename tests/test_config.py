@@ -10,7 +10,12 @@ from mynah_slm_b200.config.qwen3 import Qwen3Config
 
 
 def test_official_config_reads():
-    path = "/root/reference/reference/qwen3-0.6b/config.json"
+    """The official Qwen3-0.6B config.json that the reference's checkout carries (reference/qwen3-0.6b/), when a
+    checkout is at hand: $MYNAH_REFERENCE, or a folder `reference` beside this repository."""
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.environ.get("MYNAH_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(here)), "reference")
+    path = os.path.join(root, "reference", "qwen3-0.6b", "config.json")
     try:
         cfg = json.load(open(path))
         gen = json.load(open(path.replace("config.json", "generation_config.json")))
