@@ -16,6 +16,7 @@
 namespace {
 
 constexpr int THREADS = 1024;
+constexpr int LOADS = 8;               // loads of a row that a thread keeps in flight
 constexpr int BINS = 2048;
 
 __device__ __forceinline__ unsigned long long mass_of(float p) {
@@ -31,7 +32,9 @@ struct Prefix {            // a prefix of the sorted order
 
 struct Shared {
     unsigned int count[BINS];
-    unsigned long long mass[BINS];
+    // a digit's mass (2^-60 fixed point) as two 32-bit words: 32-bit adds are native atomics in shared memory,
+    // 64-bit ones are compare-and-swap loops that crawl when many warps hit one digit
+    unsigned int mass_lo[BINS], mass_hi[BINS];
     unsigned int warp_count[32];
     unsigned long long warp_mass[32];
     // results handed from the finding thread to the block
@@ -42,6 +45,19 @@ struct Shared {
     double red_d[32];
     unsigned int scan_u[32];
 };
+
+__device__ __forceinline__ void add_mass(Shared& sh, unsigned int d, unsigned long long m) {
+    const unsigned int lo = (unsigned int)m;
+    unsigned int hi = (unsigned int)(m >> 32);
+    if (lo != 0) {
+        const unsigned int old = atomicAdd(&sh.mass_lo[d], lo);
+        hi += old > 0xffffffffu - lo;                      // the low word wrapped: carry
+    }
+    if (hi != 0) atomicAdd(&sh.mass_hi[d], hi);
+}
+__device__ __forceinline__ unsigned long long mass_at(const Shared& sh, int d) {
+    return ((unsigned long long)sh.mass_hi[d] << 32) | sh.mass_lo[d];
+}
 
 // Finds the digit where the running (count, mass), taken from the largest
 // digit down, first satisfies the target, among elements whose higher bits
@@ -55,27 +71,71 @@ __device__ void radix_pass(const float* __restrict__ p, int V, unsigned int pref
                            Shared& sh) {
     for (int i = threadIdx.x; i < BINS; i += THREADS) {
         sh.count[i] = 0;
-        sh.mass[i] = 0;
+        sh.mass_lo[i] = 0;
+        sh.mass_hi[i] = 0;
     }
     if (threadIdx.x == 0) {
         sh.found_digit = 0;                 // the smallest digit, when the target is never met
         sh.found_above = 0xffffffffu;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += THREADS) {
-        const float v = p[i];
-        const unsigned int bits = __float_as_uint(v);
-        if ((bits & prefix_mask) == prefix_bits) {
-            const unsigned int d = (bits >> shift) & (n_bins - 1);
-            atomicAdd(&sh.count[d], 1u);
-            atomicAdd(&sh.mass[d], mass_of(v));
+    // Probabilities crowd into a few digits where the digit is the exponent (the first pass): a warp whose 32
+    // elements fall into at most four digits adds each digit's count and mass up with shuffles and lets one lane
+    // do the two atomics; a warp whose elements are spread out (the mantissa passes) uses plain atomics. Counts
+    // and masses are integers, so the order of the additions does not matter.
+    // A row of a large vocabulary comes from L2, a round trip a load: eight loads a thread are issued together.
+    const int lane_h = threadIdx.x & 31;
+    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {     // the same number of turns for every thread
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < V ? p[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            if (base0 + u * THREADS >= V) break;                  // uniform
+            bool on = false;
+            unsigned int d = 0xffffffffu;
+            unsigned long long ms = 0;
+            if (i < V) {
+                const float v = vals[u];
+                const unsigned int bits = __float_as_uint(v);
+                if ((bits & prefix_mask) == prefix_bits) {
+                    on = true;
+                    d = (bits >> shift) & (n_bins - 1);
+                    ms = mass_of(v);
+                }
+            }
+            const unsigned int peers = __match_any_sync(0xffffffffu, d);
+            const bool leader = on && lane_h == __ffs(peers) - 1;
+            const unsigned int leaders = __ballot_sync(0xffffffffu, leader);
+            if (__popc(leaders) <= 4) {
+                unsigned int rem = leaders;
+                while (rem) {                                     // uniform over the warp
+                    const int src = __ffs(rem) - 1;
+                    rem &= rem - 1;
+                    const unsigned int grp = __shfl_sync(0xffffffffu, peers, src);
+                    unsigned long long m = ((grp >> lane_h) & 1u) ? ms : 0ull;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) m += __shfl_xor_sync(0xffffffffu, m, o);
+                    if (lane_h == src) {
+                        atomicAdd(&sh.count[d], (unsigned int)__popc(grp));
+                        add_mass(sh, d, m);
+                    }
+                }
+            } else if (on) {
+                atomicAdd(&sh.count[d], 1u);
+                add_mass(sh, d, ms);
+            }
         }
     }
     __syncthreads();
     // scan from the largest digit down: thread t owns digits n_bins-1-2t and n_bins-2-2t
     const int d0 = n_bins - 1 - 2 * (int)threadIdx.x, d1 = d0 - 1;
     const unsigned int c0 = d0 >= 0 ? sh.count[d0] : 0, c1 = d1 >= 0 ? sh.count[d1] : 0;
-    const unsigned long long m0 = d0 >= 0 ? sh.mass[d0] : 0, m1 = d1 >= 0 ? sh.mass[d1] : 0;
+    const unsigned long long m0 = d0 >= 0 ? mass_at(sh, d0) : 0, m1 = d1 >= 0 ? mass_at(sh, d1) : 0;
     unsigned int cs = c0 + c1;
     unsigned long long ms = m0 + m1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -124,7 +184,7 @@ __device__ void radix_pass(const float* __restrict__ p, int V, unsigned int pref
             unsigned long long m = carry_mass;
             for (int e = n_bins - 1; e > d; e--) {
                 c += sh.count[e];
-                m += sh.mass[e];
+                m += mass_at(sh, e);
             }
             sh.found_digit = (unsigned int)d;
             sh.found_above = c;
@@ -372,10 +432,22 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     }
     // p_i = expf((l_i - max) / temp) * (float)(1 / sum), the sum in double (sampler.c:132-143)
     double part = 0.0;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
-        const float e = expf((row[i] - mx) / sp.temp);
-        row[i] = e;
-        part += (double)e;
+    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < V ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            if (i < V) {
+                const float e = expf((vals[u] - mx) / sp.temp);
+                row[i] = e;
+                part += (double)e;                          // in index order within a thread, as before
+            }
+        }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -387,7 +459,19 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     const float inv = (float)(1.0 / sum);
     unsigned int n_floor = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += THREADS) row[i] = row[i] * inv;
+    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < V ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            if (i < V) row[i] = vals[u] * inv;
+        }
+    }
     __syncthreads();
     const float p_best = row[best];
 
