@@ -13,9 +13,14 @@
 // generator state give the same token in every run.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace {
 
+namespace cg = cooperative_groups;
+
 constexpr int THREADS = 1024;
+constexpr int ROW_CTAS = 8;            // CTAs (one cluster) that share a row of a large vocabulary
 constexpr int LOADS = 8;               // loads of a row that a thread keeps in flight
 constexpr int BINS = 2048;
 
@@ -37,9 +42,13 @@ struct Shared {
     unsigned int mass_lo[BINS], mass_hi[BINS];
     unsigned int warp_count[32];
     unsigned long long warp_mass[32];
-    // results handed from the finding thread to the block
-    unsigned int found_digit, found_above;
-    unsigned long long found_mass;
+    // results handed from the finding thread to the block (and, in a cluster, read by the other CTAs); two
+    // sets used in turn, so that one pass's results can still be read while the next pass starts
+    unsigned int found_digit[2], found_above[2], found_count[2];
+    unsigned long long found_mass[2];
+    unsigned int turn;                 // passes done so far (selects the set)
+    double part_d;                     // this CTA's share of a sum over the row
+    unsigned int part_u;
     float red_f[32];
     int red_i[32];
     double red_d[32];
@@ -59,47 +68,77 @@ __device__ __forceinline__ unsigned long long mass_at(const Shared& sh, int d) {
     return ((unsigned long long)sh.mass_hi[d] << 32) | sh.mass_lo[d];
 }
 
-// Finds the digit where the running (count, mass), taken from the largest
-// digit down, first satisfies the target, among elements whose higher bits
-// equal `prefix_bits` under `prefix_mask`. by_mass: cum_mass >= target_mass;
-// else cum_count >= target_count. On return sh.found_digit is that digit and
-// sh.found_above / sh.found_mass are the count and mass of the elements in
-// larger digits (added to what the caller carries).
-__device__ void radix_pass(const float* __restrict__ p, int V, unsigned int prefix_bits, unsigned int prefix_mask,
-                           int shift, int n_bins, bool by_mass, unsigned int target_count,
-                           unsigned long long target_mass, unsigned int carry_count, unsigned long long carry_mass,
-                           Shared& sh) {
+// A row is shared by NC CTAs (NC = 1, or the ROW_CTAS CTAs of a cluster): CTA r works on the elements
+// [r * chunk, (r + 1) * chunk) and the CTAs meet through distributed shared memory. Every CTA of a row runs
+// the same code with the same decisions, so the cluster barriers below are reached by all of them.
+template <int NC>
+struct RowShare {
+    int rank, begin, end;                                   // this CTA's elements
+    __device__ RowShare(int V) {
+        if (NC == 1) {
+            rank = 0; begin = 0; end = V;
+        } else {
+            rank = (int)cg::this_cluster().block_rank();
+            const int chunk = ((V + NC - 1) / NC + 3) & ~3;
+            begin = min(V, rank * chunk);
+            end = min(V, begin + chunk);
+        }
+    }
+    __device__ __forceinline__ void sync() const {
+        if (NC == 1) __syncthreads();
+        else cg::this_cluster().sync();
+    }
+    template <typename T> __device__ __forceinline__ T* at(T* mine, int r) const {
+        return NC == 1 ? mine : cg::this_cluster().map_shared_rank(mine, r);
+    }
+};
+
+struct Found {
+    unsigned int digit, above, count;                       // the digit, the elements in larger digits, those in it
+    unsigned long long mass;                                // mass of the elements in larger digits
+};
+
+// Finds the digit where the running (count, mass), taken from the largest digit down, first satisfies the
+// target, among elements whose higher bits equal `prefix_bits` under `prefix_mask`. by_mass: cum_mass >=
+// target_mass; else cum_count >= target_count. The carried count and mass are those of the elements in larger
+// digits of earlier passes. Every thread of every CTA of the row gets the result.
+template <int NC>
+__device__ Found radix_pass(const float* __restrict__ p, const RowShare<NC>& rs, unsigned int prefix_bits, unsigned int prefix_mask,
+                            int shift, int n_bins, bool by_mass, unsigned int target_count,
+                            unsigned long long target_mass, unsigned int carry_count, unsigned long long carry_mass,
+                            Shared& sh) {
     for (int i = threadIdx.x; i < BINS; i += THREADS) {
         sh.count[i] = 0;
         sh.mass_lo[i] = 0;
         sh.mass_hi[i] = 0;
     }
-    if (threadIdx.x == 0) {
-        sh.found_digit = 0;                 // the smallest digit, when the target is never met
-        sh.found_above = 0xffffffffu;
-    }
+    const unsigned int set = sh.turn & 1u;                  // (read before the barrier below; advanced after the last read)
     __syncthreads();
+    if (threadIdx.x == 0) {
+        sh.found_digit[set] = 0;                            // the smallest digit, when the target is never met
+        sh.found_above[set] = 0xffffffffu;
+    }
     // Probabilities crowd into a few digits where the digit is the exponent (the first pass): a warp whose 32
     // elements fall into at most four digits adds each digit's count and mass up with shuffles and lets one lane
-    // do the two atomics; a warp whose elements are spread out (the mantissa passes) uses plain atomics. Counts
-    // and masses are integers, so the order of the additions does not matter.
-    // A row of a large vocabulary comes from L2, a round trip a load: eight loads a thread are issued together.
+    // do the atomics; a warp whose elements are spread out (the mantissa passes) uses plain atomics. Counts
+    // and masses are integers, so the order of the additions does not matter. A row of a large vocabulary
+    // comes from L2, a round trip a load: eight loads a thread are issued together.
     const int lane_h = threadIdx.x & 31;
-    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {     // the same number of turns for every thread
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {    // the same number of turns for every thread
         float vals[LOADS];
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            vals[u] = i < V ? p[i] : 0.f;
+            vals[u] = i < rs.end ? p[i] : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            if (base0 + u * THREADS >= V) break;                  // uniform
+            if (base0 + u * THREADS >= rs.end) break;             // uniform
             bool on = false;
             unsigned int d = 0xffffffffu;
             unsigned long long ms = 0;
-            if (i < V) {
+            if (i < rs.end) {
                 const float v = vals[u];
                 const unsigned int bits = __float_as_uint(v);
                 if ((bits & prefix_mask) == prefix_bits) {
@@ -131,89 +170,130 @@ __device__ void radix_pass(const float* __restrict__ p, int V, unsigned int pref
             }
         }
     }
-    __syncthreads();
-    // scan from the largest digit down: thread t owns digits n_bins-1-2t and n_bins-2-2t
-    const int d0 = n_bins - 1 - 2 * (int)threadIdx.x, d1 = d0 - 1;
-    const unsigned int c0 = d0 >= 0 ? sh.count[d0] : 0, c1 = d1 >= 0 ? sh.count[d1] : 0;
-    const unsigned long long m0 = d0 >= 0 ? mass_at(sh, d0) : 0, m1 = d1 >= 0 ? mass_at(sh, d1) : 0;
-    unsigned int cs = c0 + c1;
-    unsigned long long ms = m0 + m1;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    rs.sync();                                              // every CTA's histogram is complete
+    if (NC > 1) {
+        // the histograms are added up a slice of digits a CTA (all CTAs at once), the totals go to the leading CTA
+        const int per_cta = (n_bins + NC - 1) / NC;
+        const int i = rs.rank * per_cta + (int)threadIdx.x;
+        const bool mine = (int)threadIdx.x < per_cta && i < n_bins;
+        unsigned int ct = 0;
+        unsigned long long mt = 0;
+        if (mine) {
+            unsigned int c[NC], lo[NC], hi[NC];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned int c = __shfl_up_sync(0xffffffffu, cs, o);
-        const unsigned long long m = __shfl_up_sync(0xffffffffu, ms, o);
-        if (lane >= o) {
-            cs += c;
-            ms += m;
-        }
-    }
-    if (lane == 31) {
-        sh.warp_count[warp] = cs;
-        sh.warp_mass[warp] = ms;
-    }
-    __syncthreads();
-    unsigned int cbase = carry_count;
-    unsigned long long mbase = carry_mass;
-    for (int w = 0; w < warp; w++) {
-        cbase += sh.warp_count[w];
-        mbase += sh.warp_mass[w];
-    }
-    // exclusive values before this thread's first digit
-    const unsigned int c_before = cbase + cs - (c0 + c1);
-    const unsigned long long m_before = mbase + ms - (m0 + m1);
-    auto met = [&](unsigned int c, unsigned long long m) {
-        return by_mass ? (m >= target_mass) : (c >= target_count);
-    };
-    if (c0 > 0 && !met(c_before, m_before) && met(c_before + c0, m_before + m0)) {
-        sh.found_digit = (unsigned int)d0;
-        sh.found_above = c_before;
-        sh.found_mass = m_before;
-    } else if (c1 > 0 && !met(c_before + c0, m_before + m0) && met(c_before + c0 + c1, m_before + m0 + m1)) {
-        sh.found_digit = (unsigned int)d1;
-        sh.found_above = c_before + c0;
-        sh.found_mass = m_before + m0;
-    }
-    __syncthreads();
-    if (sh.found_above == 0xffffffffu) {
-        // target beyond everything (rounding): end at the smallest populated digit
-        if (threadIdx.x == 0) {
-            int d = 0;
-            while (d < n_bins - 1 && sh.count[d] == 0) d++;
-            unsigned int c = carry_count;
-            unsigned long long m = carry_mass;
-            for (int e = n_bins - 1; e > d; e--) {
-                c += sh.count[e];
-                m += mass_at(sh, e);
+            for (int r = 0; r < NC; r++) {                  // the loads first, all in flight together
+                c[r] = *rs.at(&sh.count[i], r);
+                lo[r] = *rs.at(&sh.mass_lo[i], r);
+                hi[r] = *rs.at(&sh.mass_hi[i], r);
             }
-            sh.found_digit = (unsigned int)d;
-            sh.found_above = c;
-            sh.found_mass = m;
+#pragma unroll
+            for (int r = 0; r < NC; r++) {
+                ct += c[r];
+                mt += ((unsigned long long)hi[r] << 32) | lo[r];
+            }
+        }
+        rs.sync();                                          // every digit of every CTA has been read: they may be overwritten
+        if (mine) {
+            *rs.at(&sh.count[i], 0) = ct;
+            *rs.at(&sh.mass_lo[i], 0) = (unsigned int)mt;
+            *rs.at(&sh.mass_hi[i], 0) = (unsigned int)(mt >> 32);
+        }
+        rs.sync();                                          // the leading CTA's histogram holds the row's totals
+    }
+    if (rs.rank == 0) {
+        // scan from the largest digit down: thread t owns digits n_bins-1-2t and n_bins-2-2t
+        const int d0 = n_bins - 1 - 2 * (int)threadIdx.x, d1 = d0 - 1;
+        const unsigned int c0 = d0 >= 0 ? sh.count[d0] : 0, c1 = d1 >= 0 ? sh.count[d1] : 0;
+        const unsigned long long m0 = d0 >= 0 ? mass_at(sh, d0) : 0, m1 = d1 >= 0 ? mass_at(sh, d1) : 0;
+        unsigned int cs = c0 + c1;
+        unsigned long long ms = m0 + m1;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned int c = __shfl_up_sync(0xffffffffu, cs, o);
+            const unsigned long long m = __shfl_up_sync(0xffffffffu, ms, o);
+            if (lane >= o) {
+                cs += c;
+                ms += m;
+            }
+        }
+        if (lane == 31) {
+            sh.warp_count[warp] = cs;
+            sh.warp_mass[warp] = ms;
         }
         __syncthreads();
+        unsigned int cbase = carry_count;
+        unsigned long long mbase = carry_mass;
+        for (int w = 0; w < warp; w++) {
+            cbase += sh.warp_count[w];
+            mbase += sh.warp_mass[w];
+        }
+        // exclusive values before this thread's first digit
+        const unsigned int c_before = cbase + cs - (c0 + c1);
+        const unsigned long long m_before = mbase + ms - (m0 + m1);
+        auto met = [&](unsigned int c, unsigned long long m) {
+            return by_mass ? (m >= target_mass) : (c >= target_count);
+        };
+        if (c0 > 0 && !met(c_before, m_before) && met(c_before + c0, m_before + m0)) {
+            sh.found_digit[set] = (unsigned int)d0;
+            sh.found_above[set] = c_before;
+            sh.found_mass[set] = m_before;
+            sh.found_count[set] = c0;
+        } else if (c1 > 0 && !met(c_before + c0, m_before + m0) && met(c_before + c0 + c1, m_before + m0 + m1)) {
+            sh.found_digit[set] = (unsigned int)d1;
+            sh.found_above[set] = c_before + c0;
+            sh.found_mass[set] = m_before + m0;
+            sh.found_count[set] = c1;
+        }
+        __syncthreads();
+        if (sh.found_above[set] == 0xffffffffu) {
+            // target beyond everything (rounding): end at the smallest populated digit
+            if (threadIdx.x == 0) {
+                int d = 0;
+                while (d < n_bins - 1 && sh.count[d] == 0) d++;
+                unsigned int c = carry_count;
+                unsigned long long m = carry_mass;
+                for (int e = n_bins - 1; e > d; e--) {
+                    c += sh.count[e];
+                    m += mass_at(sh, e);
+                }
+                sh.found_digit[set] = (unsigned int)d;
+                sh.found_above[set] = c;
+                sh.found_mass[set] = m;
+                sh.found_count[set] = sh.count[d];
+            }
+        }
     }
+    rs.sync();                                              // the result is there (in the leading CTA)
+    Found f;
+    f.digit = *rs.at(&sh.found_digit[set], 0);
+    f.above = *rs.at(&sh.found_above[set], 0);
+    f.count = *rs.at(&sh.found_count[set], 0);
+    f.mass = *rs.at(&sh.found_mass[set], 0);
+    __syncthreads();                                        // all of this CTA's threads have read `turn` and the result
+    if (threadIdx.x == 0) sh.turn++;                        // (the other set is used next; this one stays readable for the
+    return f;                                               //  CTAs that have not read it yet until the pass after next)
 }
 
 // The smallest prefix of the sorted order whose count reaches target_count
 // (by_mass false) or whose mass reaches target_mass (by_mass true).
-__device__ Prefix find_prefix(const float* __restrict__ p, int V, bool by_mass, unsigned int target_count,
+template <int NC>
+__device__ Prefix find_prefix(const float* __restrict__ p, const RowShare<NC>& rs, bool by_mass, unsigned int target_count,
                               unsigned long long target_mass, Shared& sh) {
-    unsigned int bits = 0, mask = 0, above = 0;
+    unsigned int bits = 0, mask = 0, above = 0, n_eq = 0;
     unsigned long long mass = 0;
     if (by_mass && target_mass == 0) target_mass = 1;      // a draw of exactly 0 takes the first element
     if (!by_mass && target_count == 0) target_count = 1;
     const int shifts[3] = {21, 10, 0}, nb[3] = {2048, 2048, 1024};
     for (int r = 0; r < 3; r++) {
-        radix_pass(p, V, bits, mask, shifts[r], nb[r], by_mass, target_count, target_mass, above, mass, sh);
-        bits |= sh.found_digit << shifts[r];
+        const Found f = radix_pass<NC>(p, rs, bits, mask, shifts[r], nb[r], by_mass, target_count, target_mass, above, mass, sh);
+        bits |= f.digit << shifts[r];
         mask |= (unsigned int)(nb[r] - 1) << shifts[r];
-        above = sh.found_above;
-        mass = sh.found_mass;
-        __syncthreads();
+        above = f.above;
+        mass = f.mass;
+        n_eq = f.count;
     }
-    // `bits` is the probability at which the prefix ends; sh.count/mass of its last digit are still valid
-    const unsigned int last = bits & 1023u;
-    const unsigned int n_eq = sh.count[last];
+    // `bits` is the probability at which the prefix ends; n_eq elements have exactly it
     const unsigned long long pm = mass_of(__uint_as_float(bits));
     unsigned int ties;
     if (by_mass) {
@@ -228,15 +308,16 @@ __device__ Prefix find_prefix(const float* __restrict__ p, int V, bool by_mass, 
         if (ties > n_eq) ties = n_eq;
     }
     if (ties < 1) ties = 1;
-    Prefix out{bits, above, ties, mass + (unsigned long long)ties * pm};
-    __syncthreads();
-    return out;
+    return Prefix{bits, above, ties, mass + (unsigned long long)ties * pm};
 }
 
-// Id of the j-th (1-based) element, by ascending id, whose probability bits equal `value`.
-__device__ int nth_equal(const float* __restrict__ p, int V, unsigned int value, unsigned int j, Shared& sh) {
-    const int per = (V + THREADS - 1) / THREADS;
-    const int lo = threadIdx.x * per, hi = min(V, lo + per);
+// Id of the j-th (1-based) element, by ascending id, whose probability bits equal `value` (-1: there is none).
+// The CTAs of a row hold consecutive ranges of ids, so the j-th lies in the first CTA whose running count reaches j.
+template <int NC>
+__device__ int nth_equal(const float* __restrict__ p, const RowShare<NC>& rs, unsigned int value, unsigned int j, Shared& sh) {
+    const int n_mine = rs.end - rs.begin;
+    const int per = (n_mine + THREADS - 1) / THREADS;
+    const int lo = rs.begin + threadIdx.x * per, hi = min(rs.end, lo + per);
     unsigned int c = 0;
     for (int i = lo; i < hi; i++) c += __float_as_uint(p[i]) == value;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -249,7 +330,14 @@ __device__ int nth_equal(const float* __restrict__ p, int V, unsigned int value,
     if (lane == 31) sh.scan_u[warp] = cs;
     if (threadIdx.x == 0) sh.red_i[0] = -1;
     __syncthreads();
-    unsigned int before = cs - c;
+    if (threadIdx.x == 0) {
+        unsigned int tot = 0;
+        for (int w = 0; w < THREADS / 32; w++) tot += sh.scan_u[w];
+        sh.part_u = tot;                                    // equal elements in this CTA's range
+    }
+    rs.sync();
+    unsigned int before = cs - c;                           // equal elements before this thread's range
+    for (int r = 0; r < rs.rank; r++) before += *rs.at(&sh.part_u, r);
     for (int w = 0; w < warp; w++) before += sh.scan_u[w];
     if (c > 0 && before < j && j <= before + c) {
         unsigned int seen = before;
@@ -260,9 +348,13 @@ __device__ int nth_equal(const float* __restrict__ p, int V, unsigned int value,
             }
         }
     }
-    __syncthreads();
-    const int r = sh.red_i[0];
-    __syncthreads();
+    rs.sync();
+    int r = -1;
+    for (int k = 0; k < NC; k++) {                          // at most one CTA has found it
+        const int v = *rs.at(&sh.red_i[0], k);
+        if (v >= 0) r = v;
+    }
+    rs.sync();                                              // red_i and part_u may be written again
     return r;
 }
 
@@ -407,8 +499,10 @@ __device__ int argmax_from_parts(const float* __restrict__ part_val, const int* 
     return bi == 0x7fffffff ? 0 : bi;
 }
 
-// One CTA per row. The row of logits is overwritten with probabilities when
-// the temperature is positive (the reference's sampler also works in place).
+// One CTA a row, or for a large vocabulary the ROW_CTAS CTAs of a cluster (NC), each with a consecutive part of
+// the row. The row of logits is overwritten with probabilities when the temperature is positive (the
+// reference's sampler also works in place).
+template <int NC>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict__ params,
               unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out,
@@ -417,35 +511,37 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     griddep_launch();
     griddep_wait();
     const SampleParams sp{params[0], params[1], params[2], (int)params[3]};
-    const int b = blockIdx.x;
+    const int b = NC == 1 ? blockIdx.x : blockIdx.x / NC;
     float* row = logits + (size_t)b * ld;
     const int slot = slots ? slots[b] : b;
-    if (slot < 0) {                          // padding row
-        if (threadIdx.x == 0) out[b] = 0;
+    const RowShare<NC> rs(V);
+    if (slot < 0) {                          // padding row (all CTAs of the row leave)
+        if (threadIdx.x == 0 && rs.rank == 0) out[b] = 0;
         return;
     }
+    if (threadIdx.x == 0) sh.turn = 0;
     float mx;
     const int best = part_val != nullptr ? argmax_from_parts(part_val, part_idx, b, sh, &mx) : block_argmax(row, V, sh, &mx);
     if (sp.temp <= 0.f) {
-        if (threadIdx.x == 0) out[b] = best;
+        if (threadIdx.x == 0 && rs.rank == 0) out[b] = best;
         return;
     }
     // p_i = expf((l_i - max) / temp) * (float)(1 / sum), the sum in double (sampler.c:132-143)
     double part = 0.0;
-    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
         float vals[LOADS];
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            vals[u] = i < V ? row[i] : 0.f;
+            vals[u] = i < rs.end ? row[i] : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            if (i < V) {
+            if (i < rs.end) {
                 const float e = expf((vals[u] - mx) / sp.temp);
                 row[i] = e;
-                part += (double)e;                          // in index order within a thread, as before
+                part += (double)e;                          // in index order within a thread
             }
         }
     }
@@ -454,26 +550,31 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     if (lane == 0) sh.red_d[warp] = part;
     __syncthreads();
+    if (threadIdx.x == 0) {
+        double mine = 0.0;
+        for (int w = 0; w < THREADS / 32; w++) mine += sh.red_d[w];
+        sh.part_d = mine;
+    }
+    rs.sync();
     double sum = 0.0;
-    for (int w = 0; w < THREADS / 32; w++) sum += sh.red_d[w];
+    for (int r = 0; r < NC; r++) sum += *rs.at(&sh.part_d, r);       // in the CTAs' order: the same value in each of them
     const float inv = (float)(1.0 / sum);
     unsigned int n_floor = 0;
-    __syncthreads();
-    for (int base0 = 0; base0 < V; base0 += THREADS * LOADS) {
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
         float vals[LOADS];
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            vals[u] = i < V ? row[i] : 0.f;
+            vals[u] = i < rs.end ? row[i] : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            if (i < V) row[i] = vals[u] * inv;
+            if (i < rs.end) row[i] = vals[u] * inv;
         }
     }
-    __syncthreads();
-    const float p_best = row[best];
+    rs.sync();                                              // the whole row holds probabilities (and part_d has been read)
+    const float p_best = __ldcg(row + best);                // possibly written by another CTA of the row
 
     // the kept prefix: top-k, then min-p, then top-p (sampler.c:146-175)
     unsigned int n = (unsigned int)V;
@@ -481,39 +582,45 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     if (sp.min_p > 0.f) {
         const float floor_p = sp.min_p * p_best;
         unsigned int c = 0;
-        for (int i = threadIdx.x; i < V; i += THREADS) c += row[i] >= floor_p;
+        for (int i = rs.begin + (int)threadIdx.x; i < rs.end; i += THREADS) c += row[i] >= floor_p;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
         if (lane == 0) sh.scan_u[warp] = c;
         __syncthreads();
-        for (int w = 0; w < THREADS / 32; w++) n_floor += sh.scan_u[w];
-        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int mine = 0;
+            for (int w = 0; w < THREADS / 32; w++) mine += sh.scan_u[w];
+            sh.part_u = mine;
+        }
+        rs.sync();
+        for (int r = 0; r < NC; r++) n_floor += *rs.at(&sh.part_u, r);
+        rs.sync();                                          // part_u may be written again
         if (n_floor < 1) n_floor = 1;
         if (n_floor < n) n = n_floor;
     }
     if (sp.top_p < 1.0f) {
         const unsigned long long target = __double2ull_ru((double)sp.top_p * 1152921504606846976.0);
-        const Prefix pp = find_prefix(row, V, true, 0, target, sh);
+        const Prefix pp = find_prefix<NC>(row, rs, true, 0, target, sh);
         const unsigned int np = pp.above + pp.ties;
         if (np < n) n = np;
     }
     if (n < 1) n = 1;
     // mass of the kept prefix, then the draw r = U * total and the walk (sampler.c:178-186)
-    const Prefix kept = find_prefix(row, V, false, n, 0, sh);
-    unsigned long long state = rng[slot];
+    const Prefix kept = find_prefix<NC>(row, rs, false, n, 0, sh);
+    unsigned long long state = rng[slot];                   // (rewritten by the leading CTA only after the last barrier)
     const double u = splitmix_uniform(&state);
     const double r = u * (double)kept.mass;
     unsigned long long target = __double2ull_ru(r);
     if (target > kept.mass) target = kept.mass;
-    Prefix hit = find_prefix(row, V, true, 0, target, sh);
+    Prefix hit = find_prefix<NC>(row, rs, true, 0, target, sh);
     unsigned int rank = hit.above + hit.ties;              // 1-based place in the sorted order
     unsigned int value = hit.value, j = hit.ties;
     if (rank > n) {                                        // only through rounding: the last kept one
         value = kept.value;
         j = kept.ties;
     }
-    const int id = nth_equal(row, V, value, j, sh);
-    if (threadIdx.x == 0) {
+    const int id = nth_equal<NC>(row, rs, value, j, sh);
+    if (threadIdx.x == 0 && rs.rank == 0) {
         out[b] = id >= 0 ? id : best;
         rng[slot] = state;
     }
@@ -603,7 +710,26 @@ MYNAH_API int mynah_sample(float* logits, int B, int V, int ld, const float* par
         mynah_launch(argmax_partial_kernel, dim3(ARGMAX_PARTS, B), dim3(PART_THREADS), 0, stream, (const float*)logits, V, ld, slots, part_val, part_idx);
         if (mynah_check_launch("argmax_partial")) return -1;
     }
-    mynah_launch(sample_kernel, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out,
+    if (part_val != nullptr && V >= ROW_CTAS * 4096) {
+        // a large vocabulary: a cluster of ROW_CTAS CTAs a row
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)B * ROW_CTAS);
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = ROW_CTAS;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel<ROW_CTAS>, logits, V, ld, params, rng, slots, out,
+                                                 (const float*)part_val, (const int*)part_idx);
+        if (e != cudaSuccess) return mynah_fail("sample: %s", cudaGetErrorString(e));
+        return mynah_check_launch("sample");
+    }
+    mynah_launch(sample_kernel<1>, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out,
                  (const float*)part_val, (const int*)part_idx);
     return mynah_check_launch("sample");
 }

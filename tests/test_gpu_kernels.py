@@ -331,7 +331,7 @@ def _sampler_state(B, seeds):
     return st
 
 
-@pytest.mark.parametrize("V", [777, 32000])
+@pytest.mark.parametrize("V", [777, 32000, 40003])      # one CTA a row; with the two-step maximum; a cluster a row
 @pytest.mark.parametrize("temp,top_k,top_p,min_p", [(0.8, 0, 1.0, 0.0), (0.6, 20, 0.95, 0.0), (1.0, 5, 1.0, 0.0),
                                                     (1.3, 0, 0.7, 0.0), (1.0, 0, 1.0, 0.05), (0.7, 50, 0.9, 0.02),
                                                     (1.0, 1, 1.0, 0.0), (0.0, 20, 0.95, 0.0), (2.0, 0, 0.999, 0.0)])
