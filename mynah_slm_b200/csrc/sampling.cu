@@ -112,8 +112,8 @@ __device__ Found radix_pass(const float* __restrict__ p, const RowShare<NC>& rs,
         sh.mass_lo[i] = 0;
         sh.mass_hi[i] = 0;
     }
-    const unsigned int set = sh.turn & 1u;                  // (read before the barrier below; advanced after the last read)
-    __syncthreads();
+    __syncthreads();                                        // (the previous pass's advance of `turn` is visible from here on)
+    const unsigned int set = sh.turn & 1u;                  // advanced only after this pass's last barrier
     if (threadIdx.x == 0) {
         sh.found_digit[set] = 0;                            // the smallest digit, when the target is never met
         sh.found_above[set] = 0xffffffffu;

@@ -334,7 +334,9 @@ def _sampler_state(B, seeds):
 @pytest.mark.parametrize("V", [777, 32000, 40003])      # one CTA a row; with the two-step maximum; a cluster a row
 @pytest.mark.parametrize("temp,top_k,top_p,min_p", [(0.8, 0, 1.0, 0.0), (0.6, 20, 0.95, 0.0), (1.0, 5, 1.0, 0.0),
                                                     (1.3, 0, 0.7, 0.0), (1.0, 0, 1.0, 0.05), (0.7, 50, 0.9, 0.02),
-                                                    (1.0, 1, 1.0, 0.0), (0.0, 20, 0.95, 0.0), (2.0, 0, 0.999, 0.0)])
+                                                    (1.0, 1, 1.0, 0.0), (0.0, 20, 0.95, 0.0), (2.0, 0, 0.999, 0.0),
+                                                    (1.0, 256, 0.98, 0.0), (0.9, 300, 0.9, 0.0), (1.0, 5, 0.5, 0.3),
+                                                    (1.5, 7, 1.0, 0.0)])
 def test_sample_matches_plain_sampler(V, temp, top_k, top_p, min_p):
     """Same logits, same generator state -> same token, draw after draw."""
     k = _k()
@@ -348,6 +350,7 @@ def test_sample_matches_plain_sampler(V, temp, top_k, top_p, min_p):
     for r in range(rounds):
         lg = (rng.standard_normal((B, V)) * (1.0 + r % 3)).astype(np.float32)
         lg[0, :8] = lg[0, 0]                                                       # equal probabilities: ids break ties
+        lg[1, 100:110] = lg[1].max() + 0.5                                         # ten equal largest: a small top-k ends among them
         want = [p.sample(lg[b].copy()) for b, p in enumerate(plain)]
         got = k.sample(torch.from_numpy(lg.copy()).to(DEV), params, state, slots).cpu().tolist()
         assert got == want, (r, got, want)
