@@ -434,14 +434,15 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     return mynah_check_launch("gemm_tcgen05");
 }
 
-// 1 (default): products of 256 rows or more run on pairs of CTAs (cta_group::2). MYNAH_GEMM_PAIR=0 keeps single CTAs.
-bool pair_enabled() {
+// 1 (default): products of 256 rows or more run on pairs of CTAs (cta_group::2) where that measured faster.
+// MYNAH_GEMM_PAIR=0 keeps single CTAs, 2 takes pairs for every product of 256 rows or more.
+int pair_mode() {
     static int v = -1;
     if (v < 0) {
         const char* e = getenv("MYNAH_GEMM_PAIR");
-        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+        v = e == nullptr ? 1 : (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1));
     }
-    return v == 1;
+    return v;
 }
 
 }  // namespace
@@ -466,7 +467,8 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     // Pairs pay once a unit has tiles to run one after the other (the ring then stays full across tiles); with
     // one tile a unit, as for a 2,048-token prompt of a small model, single CTAs measured the same or better.
     const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * (epilogue == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, 256));
-    const bool pair = pair_enabled() && M >= 2 * BM && sm_count >= 2 && pair_tiles >= 2 * (sm_count / 2);
+    const bool pair = M >= 2 * BM && sm_count >= 2 &&
+                      (pair_mode() == 2 || (pair_mode() == 1 && pair_tiles >= 2 * (sm_count / 2)));
     // wide tiles unless they would leave most SMs idle
     const long long units = pair ? sm_count / 2 : sm_count;
     const bool wide = epilogue == EPI_SWIGLU || (long long)ceil_div(N, 256) * ceil_div(M, pair ? 2 * BM : BM) * 10 >= units * 8 || N > 4096;
@@ -520,7 +522,7 @@ MYNAH_API int mynah_gemm_qkv_rope(const void* A, const void* W, int M, int H, in
     qe.pt = PageTable{page_indptr, page_ids, page_base, n_pages};
     qe.q_out = (bf16*)q_out; qe.ldq = ldq; qe.k_cache = (bf16*)k_cache; qe.v_cache = (bf16*)v_cache;
     const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * ceil_div(N, 256);
-    const bool pair = pair_enabled() && M >= 2 * BM && sm_count >= 2 && pair_tiles >= 2 * (sm_count / 2);
+    const bool pair = pair_mode() >= 1 && M >= 2 * BM && sm_count >= 2 && pair_tiles >= 2 * (sm_count / 2);
     CUtensorMap ma, mb;
     if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
     if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, 128, BK)) return -1;
