@@ -39,7 +39,7 @@ MYNAH_API int mynah_embed_gather(const void* table, int table_dtype, const int* 
 }
 
 // --------------------------------------------------------------- RMSNorm
-// v = x[r] (+ delta[r]);  x[r] = v when delta is given;
+// v = x[r] (+ delta[r]);  x[r] = v when delta is given and every row is taken (no `rows`);
 // out[i] = (v * s) * w   with   s = 1 / sqrt(mean(v^2) + eps)
 // (mynah-slm src/kernels.c:118-128; plain gain, not 1+w). `rows`, when given,
 // selects the rows to normalise (the rows whose logits are wanted); out then
@@ -53,19 +53,26 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ del
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + (size_t)r * D;
     const TA* dr = delta ? delta + (size_t)r * D : nullptr;
+    // the sum is kept in x when every row is normalised once; selected rows may repeat (several CTAs on one
+    // row), so with a selection x is only read
+    const bool keep = dr != nullptr && rows == nullptr;
     float ss = 0.f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float v = xr[i];
         if (dr) {
             v += to_f32(dr[i]);
-            xr[i] = v;
+            if (keep) xr[i] = v;
         }
         ss += v * v;
     }
     ss = block_sum(ss, red);
     const float s = 1.0f / sqrtf(ss / (float)D + eps);
     TA* o = out + (size_t)blockIdx.x * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TA>((xr[i] * s) * w.at(i));
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = xr[i];
+        if (dr && !keep) v += to_f32(dr[i]);
+        o[i] = from_f32<TA>((v * s) * w.at(i));
+    }
 }
 
 // The same norm with the row kept in registers: four consecutive elements per thread, one pass over
@@ -86,7 +93,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict_
         if (delta) {
             const TA* dr = delta + (size_t)r * D + i;
             v.x += to_f32(dr[0]); v.y += to_f32(dr[1]); v.z += to_f32(dr[2]); v.w += to_f32(dr[3]);
-            *reinterpret_cast<float4*>(xr + i) = v;
+            if (rows == nullptr) *reinterpret_cast<float4*>(xr + i) = v;     // (selected rows may repeat: x is only read)
         }
     }
     float ss = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);

@@ -97,7 +97,13 @@ struct GemmShape {
 // tcgen05.mma.cta_group::2 for both, and each reads its 128 rows of the accumulator out of its own tensor
 // memory. A CTA then loads 16 + BN/8 KB a k-block instead of 16 + BN/4, which is what the ring's depth and
 // the L2's bandwidth have to cover.
-template <int BN, int EPI, int CTAS>
+//
+// KS = 2 (single CTAs, bf16 rows, BN = 256, one tile a cluster): the two CTAs of a cluster share a tile by halves
+// of K. A product with few tiles (a narrow N at a few thousand rows) then still fills the SMs with 256-wide
+// tiles, which need fewer operand bytes a flop than the 128-wide ones. When both have accumulated, each sends
+// the 128 accumulator columns that the other will finish to the other's idle operand ring (fp32, through
+// distributed shared memory), adds what it received to its own 128 columns and stores them.
+template <int BN, int EPI, int CTAS, int KS = 1>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status, const QkvEpilogue qe) {
@@ -124,8 +130,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         gain_s[0][threadIdx.x] = qe.q_gain.p != nullptr ? qe.q_gain.at(threadIdx.x) : 1.0f;
         gain_s[EPI == EPI_QKV ? 1 : 0][threadIdx.x] = qe.k_gain.p != nullptr ? qe.k_gain.at(threadIdx.x) : 1.0f;
     }
+    static_assert(KS == 1 || (KS == 2 && CTAS == 1 && EPI == EPI_BF16 && BN == 256), "K is split for single CTAs with bf16 rows only");
     const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;         // 0 leads
-    const int unit = blockIdx.x / CTAS, n_units = gridDim.x / CTAS;  // a unit walks over tiles: a CTA or a pair
+    const int krank = KS == 2 ? (int)cluster_ctarank() : 0;          // which half of K
+    const int unit = blockIdx.x / (CTAS * KS), n_units = gridDim.x / (CTAS * KS);   // a unit walks over tiles: a CTA, a pair, or two halves of K
+    const int kb_begin = krank == 0 ? 0 : (nk + 1) / 2, kb_end = KS == 2 && krank == 0 ? (nk + 1) / 2 : nk;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -161,7 +170,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
                 const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
-                for (int kb = 0; kb < nk; kb++, it++) {
+                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1) || *abort_flag) {
@@ -212,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < nk; kb++, it++) {
+                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(full0 + 8 * s, ph) || *abort_flag) {
@@ -226,13 +235,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
                         if (CTAS == 2) tc_mma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
-                        else tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
+                        else tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, ((kb - kb_begin) | k) != 0);
                     }
                     // the stage is free (in both CTAs) once these have read it
                     if (CTAS == 2) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
                 }
                 // arrives when the tile is accumulated
                 if (CTAS == 2) tc_commit_pair(acc_full0 + 8 * buf); else tc_commit(acc_full0 + 8 * buf);
+            }
+        }
+    } else if (KS == 2) {                                            // ---- epilogue warps, K split: the tile is accumulated (this half)
+        if (unit < total_tiles && (!mbar_wait(acc_full0, 0) || *abort_flag)) {
+            if (lane == 0) {
+                *abort_flag = 1;
+                atomicOr(status, MYNAH_ST_TIMEOUT);
             }
         }
     } else {                                                         // ---- epilogue: warps 2..5 -> lane quadrants 2,3,0,1
@@ -387,6 +403,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         if (lane == 0) tma_store_wait_all();
     }
+    if (KS == 2) {
+        // Both CTAs are past their last product (or gave up): their operand rings are idle and may be written.
+        tc_fence_before();
+        __syncthreads();
+        cluster_sync_all();
+        tc_fence_after();
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                            // of the tile; epilogue warps only
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const bool work = warp >= 2 && unit < total_tiles;
+        if (work) {
+            // the other CTA's 128 columns of this CTA's accumulator, as fp32 rows of 512 bytes, 16-byte pieces
+            // swizzled by the row so that neither these stores nor the loads below meet in a bank
+            const uint32_t there = cluster_map(smem_u32(smem), (uint32_t)(krank ^ 1)) + (uint32_t)row * 512u;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t r[32];
+                tc_ld32(t_row + (krank ^ 1) * 128 + c * 32, r);
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    st_cluster_v4(there + (uint32_t)(((c * 8 + j) ^ (lane & 7)) * 16), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+        }
+        cluster_sync_all();                                          // what the other CTA sent has arrived
+        if (work) {
+            const int m_tile = unit % g.m_tiles, n_tile = unit / g.m_tiles;
+            const int row0 = m_tile * BM + quad * 32;
+            unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
+            const unsigned char* got = smem + (size_t)row * 512;
+#pragma unroll 1
+            for (int c0 = 0, n_store = 0; c0 < 128; c0 += 64, n_store++) {
+                unsigned char* st = my_stage + (n_store & 1) * STAGING_BYTES;
+                unsigned char* my_row = st + lane * 128;
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t r[32];
+                    tc_ld32(t_row + krank * 128 + c0 + half * 32, r);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int piece = (c0 + half * 32 + 8 * j) / 4;
+                        const float4 pa = *reinterpret_cast<const float4*>(got + ((piece ^ (lane & 7)) * 16));
+                        const float4 pb = *reinterpret_cast<const float4*>(got + (((piece + 1) ^ (lane & 7)) * 16));
+                        const uint4 v = make_uint4(pack2(__uint_as_float(r[8 * j]) + pa.x, __uint_as_float(r[8 * j + 1]) + pa.y),
+                                                   pack2(__uint_as_float(r[8 * j + 2]) + pa.z, __uint_as_float(r[8 * j + 3]) + pa.w),
+                                                   pack2(__uint_as_float(r[8 * j + 4]) + pb.x, __uint_as_float(r[8 * j + 5]) + pb.y),
+                                                   pack2(__uint_as_float(r[8 * j + 6]) + pb.z, __uint_as_float(r[8 * j + 7]) + pb.w));
+                        *reinterpret_cast<uint4*>(my_row + (((half * 4 + j) ^ (lane & 7)) * 16)) = v;
+                    }
+                }
+                fence_async_smem();                                  // the staged rows become visible to the TMA engine
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_c, smem_u32(st), n_tile * BN + krank * 128 + c0, row0);
+                    tma_store_commit();
+                }
+            }
+            if (lane == 0) tma_store_wait_all();
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (CTAS == 2) cluster_sync_all();                               // neither CTA leaves while the other may still touch it
@@ -397,12 +472,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int BN, int EPI, int CTAS>
+template <int BN, int EPI, int CTAS, int KS = 1>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
                 int sm_count, int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{}) {
     constexpr int STAGES = ring_stages(BN, CTAS);
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2 / CTAS) + 4 * 2 * STAGING_BYTES + 256 + 1024;
-    auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS>;
+    auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS, KS>;
     static bool opted = false;
     if (!opted) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -415,20 +490,21 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     g.n_tiles = EPI == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, BN);
     const long long tiles = (long long)g.m_tiles * g.n_tiles;
     MYNAH_REQUIRE(tiles < (1ll << 30), "gemm_tcgen05: too many tiles");
-    const int max_units = sm_count / CTAS;
+    const int max_units = sm_count / (CTAS * KS);
     const int units = (int)(tiles < max_units ? tiles : max_units);
+    MYNAH_REQUIRE(KS == 1 || tiles <= max_units, "gemm_tcgen05: K is split only when every tile has a cluster of its own");
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(units * CTAS);
+    cfg.gridDim = dim3(units * CTAS * KS);
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.x = CTAS * KS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = CTAS == 2 ? 1 : 0;
+    cfg.numAttrs = CTAS * KS == 2 ? 1 : 0;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, g, status, qe);
     if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
     return mynah_check_launch("gemm_tcgen05");
@@ -451,6 +527,15 @@ MYNAH_API int mynah_gemm_tcgen05_supported(int M, int N, int K) {
     return M >= 1 && N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0;      // rows of 16-byte multiples for TMA
 }
 
+// Whether the bf16-rows product of this shape is run as two halves of K (its sums then differ in rounding from
+// the product run whole). MYNAH_GEMM_KSPLIT=0 keeps whole tiles.
+MYNAH_API int mynah_gemm_tcgen05_splits_k(int M, int N, int K, int sm_count) {
+    static const bool on = [] { const char* e = getenv("MYNAH_GEMM_KSPLIT"); return !(e != nullptr && e[0] == '0'); }();
+    if (sm_count <= 0) sm_count = 148;
+    // (the exchange costs about 4 us; a k-block about 0.34 us on a 128-wide tile, 0.39 us on half of a 256-wide one)
+    return on && ceil_div(K, BK) >= 32 && (long long)ceil_div(M, BM) * ceil_div(N, 256) <= sm_count / 2;
+}
+
 // epilogue 0: C bf16 [M, N]; 1: C fp32 [M, N]; 2: SwiGLU, W holds N gate rows then N up rows, C bf16 [M, N].
 // A [M, K] and W [rows, K] are bf16, row-major, 16-byte aligned; ldc is C's row pitch in elements. `status`
 // receives MYNAH_ST_TIMEOUT if a wait inside the kernel ran out.
@@ -469,6 +554,14 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * (epilogue == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, 256));
     const bool pair = M >= 2 * BM && sm_count >= 2 &&
                       (pair_mode() == 2 || (pair_mode() == 1 && pair_tiles >= 2 * (sm_count / 2)));
+    // Few tiles even at 256 columns (a narrow N): two CTAs a tile, a half of K each.
+    if (epilogue == EPI_BF16 && !pair && mynah_gemm_tcgen05_splits_k(M, N, K, sm_count)) {
+        CUtensorMap ma, mb, mc;
+        if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
+        if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, 128, BK)) return -1;
+        if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
+        return launch_gemm<256, EPI_BF16, 1, 2>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
+    }
     // wide tiles unless they would leave most SMs idle
     const long long units = pair ? sm_count / 2 : sm_count;
     const bool wide = epilogue == EPI_SWIGLU || (long long)ceil_div(N, 256) * ceil_div(M, pair ? 2 * BM : BM) * 10 >= units * 8 || N > 4096;

@@ -53,6 +53,11 @@ def tcgen05_supported(M: int, N: int, K: int) -> bool:
     return bool(lib.load().mynah_gemm_tcgen05_supported(M, N, K))
 
 
+def splits_k(M: int, N: int, K: int, device) -> bool:
+    """Whether the bf16-rows product of this shape runs as two halves of K on two CTAs a tile."""
+    return bool(lib.load().mynah_gemm_tcgen05_splits_k(M, N, K, _sm_count(device)))
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """epilogue 0: bf16 rows, 1: fp32 rows, 2: SwiGLU (w = N gate rows then N up rows)."""
     M, K = x.shape

@@ -57,7 +57,8 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, act_dtype: torch.dtype,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """h = RMSNorm(x (+ delta)) * gain; x is updated in place when delta is given."""
+    """h = RMSNorm(x (+ delta)) * gain. Without `rows`, x is updated in place when delta is given; with `rows`
+    (which may name a row more than once) x is only read."""
     _chk(x, "residual", torch.float32, 2)
     _chk(gain, "norm gain", dim=1)
     T, D = x.shape

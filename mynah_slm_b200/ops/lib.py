@@ -112,6 +112,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_attn_prefill_tcgen05_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_gemm_tcgen05_supported.restype = c_int
     lib.mynah_gemm_tcgen05_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_gemm_tcgen05_splits_k.restype = c_int
+    lib.mynah_gemm_tcgen05_splits_k.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int
     lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():
