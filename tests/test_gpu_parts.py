@@ -2,7 +2,9 @@
 generality: a toy architecture defined HERE (a mixer with fixed-size state of
 its own, a layer that runs twice, a run that reads another run's cache) is
 registered, written as a random folder, built and stepped without a change to
-the library's files."""
+the library's files; and a second one with a feed-forward that routes tokens to
+experts (beside a dense one in another layer) and a rotary encoding in another
+pairing that the attention applies through the unfused interface."""
 import json
 import os
 
@@ -355,3 +357,181 @@ def test_toy_architecture_with_state_registers_builds_and_steps(tmp_path):
     slot = eng.open_sequence()
     assert slot in slots
     assert_close(refs[1], eng.step([StepEntry(slot, seqs[1], range(len(seqs[1])))]).cpu().numpy(), FP32_REL, "toy reused slot")
+
+
+# ------------------------------------- a toy model with routing and another position encoding
+
+ROUTED_ARCH = "ToyRoutedForCausalLM"
+
+
+def _register_routed():
+    """A feed-forward that routes each token to one of several experts, and a rotary encoding in the
+    interleaved pairing that the attention's own kernel does not apply: both live in this test file."""
+    from dataclasses import dataclass
+
+    from mynah_slm_b200.config.keys import req_float, req_int
+    from mynah_slm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from mynah_slm_b200.parts import FeedForward, PositionEncoding, TensorSpec, register_ffn, register_position
+    from mynah_slm_b200.registry import known_architectures, register_architecture
+
+    class TopOneExperts(FeedForward):
+        """e = argmax of the router's logits (fp32); out = softmax(logits)[e] * W2_e relu(W1_e h)."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.D, self.F, self.E, self.prefix = spec["hidden_size"], spec["ffn_size"], spec["experts"], spec["prefix"]
+
+        def tensor_specs(self):
+            specs = [TensorSpec(self.prefix + "router.weight", (self.E, self.D), std=0.5)]
+            for e in range(self.E):
+                specs += [TensorSpec(f"{self.prefix}experts.{e}.w1.weight", (self.F, self.D), std=0.2),
+                          TensorSpec(f"{self.prefix}experts.{e}.w2.weight", (self.D, self.F), std=0.2)]
+            return specs
+
+        def bind(self, tensors, runtime):
+            self.router = tensors[self.prefix + "router.weight"]
+            self.w1 = torch.stack([tensors[f"{self.prefix}experts.{e}.w1.weight"] for e in range(self.E)])
+            self.w2 = torch.stack([tensors[f"{self.prefix}experts.{e}.w2.weight"] for e in range(self.E)])
+
+        def forward(self, h, ctx):
+            x = h.float()
+            logits = x @ self.router.float().t()
+            e = logits.argmax(dim=-1)
+            gate = torch.softmax(logits, dim=-1).gather(1, e[:, None])
+            mid = torch.relu(torch.einsum("td,tfd->tf", x, self.w1.float()[e]))
+            return (gate * torch.einsum("tf,tdf->td", mid, self.w2.float()[e])).to(h.dtype)
+
+    class InterleavedRope(PositionEncoding):
+        """Rotates the pairs (2i, 2i+1) of every head by pos * theta^(-2i/dim), in place."""
+        fusable = False
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.theta, self.dim = float(spec["theta"]), int(spec["dim"])
+
+        def apply(self, q, k, ctx):
+            inv = self.theta ** (-torch.arange(0, self.dim, 2, device=q.device, dtype=torch.float64) / self.dim)
+            ang = ctx.tok_pos.to(torch.float64)[:, None] * inv[None, :]
+            c, s = torch.cos(ang).float()[:, None, :], torch.sin(ang).float()[:, None, :]
+            for x in (q, k):
+                if x is None:
+                    continue
+                a, b = x[..., 0::2].float().clone(), x[..., 1::2].float().clone()     # (float() of fp32 is a view)
+                x[..., 0::2] = (a * c - b * s).to(x.dtype)
+                x[..., 1::2] = (b * c + a * s).to(x.dtype)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        raw: tuple
+
+        @classmethod
+        def from_dict(cls, d, generation=None):
+            for k in ("hidden_size", "vocab_size", "num_heads", "num_kv_heads", "head_dim", "ffn_size", "experts",
+                      "layers", "max_positions"):
+                req_int(d, k)
+            req_float(d, "eps"), req_float(d, "theta")
+            return cls(tuple(sorted((k, json.dumps(v)) for k, v in d.items())))
+
+        def to_dict(self):
+            return {k: json.loads(v) for k, v in self.raw}
+
+        def model_spec(self):
+            d = self.to_dict()
+            D = d["hidden_size"]
+            layers = []
+            for i in range(d["layers"]):
+                p = f"layers.{i}."
+                norms = {k: PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": f"{p}{k}_norm.weight"}) for k in ("mixer", "ffn")}
+                mixer = PartSpec("gqa_attention", {"hidden_size": D, "num_heads": d["num_heads"], "num_kv_heads": d["num_kv_heads"],
+                                                   "head_dim": d["head_dim"], "qk_norm": None, "window": None, "prefix": p + "attn.",
+                                                   "position": PartSpec("toy_interleaved_rope", {"theta": d["theta"], "dim": d["head_dim"]})})
+                # the first layer's feed-forward is dense, the others route: chosen layer by layer
+                ffn = (PartSpec("swiglu_dense", {"hidden_size": D, "intermediate_size": d["ffn_size"], "prefix": p + "mlp."}) if i == 0 else
+                       PartSpec("toy_top1_experts", {"hidden_size": D, "ffn_size": d["ffn_size"], "experts": d["experts"], "prefix": p + "moe."}))
+                layers.append(LayerSpec(PartSpec("prenorm_residual", {}), mixer, ffn, norms, p))
+            sched = tuple(ScheduleEntry(i, None) for i in range(d["layers"]))
+            return ModelSpec(ROUTED_ARCH, d["vocab_size"], D, d["max_positions"], tuple(layers), sched,
+                             PartSpec("token_embedding", {"name": "embed.weight", "vocab_size": d["vocab_size"], "dim": D}),
+                             PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": "final_norm.weight"}),
+                             PartSpec("linear_head", {"tied": False, "name": "head.weight", "vocab_size": d["vocab_size"], "dim": D}))
+
+    register_ffn("toy_top1_experts", TopOneExperts, replace=True)
+    register_position("toy_interleaved_rope", InterleavedRope, replace=True)
+    if ROUTED_ARCH not in known_architectures():
+        register_architecture(ROUTED_ARCH, RoutedConfig.from_dict)
+
+
+ROUTED = dict(architectures=[ROUTED_ARCH], hidden_size=48, vocab_size=211, num_heads=6, num_kv_heads=2, head_dim=16,
+              ffn_size=40, experts=5, layers=3, max_positions=256, eps=1e-5, theta=300.0)
+
+
+def _routed_plain(cfg, t, tokens):
+    D, H, KV, HD, E = cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["experts"]
+    n = len(tokens)
+    x = t["embed.weight"][np.asarray(tokens)]
+    inv = cfg["theta"] ** (-np.arange(0, HD, 2, dtype=np.float64) / HD)
+    ang = np.arange(n, dtype=np.float64)[:, None] * inv[None, :]
+    c, s = np.cos(ang).astype(np.float32)[:, None, :], np.sin(ang).astype(np.float32)[:, None, :]
+
+    def rot(v):
+        a, b = v[..., 0::2], v[..., 1::2]
+        out = np.empty_like(v)
+        out[..., 0::2], out[..., 1::2] = a * c - b * s, b * c + a * s
+        return out
+    chosen = []
+    for l in range(cfg["layers"]):
+        p = f"layers.{l}."
+        h = rms_norm(x, t[p + "mixer_norm.weight"], cfg["eps"])
+        q = rot(linear(h, t[p + "attn.q_proj.weight"]).reshape(n, H, HD))
+        k = rot(linear(h, t[p + "attn.k_proj.weight"]).reshape(n, KV, HD))
+        v = linear(h, t[p + "attn.v_proj.weight"]).reshape(n, KV, HD)
+        x = x + linear(gqa_attention(q, k, v).reshape(n, H * HD), t[p + "attn.o_proj.weight"])
+        h = rms_norm(x, t[p + "ffn_norm.weight"], cfg["eps"])
+        if l == 0:
+            x = x + linear(swiglu(linear(h, t[p + "mlp.gate_proj.weight"]), linear(h, t[p + "mlp.up_proj.weight"])),
+                           t[p + "mlp.down_proj.weight"])
+            continue
+        logits = linear(h, t[p + "moe.router.weight"]).astype(np.float32)
+        e = logits.argmax(axis=-1)
+        chosen.append(e)
+        z = np.exp(logits - logits.max(axis=-1, keepdims=True))
+        gate = (z / z.sum(axis=-1, keepdims=True))[np.arange(n), e]
+        rows = [linear(np.maximum(linear(h[i:i + 1], t[f"{p}moe.experts.{e[i]}.w1.weight"]), 0.0),
+                       t[f"{p}moe.experts.{e[i]}.w2.weight"])[0] * gate[i] for i in range(n)]
+        x = x + np.stack(rows)
+    return linear(rms_norm(x, t["final_norm.weight"], cfg["eps"]), t["head.weight"]), chosen
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """A feed-forward with routing and a position encoding of the test's own are registered, written as a random
+    folder, built and stepped (whole, in a batch of unequal lengths, token by token) without a change to the
+    library's files; the layers of one model have different feed-forwards."""
+    _register_routed()
+    from mynah_slm_b200.engine.engine import Engine, StepEntry
+    from mynah_slm_b200.registry import parse_config
+    from mynah_slm_b200.weights.random_init import write_random_model
+    folder = write_random_model(str(tmp_path / "routed"), parse_config(ROUTED), seed=5, dtype=torch.float32)
+    cfg, tensors = read_folder(folder)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 6)
+    rng = np.random.default_rng(6)
+    seqs = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in (75, 12, 40)]
+    refs, chosen = zip(*[_routed_plain(cfg, tensors, s) for s in seqs])
+    assert len(set(np.concatenate([np.concatenate(c) for c in chosen]).tolist())) >= 3      # the routing does route
+    for s, r in zip(seqs, refs):
+        slot = eng.open_sequence()
+        assert_close(r, eng.step([StepEntry(slot, s, range(len(s)))]).cpu().numpy(), FP32_REL, "routed whole")
+        eng.close_sequence(slot)
+    slots = [eng.open_sequence() for _ in seqs]
+    heads = [len(s) - 4 for s in seqs]
+    out = eng.step([StepEntry(sl, s[:h], range(h)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+    got = [[] for _ in seqs]
+    row = 0
+    for i, h in enumerate(heads):
+        got[i].append(out[row:row + h]); row += h
+    for t in range(4):
+        out = eng.step([StepEntry(sl, [s[h + t]], (0,)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+        for i in range(len(seqs)):
+            got[i].append(out[i:i + 1])
+    eng.check_status()
+    for i, r in enumerate(refs):
+        assert_close(r, np.concatenate(got[i]), FP32_REL, f"routed request {i} in a batch, last 4 one by one")
