@@ -275,26 +275,52 @@ __device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t 
 // One CTA a page; six CTAs an SM cover one another's waits. (Persistent CTAs that prefetch their next page were
 // built and measured slower: 5.7 against 3.9 ms a step at batch 64; three CTAs an SM, and each turn of the loop
 // pays the chain of dependent reads that finds its next page.)
-template <int HD>
+template <int HD> __device__ __forceinline__ void merge_pages(const float* __restrict__, const float* __restrict__, bf16* __restrict__,
+                                                              size_t, int, int, int, float*, float*, float*);
+
+// MERGE: the CTA that finishes a (sequence, kv head) last also merges its pages (a count per pair, zero before the
+// first launch and left zero by every launch), which saves the merge's launch; without it the merge is a launch
+// of its own with a CTA per head.
+template <int HD, bool MERGE>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                       const int* __restrict__ kv_len, PageTable pt, TcArgs a,
-                      float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
-    __shared__ __align__(128) unsigned char k_s[KEYS * HD * 2];
-    __shared__ __align__(128) unsigned char v_s[KEYS * HD * 2];
+                      float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status,
+                      unsigned* __restrict__ counters, bf16* __restrict__ out, int ldo) {
+    __shared__ __align__(128) unsigned char k_s[KEYS * HD * 2];     // reused by the merge for the pages' weights
+    __shared__ __align__(128) unsigned char v_s[KEYS * HD * 2];     // reused by the merge for its series
     __shared__ __align__(16) bf16 p_s[MAX_G * KEYS];  // probabilities [head][key], rows of 8 chunks, swizzled
     __shared__ float red_m[WARPS][MAX_G], red_l[WARPS][MAX_G];
+    __shared__ int last_flag;
     griddep_launch();
     griddep_wait();
     const PageJob job = page_job<HD>(blockIdx.x, blockIdx.y, blockIdx.z, kv_len, pt, a, status, threadIdx.x == 0);
     if (job.empty) {
         write_empty_partial(job, a, part_ml);
-        return;
+        if (!MERGE) return;
+    } else {
+        issue_page_copies<HD>(job, k_cache, v_cache, a, smem_u32(k_s), smem_u32(v_s));
+        uint32_t qa[HD / 16][4];
+        load_q_fragments<HD>(job, q, a, qa);
+        compute_page<HD, 1, 0>(job, qa, a, smem_u32(k_s), smem_u32(v_s), p_s, red_m, red_l, part_o, part_ml);
     }
-    issue_page_copies<HD>(job, k_cache, v_cache, a, smem_u32(k_s), smem_u32(v_s));
-    uint32_t qa[HD / 16][4];
-    load_q_fragments<HD>(job, q, a, qa);
-    compute_page<HD, 1, 0>(job, qa, a, smem_u32(k_s), smem_u32(v_s), p_s, red_m, red_l, part_o, part_ml);
+    if (MERGE) {
+        const int b = job.b, g = job.g, G = a.H / a.KV;
+        __syncthreads();                              // the CTA's partial is written ...
+        if (threadIdx.x == 0) {
+            unsigned old;                             // ... and released with the count (the fence is cumulative)
+            asm volatile("atom.add.acq_rel.gpu.u32 %0, [%1], 1;\n" : "=r"(old) : "l"(counters + (size_t)b * a.KV + g) : "memory");
+            last_flag = old == gridDim.x - 1;
+            if (last_flag) counters[(size_t)b * a.KV + g] = 0;
+        }
+        __syncthreads();
+        if (!last_flag) return;
+        const int hi = kv_len[b];
+        const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+        const int n_vis = hi > 0 ? min(a.S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
+        merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)g * G * HD, ((size_t)b * a.H + (size_t)g * G) * a.S,
+                        G, a.S, n_vis, reinterpret_cast<float*>(k_s), reinterpret_cast<float*>(v_s), red_m[0]);
+    }
 }
 
 // Merge of the pages of one (sequence, kv head) by a CTA of WARPS warps: the G heads of the group, n_vis pages.
@@ -656,12 +682,14 @@ MYNAH_API int mynah_attn_decode_tc_supported(int H, int KV, int HD) {
     return (HD == 64 || HD == 128) && KV > 0 && H % KV == 0 && H / KV <= MAX_G;
 }
 
-// Same arguments and scratch layout as mynah_attn_decode; bfloat16 only.
+// Same arguments and scratch layout as mynah_attn_decode; bfloat16 only. `counters`: B * KV words that are zero
+// before the first call (every call leaves them zero), or null: with them the pages' kernel also merges, by the
+// CTA that finishes a (sequence, kv head) last; without them the merge is a second launch. The result is the same.
 MYNAH_API int mynah_attn_decode_tc(
     const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
-    int window, int n_splits, float* scratch, int* status, cudaStream_t stream) {
+    int window, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(mynah_attn_decode_tc_supported(H, KV, HD), "attn_decode_tc: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0, "attn_decode_tc: query row stride %d must be a multiple of 8", ldq);
@@ -672,12 +700,23 @@ MYNAH_API int mynah_attn_decode_tc(
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * n_splits * HD;
     const dim3 grid(n_splits, KV, B);
+    if (counters != nullptr) {
+        MYNAH_REQUIRE((size_t)(H / KV) * n_splits * sizeof(float) <= MERGE_MAX_BYTES,
+                      "attn_decode_tc: %d pages a sequence exceed what the merge holds", n_splits);
+        if (HD == 128)
+            mynah_launch(attn_decode_tc_kernel<128, true>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                         kv_len, pt, a, part_o, part_ml, status, counters, (bf16*)out, ldo);
+        else
+            mynah_launch(attn_decode_tc_kernel<64, true>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                         kv_len, pt, a, part_o, part_ml, status, counters, (bf16*)out, ldo);
+        return mynah_check_launch("attn_decode_tc (merging)");
+    }
     if (HD == 128)
-        mynah_launch(attn_decode_tc_kernel<128>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                                                    kv_len, pt, a, part_o, part_ml, status);
+        mynah_launch(attn_decode_tc_kernel<128, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                     kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
     else
-        mynah_launch(attn_decode_tc_kernel<64>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                                                   kv_len, pt, a, part_o, part_ml, status);
+        mynah_launch(attn_decode_tc_kernel<64, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                     kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
     if (mynah_check_launch("attn_decode_tc")) return -1;
     const size_t dyn = (size_t)n_splits * sizeof(float);
     MYNAH_REQUIRE(dyn <= MERGE_MAX_BYTES, "attn_decode_tc: %d pages a sequence exceed what the merge holds", n_splits);

@@ -52,14 +52,21 @@ def decode_fused_ok(dtype: torch.dtype, H: int, KV: int, HD: int, rotary_dim: in
     return _tc_fits(H, KV, n_splits) and (cos is None or rotary_dim == HD)
 
 
+# Whether the pages' kernel of the tensor-core decode attention also merges (the CTA that finishes a sequence's
+# kv head last), instead of a merge launch of its own with a CTA per head. The bits are the same; the launch of its
+# own measured faster (batch 8: 1.37 against 1.48 ms a step; batch 64: 3.92 against 4.60), so this is off.
+MERGE_IN_PAGES_KERNEL = os.environ.get("MYNAH_ATTN_MERGE_IN_PAGES", "0") == "1"
+
+
 def decode(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, k_cache: torch.Tensor,
-           v_cache: torch.Tensor, pages, window: int, scratch: torch.Tensor) -> None:
+           v_cache: torch.Tensor, pages, window: int, scratch: torch.Tensor, counters=None) -> None:
     """One query per sequence. Both kernels split a sequence page by page and
     combine in page order, so either gives a sequence the same bits whatever
     the batch."""
     if kernels.attn_decode_tc_supported(qkv.dtype, H, KV, HD) and _tc_fits(H, KV, ctx.decode_splits):
         kernels.attn_decode_tc(qkv, out, ctx.B, H, KV, HD, k_cache, v_cache, ctx.kv_len, pages, window,
-                               ctx.decode_splits, scratch, ctx.status)
+                               ctx.decode_splits, scratch, ctx.status,
+                               counters if MERGE_IN_PAGES_KERNEL else None)
     else:
         kernels.attn_decode(qkv, out, ctx.B, H, KV, HD, k_cache, v_cache, ctx.kv_len, pages, window,
                             ctx.decode_splits, scratch, ctx.status)

@@ -344,9 +344,16 @@ def attn_decode_tc_supported(dtype: torch.dtype, H: int, KV: int, HD: int) -> bo
 
 def attn_decode_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,
                    k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor, pages: PageTableView,
-                   window: int, n_splits: int, scratch: torch.Tensor, status: torch.Tensor) -> None:
-    """The tensor-core decode attention (bfloat16, head_dim 64 or 128); same contract as attn_decode."""
+                   window: int, n_splits: int, scratch: torch.Tensor, status: torch.Tensor,
+                   counters: Optional[torch.Tensor] = None) -> None:
+    """The tensor-core decode attention (bfloat16, head_dim 64 or 128); same contract as attn_decode. With
+    `counters` (B * KV zeroed int32 words, left zero) the pages' kernel also merges and no second launch is made;
+    the result is the same."""
     _chk(qkv, "q", torch.bfloat16, 2)
+    if counters is not None:
+        _chk(counters, "counters", torch.int32, 1)
+        if counters.numel() < B * KV:
+            raise KernelError(f"attn_decode_tc: {counters.numel()} counters, {B * KV} are needed")
     _chk(out, "attention output", torch.bfloat16, 2)
     _chk(scratch, "scratch", torch.float32)
     need = B * H * n_splits * (HD + 2)
@@ -355,7 +362,7 @@ def attn_decode_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int
     call("mynah_attn_decode_tc", ptr(qkv), ptr(out), B, H, KV, HD, qkv.shape[1], out.shape[1],
          ptr(k_cache), ptr(v_cache), ptr(kv_len),
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
-         window or 0, n_splits, ptr(scratch), ptr(status), stream_ptr())
+         window or 0, n_splits, ptr(scratch), ptr(counters), ptr(status), stream_ptr())
 
 
 def attn_decode_fused(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,

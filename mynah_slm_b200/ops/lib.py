@@ -53,7 +53,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_attn_decode_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                              P, P, P,
                              P, P, P, c_int,
-                             c_int, c_int, P, P, P],
+                             c_int, c_int, P, P, P, P],
     "mynah_gemm_qkv_rope": [P, P, c_int, c_int, c_int, c_int, c_int,
                             P, P, c_int, c_float,
                             P, P, c_int,

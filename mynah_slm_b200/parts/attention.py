@@ -133,7 +133,8 @@ class GQAttention(Mixer):
             cache.k if writes else None, cache.v if writes else None, ctx.status)
         if ctx.is_decode:
             attention_dispatch.decode(qkv, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0,
-                                      self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits))
+                                      self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits),
+                                      self.runtime.attn_counters(ctx.B * KV))
         else:
             attention_dispatch.prefill(qkv, out, ctx, H, KV, HD, cache.k, cache.v, pages, self.window or 0)
         return kernels.linear(out, self.w_o)

@@ -460,6 +460,13 @@ def test_attn_decode_tensor_cores(H, KV, HD, window):
         assert status.item() == 0
         outs.append(out)
     assert torch.equal(outs[0], outs[1])                       # the size of the launch does not change a bit
+    # the pages' kernel merging by itself (the last CTA of a sequence's kv head): the same bits, counts left zero
+    counters = torch.zeros(B * KV, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        out_m = torch.full((B, H * HD), 7.0, dtype=torch.bfloat16, device=DEV)
+        scratch = torch.full((k.attn_decode_scratch_floats(B, H, HD, 9),), float("nan"), dtype=torch.float32, device=DEV)
+        k.attn_decode_tc(qd, out_m, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, 9, scratch, status, counters)
+        assert status.item() == 0 and torch.equal(out_m, outs[0]) and int(counters.abs().sum().item()) == 0
     got = outs[0].float().cpu().numpy()
     assert np.isfinite(got).all()
     for b, n in enumerate(lens):
