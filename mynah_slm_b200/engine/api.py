@@ -12,6 +12,7 @@ template) is not part of this library.
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Callable, Optional, Sequence
 
@@ -31,6 +32,10 @@ class EngineBackend:
         self.params = params
         self.max_positions = engine.spec.max_positions
         engine.sampler.set_params(params)
+        self._host_rows: list[torch.Tensor] = []
+        self._turn = 0
+        # steps fed from the device are replayed graphs; MYNAH_RUN_AHEAD=0 keeps the step-by-step loop
+        self.runs_ahead = bool(engine.use_graphs and engine.graph_safe) and os.environ.get("MYNAH_RUN_AHEAD", "1") != "0"
 
     def free_tokens(self) -> int:
         return self.engine.free_tokens()
@@ -54,6 +59,32 @@ class EngineBackend:
     def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> list[int]:
         out = self.engine.decode_sampled(slots, tokens)
         return out[:len(slots)].cpu().tolist()
+
+    # A step that is not waited for: its tokens are copied to pinned host memory behind it on the stream, and an
+    # event marks the copy's end, so that the next step can be launched (fed from this one's result on the device)
+    # before the host reads them.
+    def decode_launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None, feed=None) -> "_InFlight":
+        n = len(slots)
+        out = self.engine.decode_sampled(slots, tokens, None if feed is None else (feed[0].device_tokens, feed[1]))
+        if not self._host_rows or self._host_rows[0].numel() < n:
+            self._host_rows = [torch.empty((max(n, 64),), dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        host = self._host_rows[self._turn % 3]               # (at most two steps are in flight)
+        self._turn += 1
+        host[:n].copy_(out[:n], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return _InFlight(out, host, done, n)
+
+    def decode_collect(self, step: "_InFlight") -> list[int]:
+        step.done.synchronize()
+        return step.host[:step.n].tolist()
+
+
+class _InFlight:
+    __slots__ = ("device_tokens", "host", "done", "n")
+
+    def __init__(self, device_tokens: torch.Tensor, host: torch.Tensor, done, n: int):
+        self.device_tokens, self.host, self.done, self.n = device_tokens, host, done, n
 
 
 class LLM:

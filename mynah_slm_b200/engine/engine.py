@@ -479,11 +479,23 @@ class Engine:
         return sampled
 
     # -------------------------------------------------- sampled decode steps
-    def decode_sampled(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+    def decode_sampled(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None,
+                       feed: Optional[tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
         """One decode step for `slots` with `tokens` as their next inputs;
         samples on the device with the sampler's current parameters and returns
-        the int32 tokens [bucket] (device; the first len(slots) rows count)."""
+        the int32 tokens [bucket] (device; the first len(slots) rows count; the
+        buffer is written again by a later step of the same size).
+        With feed = (result of an earlier step, rows) sequence i's input is that
+        result's row rows[i], taken on the device: the host need not have seen it."""
         pages = self.cache.pages
+        if feed is not None:
+            if not (self.use_graphs and self.graph_safe):
+                raise EngineError("a step fed from the device needs CUDA graphs")
+            if len(feed[1]) != len(slots):
+                raise EngineError("feed: one row per sequence is needed")
+            tokens = [0] * len(slots)
+        elif tokens is None:
+            raise EngineError("a step needs its input tokens")
         if self.use_graphs and self.graph_safe:
             # the common case: checks, pages and the step's description in one call of the native host runtime
             slots_a = np.asarray(slots, dtype=np.int32)
@@ -506,6 +518,13 @@ class Engine:
                 raise EngineError(str(e)) from None
             g.meta.copy_(host[:g.layout.size], non_blocking=True)
             self._staging.sent(hi)
+            if feed is not None:
+                prev, rows = feed
+                n = len(slots_a)
+                if list(rows) == list(range(n)):
+                    g.ctx.tokens[:n].copy_(prev[:n])
+                else:
+                    g.ctx.tokens[:n].copy_(prev[torch.tensor(list(rows), dtype=torch.int64, device=self.device)])
             out = self._run_graph(g, "sample", 1)
             pages.commit_many(slots_a, 1)
             return out

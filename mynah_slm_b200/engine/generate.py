@@ -20,6 +20,15 @@ start, in the slots and pages that were freed.
 
 The decisions are made on the host against a small `Backend` interface, so
 they can be tested without a device.
+
+A backend that can launch a step without waiting for it (`runs_ahead`, with
+`decode_launch` and `decode_collect`) is driven one step ahead: while the device runs step n + 1,
+whose input tokens it takes from step n's result on the device, the host reads
+step n's tokens and decides. A sequence that step n ends with a stop token or
+through the callback has then run one row too many; the row is dropped, and
+the sequence gives its slot and pages back one step later. Sequences that must
+end with step n whatever it samples (token limit, full context) are not
+launched again. The results are those of the step-by-step loop.
 """
 from __future__ import annotations
 
@@ -76,6 +85,11 @@ class Backend(Protocol):
     def close(self, slot: int) -> None: ...
     def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> list[int]: ...
     def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> list[int]: ...
+    # Optional, with `runs_ahead = True`:
+    #   decode_launch(slots, tokens=None, feed=None) -> handle   starts a step and returns at once; the input
+    #       tokens are `tokens` (host ids) or, with feed = (handle of the step before, rows), row rows[i] of that
+    #       step's result, taken on the device;
+    #   decode_collect(handle) -> list[int]                      waits for that step and returns its tokens.
 
 
 class GenerationError(RuntimeError):
@@ -180,6 +194,36 @@ def generate(backend: Backend, requests: Sequence[Request], stop_ids: Sequence[i
                 else:
                     backend.close(l.slot)
             live = going
+            if getattr(backend, "runs_ahead", False):
+                # one step ahead: `rows` are the sequences of the step in flight, in its row order; `dead` those
+                # among them that an earlier step has ended (their rows are dropped, their slots closed below)
+                def certain_end(l: _Live) -> bool:          # its next token ends it whatever it is
+                    return (results[l.index].produced + 1 >= requests[l.index].max_new
+                            or l.length + 1 >= backend.max_positions)
+                rows = list(live)
+                dead: set[int] = set()
+                handle = backend.decode_launch([l.slot for l in rows], tokens=[l.next_token for l in rows]) if rows else None
+                while handle is not None:
+                    ahead = [(j, l) for j, l in enumerate(rows) if l.index not in dead and not certain_end(l)]
+                    nxt = None
+                    if ahead:
+                        nxt = backend.decode_launch([l.slot for _, l in ahead], feed=(handle, [j for j, _ in ahead]))
+                    toks = backend.decode_collect(handle)
+                    for l, tok in zip(rows, toks):
+                        if l.index in dead:                 # ended a step ago: this row was one too many
+                            dead.discard(l.index)
+                            live.remove(l)
+                            backend.close(l.slot)
+                            continue
+                        l.length += 1
+                        if not accept(l, int(tok)):
+                            if nxt is not None and any(a is l for _, a in ahead):
+                                dead.add(l.index)           # it is in the step in flight: close when that is done
+                            else:
+                                live.remove(l)
+                                backend.close(l.slot)
+                    rows = [l for _, l in ahead]
+                    handle = nxt
             while live:
                 toks = backend.decode([l.slot for l in live], [l.next_token for l in live])
                 going = []

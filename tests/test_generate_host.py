@@ -140,3 +140,87 @@ def test_slots_are_given_back_when_a_step_fails():
     with pytest.raises(RuntimeError, match="boom"):
         generate(be, [Request([1], 5), Request([2], 5)])
     assert not be.state
+
+
+# ---------------------------------------------------------------- one step ahead
+
+class ScriptedAhead(Scripted):
+    """The same scripted sequences behind the launch/collect pair: a launched step's result stays "on the
+    device" (in the handle) until it is collected, and a later launch may be fed from it row by row."""
+    runs_ahead = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.in_flight = 0
+
+    def decode(self, slots, tokens):
+        raise AssertionError("a backend that runs ahead is not driven step by step")
+
+    def decode_launch(self, slots, tokens=None, feed=None):
+        if feed is not None:
+            prev, rows = feed
+            assert tokens is None and len(rows) == len(slots)
+            tokens = [prev["tokens"][j] for j in rows]          # taken "on the device"
+        for s, t in zip(slots, tokens):
+            assert s in self.state, "a closed slot is stepped"
+            assert t == self.state[s][0], "the step must be fed the token sampled for this sequence"
+            assert self.state[s][1] < self.max_positions, "a step beyond the last position"
+            self.state[s][1] += 1
+        self.in_flight += 1
+        assert self.in_flight <= 2
+        self.log.append(("decode", tuple(slots)))
+        return {"tokens": [self._next(s) for s in slots], "collected": False}
+
+    def decode_collect(self, h):
+        assert not h["collected"]
+        h["collected"] = True
+        self.in_flight -= 1
+        return list(h["tokens"])
+
+
+SCENARIOS = [
+    dict(reqs=[([100, 1, 2], 5), ([200], 2), ([300] * 7, 4)], kw={}),
+    dict(reqs=[([10], 10), ([20], 10)], kw=dict(stop_ids=[13, 22])),
+    dict(reqs=[([10], 10)], kw=dict(stop_ids=[11])),
+    dict(reqs=[([100 * (i + 1)], 1 + i) for i in range(5)], kw=dict(max_batch=2), n_slots=2),
+    dict(reqs=[([1, 2, 3], 0), ([50, 1, 1, 1], 10)], kw={}, max_positions=6),
+    dict(reqs=[([10], 5), ([20], 3), ([30], 1), ([40], 9)], kw=dict(stop_ids=[43, 12])),
+]
+
+
+@pytest.mark.parametrize("sc", SCENARIOS)
+def test_one_step_ahead_gives_the_step_by_step_results(sc):
+    outs = []
+    for cls in (Scripted, ScriptedAhead):
+        be = cls(max_positions=sc.get("max_positions", 4096), n_slots=sc.get("n_slots", 8))
+        seen = []
+        out = generate(be, [Request(list(p), n) for p, n in sc["reqs"]], callback=lambda i, t: seen.append((i, t)) or 0, **sc["kw"])
+        assert not be.state                                                       # every slot given back, once
+        outs.append(([(r.tokens, r.produced, r.finish_reason) for r in out], sorted(seen), be))
+    assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1]
+    assert outs[1][2].in_flight == 0
+
+
+def test_one_step_ahead_runs_a_stopped_sequence_one_row_more_and_no_certain_end():
+    be = ScriptedAhead()
+    out = generate(be, [Request([10], 10), Request([20], 3)], stop_ids=[12])
+    assert out[0].tokens == [11] and out[0].finish_reason == "stop" and out[1].tokens == [21, 22, 23]
+    steps = [e for e in be.log if e[0] in ("decode", "close")]
+    # step 1 samples 12 (stop) for slot 0, but step 2 was already launched with it; it is closed after that step.
+    # Slot 1 samples its third and last token in step 2, which is known beforehand: there is no step 3.
+    assert steps == [("decode", (0, 1)), ("decode", (0, 1)), ("close", 0), ("close", 1)]
+
+
+def test_one_step_ahead_callback_and_failure():
+    be = ScriptedAhead()
+    out = generate(be, [Request([10], 5), Request([20], 3)], callback=lambda i, t: 1 if (i, t) == (0, 12) else 0)
+    assert out[0].tokens == [11, 12] and out[0].finish_reason == "callback" and out[1].tokens == [21, 22, 23]
+    assert not be.state
+
+    class Failing(ScriptedAhead):
+        def decode_collect(self, h):
+            raise RuntimeError("boom")
+    be = Failing()
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(be, [Request([1], 5), Request([2], 5)])
+    assert not be.state
