@@ -418,7 +418,7 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     __shared__ float inv_s[MAX_G];
     const int h = blockIdx.x, b = blockIdx.y;
     griddep_wait();
-    griddep_launch();
+    griddep_launch_small();
     const int hi = kv_len[b];
     const int lo = window > 0 ? max(0, hi - window) : 0;
     const int n_vis = hi > 0 ? min(S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;

@@ -114,6 +114,11 @@ __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.
 __device__ __forceinline__ void griddep_launch() {}
 #endif
 
+// The same for the small kernels between the products (norms, rotation and cache write, merge): their few CTAs
+// start at once, so letting the product behind them start too costs them nothing, and that product's CTAs
+// fetch their first weights while these still run.
+__device__ __forceinline__ void griddep_launch_small() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 1: launch the decode-path kernels with the programmatic-serialization attribute.
 int mynah_pdl_enabled();
 

@@ -48,7 +48,7 @@ template <typename TA>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
                                const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
     __shared__ float red[32];
-    griddep_launch();
+    griddep_launch_small();
     griddep_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + (size_t)r * D;
@@ -81,7 +81,7 @@ template <typename TA>
 __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
                                     const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
     __shared__ float red[32];
-    griddep_launch();
+    griddep_launch_small();
     griddep_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + (size_t)r * D;

@@ -139,6 +139,10 @@ class _PromptGraph:
     last_use: int = 0
 
 
+# Decode steps of at most this many rows are captured with programmatic dependent launch (0: none).
+PDL_MAX_ROWS = int(os.environ.get("MYNAH_PDL_MAX_ROWS", "2"))
+
+
 def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
@@ -445,14 +449,22 @@ class Engine:
         from ..ops import lib
         if mode not in g.graphs:
             # first use of this bucket: run once for real (this also sizes scratch
-            # memory and warms the library), then record the same launches
-            n0 = lib.launch_count()
-            out = self._decode_body(g, mode)
-            n_kernels = lib.launch_count() - n0
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                res = self._decode_body(g, mode)
+            # memory and warms the library), then record the same launches.
+            # Steps of one or two sequences are recorded with programmatic dependent launch: their kernels are
+            # so short that a product's start under the norm before it shows (batch 1: 1.014 -> 0.984 ms a
+            # step); from batch 8 on it measured the same or slower.
+            pdl_before = lib.set_pdl(True) if g.bucket <= PDL_MAX_ROWS else None
+            try:
+                n0 = lib.launch_count()
+                out = self._decode_body(g, mode)
+                n_kernels = lib.launch_count() - n0
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    res = self._decode_body(g, mode)
+            finally:
+                if pdl_before is not None:
+                    lib.set_pdl(pdl_before)
             lib.add_launches(-n_kernels)              # recorded, not run
             res.copy_(out)                             # the eager run has produced this step's result
             g.graphs[mode] = (graph, res, n_kernels)

@@ -127,10 +127,25 @@ def load() -> ctypes.CDLL:
     if arch != 100:
         raise KernelLibraryError(f"the kernels are built for sm_100a only; the current device reports sm_{arch}")
     import os
-    if os.environ.get("MYNAH_PDL", "0") == "1":        # programmatic dependent launch of the decode kernels
-        lib.mynah_set_pdl(1)
+    global _pdl
+    _pdl = os.environ.get("MYNAH_PDL", "0") == "1"     # programmatic dependent launch of every kernel launched from here on
+    lib.mynah_set_pdl(1 if _pdl else 0)
     _lib = lib
     return lib
+
+
+_pdl = False
+
+
+def set_pdl(on: bool) -> bool:
+    """Launch the kernels from now on with (or without) the programmatic-serialization attribute, which lets a
+    kernel start while the one before it on the stream still runs, up to its `griddepcontrol.wait`. A captured
+    graph keeps what was set while it was captured. Returns the setting before."""
+    global _pdl
+    before = _pdl
+    load().mynah_set_pdl(1 if on else 0)
+    _pdl = bool(on)
+    return before
 
 
 def register(name: str, argtypes: list, restype=c_int) -> None:
