@@ -105,6 +105,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int kt_hi = (past + q0 + rows_valid - 1) / BKV;      // tile of the last key that the last row sees
     const int kt_lo = a.window > 0 ? max(0, past + q0 - a.window + 1) / BKV : 0;
     const int n_tiles = kt_hi - kt_lo + 1;
+    const int lo_min = a.window > 0 ? max(0, past + q0 - a.window + 1) : 0;    // the first key that any row of the tile sees
     const int kvh = h / (a.H / a.KV);
 
     if (threadIdx.x == 0) {
@@ -142,13 +143,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int st = j & 1;
                 const uint32_t prev_use = ((j >> 1) & 1) ^ 1;  // parity of the stage's use before this one
                 const int key0 = (kt_lo + j) * BKV;
-                const int p0 = page_of(pt, b, key0);
-                const int p1 = key0 + PAGE_TOKENS < kvl ? page_of(pt, b, key0 + PAGE_TOKENS) : -1;
-                if (p0 < 0 || (key0 + PAGE_TOKENS < kvl && p1 < 0)) {
+                // A page is brought only if it holds a key that some row of the tile sees: the first page of the
+                // first tile may lie wholly before the window (a cache that keeps a window has given it back),
+                // the second page of the last tile beyond the sequence's end.
+                const bool need0 = key0 + PAGE_TOKENS > lo_min, need1 = key0 + PAGE_TOKENS < kvl;
+                const int p0 = need0 ? page_of(pt, b, key0) : -1;
+                const int p1 = need1 ? page_of(pt, b, key0 + PAGE_TOKENS) : -1;
+                if ((need0 && p0 < 0) || (need1 && p1 < 0) || (!need0 && !need1)) {
                     atomicOr(status, MYNAH_ST_PAGE_RANGE);
                     break;
                 }
-                const uint32_t bytes = (p1 >= 0 ? 2 : 1) * HALVES * PAGE_BYTES;
+                const uint32_t bytes = ((p0 >= 0 ? 1 : 0) + (p1 >= 0 ? 1 : 0)) * HALVES * PAGE_BYTES;
                 if (j >= 2 && !mbar_wait(s_full + 8 * st, prev_use)) {      // the scores of tile j-2 are done: its K is free
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
@@ -157,7 +162,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mbar_expect_tx(k_full + 8 * st, bytes);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; hf++) {
-                    tma_load_2d(smem_u32(kd + hf * HALF_BYTES), &map_k, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
+                    if (p0 >= 0) tma_load_2d(smem_u32(kd + hf * HALF_BYTES), &map_k, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
                     if (p1 >= 0) tma_load_2d(smem_u32(kd + hf * HALF_BYTES + PAGE_BYTES), &map_k, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
                 }
                 k_issued = j + 1;
@@ -169,7 +174,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mbar_expect_tx(v_full + 8 * st, bytes);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; hf++) {
-                    tma_load_2d(smem_u32(vd + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
+                    if (p0 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
                     if (p1 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
                 }
                 v_issued = j + 1;
@@ -303,9 +308,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tc_st32(t_s + grp * (HALF_KEYS / 2), pk);
             tc_wait_st();
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            if ((kt_lo + j) * BKV + BKV > kvl) {               // the sequence ends inside this tile: zero V beyond its end
+            // Rows of V that were not brought (beyond the sequence's end, or a first page wholly before the window)
+            // hold whatever was there: zero them, a probability of zero times a stale NaN would still be NaN.
+            const int tile_key0 = (kt_lo + j) * BKV;
+            const bool past_end = tile_key0 + BKV > kvl, before_window = tile_key0 + PAGE_TOKENS <= lo_min;
+            if (past_end || before_window) {
                 if (!warp_wait(v_full + 8 * st, use)) { ok = false; break; }
-                if (row >= kvl - (kt_lo + j) * BKV) {
+                if ((past_end && row >= kvl - tile_key0) || (before_window && row < PAGE_TOKENS)) {
                     for (int hf = grp; hf < HALVES; hf += 2) {
                         uint4* dst = reinterpret_cast<uint4*>(v_s + st * TILE_BYTES + hf * HALF_BYTES + row * 128);
 #pragma unroll

@@ -272,6 +272,28 @@ def test_a_long_context(tmp_path, name, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_a_prompt_piece_far_behind_a_short_window(tmp_path, name, dtype):
+    """Windows of 40 positions and pages of 64: when a prompt goes on in pieces, the windowed layers have given
+    back whole pages before the piece's first key tile ends, so a tile's first page may not exist any more. Pieces
+    that start at many offsets of a page and of a key tile, against the plain implementation."""
+    wdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = make_folder(tmp_path, name, wdt)
+    plain = PlainQwen3.from_folder(folder)
+    eng = _engine(folder, dtype, 64 * 16)
+    rng = np.random.default_rng(91)
+    for cuts in ([0, 150, 230], [0, 104, 105, 300], [0, 64, 128, 192, 256, 320], [0, 200, 201, 264, 330], [0, 127, 171, 340]):
+        n = cuts[-1]
+        toks = rng.integers(0, TINY[name]["vocab_size"], size=n).tolist()
+        ref = plain.forward(toks)
+        slot = eng.open_sequence()
+        got = [eng.step([_entry(slot, toks[lo:hi], range(hi - lo))]).cpu().numpy() for lo, hi in zip(cuts[:-1], cuts[1:])]
+        eng.check_status()
+        eng.close_sequence(slot)
+        assert_close(ref, np.concatenate(got), tol(dtype), f"{name} {dtype} pieces at {cuts}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_padding_and_company_change_nothing(folders, dtype):
     """A decode step's logits for one sequence have the same bits whether its
     rows are padding or other sequences and whichever row it takes. In 32-bit
