@@ -271,6 +271,42 @@ def test_a_long_context(tmp_path, name, window):
         assert_close(ref[n + t:n + t + 1], got[1:2], BF16_REL, f"decode step {t}, the sequence that came in pieces")
 
 
+def test_layers_of_the_benchmark_shape(tmp_path):
+    """Two layers with the layer sizes of the measured configuration (width 1,024, 16 query heads over 8 kv heads
+    of 128, feed-forward 3,072; a small odd vocabulary keeps the plain implementation quick): the prompt-step
+    products run as pairs of CTAs, with K in two halves and with the fused activation, the prompt attention has 17
+    key tiles, decode steps read 33 pages. A prompt of 2,100 tokens alone, a ragged batch of two more, then all
+    three token by token, against the plain implementation."""
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=1024,
+               num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=4099,
+               rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+               hidden_act="silu", attention_bias=False, rope_scaling=None, use_sliding_window=False, sliding_window=None,
+               max_window_layers=2, eos_token_id=1)
+    folder = make_folder(tmp_path, "shape", torch.bfloat16, config=cfg, seed=5)
+    plain = PlainQwen3.from_folder(folder)
+    eng = _engine(folder, "bfloat16", 64 * 80)
+    rng = np.random.default_rng(123)
+    lens = [2100, 700, 1300]
+    seqs = [rng.integers(0, cfg["vocab_size"], size=n + 3).tolist() for n in lens]
+    refs = [plain.forward(s) for s in seqs]
+    slots = [eng.open_sequence() for _ in seqs]
+    places = (0, 127, 128, 1000, 2047, 2048, lens[0] - 1)
+    got = eng.step([_entry(slots[0], seqs[0][:lens[0]], places)]).cpu().numpy()
+    eng.check_status()
+    for i, j in enumerate(places):
+        assert_close(refs[0][j:j + 1], got[i:i + 1], BF16_REL, f"prompt of {lens[0]}, place {j}")
+    got = eng.step([_entry(slots[1], seqs[1][:lens[1]], (0, 255, lens[1] - 1)),
+                    _entry(slots[2], seqs[2][:lens[2]], (63, 64, lens[2] - 1))]).cpu().numpy()
+    eng.check_status()
+    for r, (i, j) in enumerate([(1, 0), (1, 255), (1, lens[1] - 1), (2, 63), (2, 64), (2, lens[2] - 1)]):
+        assert_close(refs[i][j:j + 1], got[r:r + 1], BF16_REL, f"ragged batch, sequence {i}, place {j}")
+    for t in range(3):
+        got = eng.step([_entry(s, [q[n + t]], (0,)) for s, q, n in zip(slots, seqs, lens)]).cpu().numpy()
+        eng.check_status()
+        for i, n in enumerate(lens):
+            assert_close(refs[i][n + t:n + t + 1], got[i:i + 1], BF16_REL, f"decode step {t}, sequence {i}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["C", "E"])
 def test_a_prompt_piece_far_behind_a_short_window(tmp_path, name, dtype):
