@@ -499,6 +499,13 @@ __device__ int argmax_from_parts(const float* __restrict__ part_val, const int* 
     return bi == 0x7fffffff ? 0 : bi;
 }
 
+// A top-k of at most MAX_CAND entries is drawn by sample_top_k_kernel, everything else by sample_kernel; both are
+// launched for every step (the parameters are read on the device) and each leaves at once when the other is due.
+constexpr int MAX_CAND = 256;
+__device__ __forceinline__ bool small_top_k(const SampleParams& sp, int V) {
+    return sp.temp > 0.f && sp.top_k > 0 && sp.top_k <= MAX_CAND && sp.top_k < V;
+}
+
 // One CTA a row, or for a large vocabulary the ROW_CTAS CTAs of a cluster (NC), each with a consecutive part of
 // the row. The row of logits is overwritten with probabilities when the temperature is positive (the
 // reference's sampler also works in place).
@@ -511,6 +518,7 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     griddep_launch();
     griddep_wait();
     const SampleParams sp{params[0], params[1], params[2], (int)params[3]};
+    if (small_top_k(sp, V)) return;          // (every CTA of the launch: sample_top_k_kernel draws this step)
     const int b = NC == 1 ? blockIdx.x : blockIdx.x / NC;
     float* row = logits + (size_t)b * ld;
     const int slot = slots ? slots[b] : b;
@@ -626,6 +634,171 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     }
 }
 
+// The draw with a small top-k (sampler.c:132-186, the same decisions in another order). The k largest
+// probabilities are found once (a search by count, then the id up to which entries equal to the k-th belong),
+// gathered into the leading CTA and sorted by (probability descending, id ascending), which is the order that
+// the general kernel walks. min-p, top-p, the kept mass and the drawn place are then prefixes of at most k
+// entries, walked by one thread in the same integer arithmetic: seven passes over the row instead of thirteen.
+struct Candidates {
+    unsigned long long key[MAX_CAND];      // probability bits above, ~id below: larger keys come first
+    unsigned int n;
+};
+
+template <int NC>
+__global__ void __launch_bounds__(THREADS)
+sample_top_k_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict__ params,
+                    unsigned long long* __restrict__ rng, const int* __restrict__ slots, int* __restrict__ out,
+                    const float* __restrict__ part_val, const int* __restrict__ part_idx) {
+    __shared__ Shared sh;
+    __shared__ Candidates cand;
+    griddep_launch();
+    griddep_wait();
+    const SampleParams sp{params[0], params[1], params[2], (int)params[3]};
+    if (!small_top_k(sp, V)) return;         // (every CTA of the launch)
+    const int b = NC == 1 ? blockIdx.x : blockIdx.x / NC;
+    float* row = logits + (size_t)b * ld;
+    const int slot = slots ? slots[b] : b;
+    const RowShare<NC> rs(V);
+    if (slot < 0) {                          // padding row (all CTAs of the row leave)
+        if (threadIdx.x == 0 && rs.rank == 0) out[b] = 0;
+        return;
+    }
+    if (threadIdx.x == 0) sh.turn = 0;
+    float mx;
+    const int best = part_val != nullptr ? argmax_from_parts(part_val, part_idx, b, sh, &mx) : block_argmax(row, V, sh, &mx);
+    // p_i = expf((l_i - max) / temp) * (float)(1 / sum), the sum in double, as in sample_kernel
+    double part = 0.0;
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < rs.end ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            if (i < rs.end) {
+                const float e = expf((vals[u] - mx) / sp.temp);
+                row[i] = e;
+                part += (double)e;
+            }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) sh.red_d[warp] = part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double mine = 0.0;
+        for (int w = 0; w < THREADS / 32; w++) mine += sh.red_d[w];
+        sh.part_d = mine;
+    }
+    rs.sync();
+    double sum = 0.0;
+    for (int r = 0; r < NC; r++) sum += *rs.at(&sh.part_d, r);
+    const float inv = (float)(1.0 / sum);
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < rs.end ? row[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            if (i < rs.end) row[i] = vals[u] * inv;
+        }
+    }
+    if (threadIdx.x == 0) cand.n = 0;
+    for (int i = threadIdx.x; i < MAX_CAND; i += THREADS) cand.key[i] = 0ull;
+    rs.sync();                                              // the row holds probabilities; the leading CTA's list is empty
+    const float p_best = __ldcg(row + best);
+
+    // the k-th largest probability, and the last id among its equals that still belongs to the k
+    const Prefix topk = find_prefix<NC>(row, rs, false, (unsigned int)sp.top_k, 0, sh);
+    const int id_bound = nth_equal<NC>(row, rs, topk.value, topk.ties, sh);
+    unsigned int* cnt = rs.at(&cand.n, 0);
+    unsigned long long* keys = rs.at(&cand.key[0], 0);
+    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
+        float vals[LOADS];
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            vals[u] = i < rs.end ? __ldcg(row + i) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < LOADS; u++) {
+            const int i = base0 + u * THREADS + (int)threadIdx.x;
+            const unsigned int bits = __float_as_uint(vals[u]);     // probabilities are not negative: bits order as values
+            if (i < rs.end && (bits > topk.value || (bits == topk.value && i <= id_bound))) {
+                const unsigned int at = atomicAdd(cnt, 1u);
+                if (at < (unsigned int)MAX_CAND) keys[at] = ((unsigned long long)bits << 32) | (0xffffffffu - (unsigned int)i);
+            }
+        }
+    }
+    rs.sync();                                              // the list is complete
+    if (rs.rank != 0) return;                               // (the leading CTA reads its own memory only from here on)
+    // bitonic sort, largest key first: larger probability, then lower id
+    for (int size = 2; size <= MAX_CAND; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const int t = threadIdx.x, partner = t ^ stride;
+            if (t < MAX_CAND && partner > t) {
+                const unsigned long long a = cand.key[t], c = cand.key[partner];
+                const bool descending = (t & size) == 0;
+                if (descending ? a < c : a > c) {
+                    cand.key[t] = c;
+                    cand.key[partner] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (threadIdx.x != 0) return;
+    const unsigned int n_c = min(cand.n, (unsigned int)MAX_CAND);      // top_k, unless the row has fewer entries
+    unsigned int n = n_c;
+    if (sp.min_p > 0.f) {
+        const float floor_p = sp.min_p * p_best;
+        unsigned int c = 0;
+        while (c < n_c && __uint_as_float((unsigned int)(cand.key[c] >> 32)) >= floor_p) c++;
+        if (c < 1) c = 1;
+        if (c < n) n = c;
+    }
+    if (sp.top_p < 1.0f) {
+        unsigned long long target = __double2ull_ru((double)sp.top_p * 1152921504606846976.0);
+        if (target == 0) target = 1;
+        unsigned long long cum = 0;
+        for (unsigned int i = 0; i < n; i++) {
+            cum += mass_of(__uint_as_float((unsigned int)(cand.key[i] >> 32)));
+            if (cum >= target) {
+                n = i + 1;
+                break;
+            }
+        }
+    }
+    if (n < 1) n = 1;
+    unsigned long long total = 0;
+    for (unsigned int i = 0; i < n; i++) total += mass_of(__uint_as_float((unsigned int)(cand.key[i] >> 32)));
+    unsigned long long state = rng[slot];
+    const double u = splitmix_uniform(&state);
+    unsigned long long target = __double2ull_ru(u * (double)total);
+    if (target > total) target = total;
+    if (target == 0) target = 1;
+    unsigned int pick = n - 1;                              // (only through rounding: the last kept one)
+    unsigned long long cum = 0;
+    for (unsigned int i = 0; i < n; i++) {
+        cum += mass_of(__uint_as_float((unsigned int)(cand.key[i] >> 32)));
+        if (cum >= target) {
+            pick = i;
+            break;
+        }
+    }
+    out[b] = n_c > 0 ? (int)(0xffffffffu - (unsigned int)cand.key[pick]) : best;
+    rng[slot] = state;
+}
+
 // One thread per row: the reference's loop over the ring of recent tokens,
 // entry by entry (a token that sits in the ring c times is penalised c times).
 // The ring rows are `stride` apart; the window in use is params[7] <= stride.
@@ -724,11 +897,17 @@ MYNAH_API int mynah_sample(float* logits, int B, int V, int ld, const float* par
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel<ROW_CTAS>, logits, V, ld, params, rng, slots, out,
-                                                 (const float*)part_val, (const int*)part_idx);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, sample_top_k_kernel<ROW_CTAS>, logits, V, ld, params, rng, slots, out,
+                                           (const float*)part_val, (const int*)part_idx);
+        if (e == cudaSuccess)
+            e = cudaLaunchKernelEx(&cfg, sample_kernel<ROW_CTAS>, logits, V, ld, params, rng, slots, out,
+                                   (const float*)part_val, (const int*)part_idx);
         if (e != cudaSuccess) return mynah_fail("sample: %s", cudaGetErrorString(e));
         return mynah_check_launch("sample");
     }
+    mynah_launch(sample_top_k_kernel<1>, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out,
+                 (const float*)part_val, (const int*)part_idx);
+    if (mynah_check_launch("sample (top-k)")) return -1;
     mynah_launch(sample_kernel<1>, dim3(B), dim3(THREADS), 0, stream, logits, V, ld, params, rng, slots, out,
                  (const float*)part_val, (const int*)part_idx);
     return mynah_check_launch("sample");
