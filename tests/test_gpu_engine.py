@@ -409,6 +409,32 @@ def test_greedy_generation_through_the_entry_point(folders, plain_models, name, 
     assert llm.last_timing.n_gen == stop_at + 1 and "decode" in llm.last_timing.format()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_without_the_host_in_between(folders, dtype):
+    """`decode_loop` (K sampled steps with the token fed back on the device, what the measurement times) against
+    the same K steps through the host: the same tokens, and the same cache afterwards."""
+    from mynah_slm_b200.sampling.sampler import SamplingParams
+    prompts = prompts_for("B", [40, 3, 65], seed=9)
+    K = 9
+    lasts, afters = [], []
+    for through_host in (False, True):
+        eng = _engine(folders[("B", torch.bfloat16)], dtype, 64 * 8)
+        eng.sampler.set_params(SamplingParams(temp=0.0))
+        slots = [eng.open_sequence() for _ in prompts]
+        logits = eng.step([_entry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
+        toks = logits.argmax(dim=-1).cpu().tolist()
+        if through_host:
+            for _ in range(K):
+                toks = eng.decode_sampled(slots, toks)[:len(slots)].cpu().tolist()
+        else:
+            toks = eng.decode_loop(slots, toks, K)[:len(slots)].cpu().tolist()
+        eng.check_status()
+        lasts.append(toks)
+        afters.append(eng.step([_entry(s, [t], (0,)) for s, t in zip(slots, toks)]).cpu())
+    assert lasts[0] == lasts[1]
+    assert torch.equal(afters[0], afters[1])
+
+
 def test_temperature_generation_matches_plain_in_32_bit(folders, plain_models):
     """Temperature 0.8, seed 1, on B in 32-bit: token for token what the plain
     sampler draws from the plain model, whatever the batch."""
