@@ -69,6 +69,22 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two fp32 operations an instruction (each half is the plain round-to-nearest operation), and the maximum of
+// three: the softmax warps are bound by the number of instructions they issue.
+__device__ __forceinline__ void fma2(float& x0, float& x1, float a0, float a1, float b, float c) {
+    asm("{ .reg .b64 ra, rb, rc, rd;\n\t mov.b64 ra, {%2, %3};\n\t mov.b64 rb, {%4, %4};\n\t mov.b64 rc, {%5, %5};\n\t"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n\t mov.b64 {%0, %1}, rd; }"
+        : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& x0, float& x1, float a0, float a1) {
+    asm("{ .reg .b64 ra, rb;\n\t mov.b64 ra, {%0, %1};\n\t mov.b64 rb, {%2, %3};\n\t add.rn.f32x2 ra, ra, rb;\n\t mov.b64 {%0, %1}, ra; }"
+        : "+f"(x0), "+f"(x1) : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -261,7 +277,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < HALF_KEYS; e++) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+            for (int e = 0; e < HALF_KEYS; e += 2) mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], s[e], s[e + 1]);
             const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the row's maximum over both groups, through shared memory (two buffers: a value is read before the
             // barrier of the next tile, and overwritten only after it)
@@ -295,13 +311,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 tc_wait_st();
             }
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};              // two pairs of running sums
             uint32_t pk[HALF_KEYS / 2];
 #pragma unroll
             for (int e = 0; e < HALF_KEYS; e += 2) {
-                const float p0 = ex2(fmaf(s[e], a.scale_log2, -m_use));           // 2^-inf = 0
-                const float p1 = ex2(fmaf(s[e + 1], a.scale_log2, -m_use));
-                sum4[(e >> 1) & 3] += p0 + p1;
+                float x0, x1;
+                fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
+                const float p0 = ex2(x0), p1 = ex2(x1);                           // 2^-inf = 0
+                add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
                 pk[e >> 1] = pack2(p0, p1);
             }
             // over the scores: both groups have theirs in registers since the exchange above
