@@ -154,6 +154,9 @@ def main(argv: list[str] | None = None) -> int:
     if argv[0] in ("--help", "-h"):
         print(USAGE)
         return 0
+    if argv[0] in ("run", "random") and any(a in ("--help", "-h") for a in argv[1:]):
+        print(USAGE)
+        return 0
     if argv[0] == "run":
         return cmd_run(argv[1:])
     if argv[0] == "random":
