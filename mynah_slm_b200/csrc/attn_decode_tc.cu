@@ -442,7 +442,7 @@ struct FusedArgs {
     float scale, qk_eps;
 };
 
-template <int HD>
+template <int HD, bool MERGE>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -661,6 +661,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
         }
     }
 
+    if (!MERGE) return;                               // the merge is a launch of its own (a CTA a head)
     // ---- the CTA that finishes this (sequence, kv head) last merges the pages
     __syncthreads();                                  // the CTA's partial is written ...
     if (tid == 0) {
@@ -742,7 +743,7 @@ MYNAH_API int mynah_attn_decode_fused(
     MYNAH_REQUIRE(mynah_attn_decode_tc_supported(H, KV, HD), "attn_decode_fused: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0, "attn_decode_fused: row strides %d, %d must be multiples of 8", ldq, ldo);
     MYNAH_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 65535 && KV <= 65535, "attn_decode_fused: launch too large");
-    MYNAH_REQUIRE(scratch != nullptr && counters != nullptr, "attn_decode_fused: no scratch memory given");
+    MYNAH_REQUIRE(scratch != nullptr, "attn_decode_fused: no scratch memory given");
     MYNAH_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "attn_decode_fused: the two rotation tables go together");
     MYNAH_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "attn_decode_fused: the two gains go together");
     MYNAH_REQUIRE((size_t)(H / KV) * n_splits * sizeof(float) <= MERGE_MAX_BYTES,
@@ -754,11 +755,27 @@ MYNAH_API int mynah_attn_decode_fused(
     float* part_ml = scratch + (size_t)B * H * n_splits * HD;
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
     const dim3 grid(n_splits, KV, B);
+    if (counters == nullptr) {
+        // without counters: the pages' CTAs do not merge; the merge follows as a launch of its own (the same bits)
+        if (HD == 128)
+            mynah_launch(attn_decode_fused_kernel<128, false>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+                         kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
+        else
+            mynah_launch(attn_decode_fused_kernel<64, false>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+                         kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
+        if (mynah_check_launch("attn_decode_fused (pages)")) return -1;
+        const size_t dyn_m = (size_t)n_splits * sizeof(float);
+        if (HD == 128)
+            mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+        else
+            mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+        return mynah_check_launch("attn_decode_merge");
+    }
     if (HD == 128)
-        mynah_launch(attn_decode_fused_kernel<128>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+        mynah_launch(attn_decode_fused_kernel<128, true>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
                      kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
     else
-        mynah_launch(attn_decode_fused_kernel<64>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
+        mynah_launch(attn_decode_fused_kernel<64, true>, grid, dim3(WARPS * 32), dyn, stream, (const bf16*)qkv, qg, kg, cos_t, sin_t, tok_pos,
                      kv_len, pt, (bf16*)k_cache, (bf16*)v_cache, a, part_o, part_ml, counters, (bf16*)out, status);
     return mynah_check_launch("attn_decode_fused");
 }

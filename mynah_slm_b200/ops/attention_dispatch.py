@@ -44,12 +44,24 @@ def _tc_fits(H: int, KV: int, n_splits: int) -> bool:
     return (H // KV) * n_splits <= _MERGE_FLOATS
 
 
+# Larger steps can still let the pages' kernel prepare the queries and write the new key and value itself (no
+# rotation/cache-write launch before it) and merge with a launch of its own. 1: do so.
+FUSED_PREP_LARGE = os.environ.get("MYNAH_FUSED_ATTN_PREP", "0") == "1"
+
+
 def decode_fused_ok(dtype: torch.dtype, H: int, KV: int, HD: int, rotary_dim: int, cos, B: int, n_splits: int) -> bool:
     """Whether the one-launch decode attention takes this layer in this step: the tensor-core sizes, a rotation
     of the whole head or none, and few enough CTAs."""
-    if B * KV * n_splits > FUSED_DECODE_MAX_CTAS or not kernels.attn_decode_tc_supported(dtype, H, KV, HD):
+    if not kernels.attn_decode_tc_supported(dtype, H, KV, HD):
+        return False
+    if B * KV * n_splits > FUSED_DECODE_MAX_CTAS and not FUSED_PREP_LARGE:
         return False
     return _tc_fits(H, KV, n_splits) and (cos is None or rotary_dim == HD)
+
+
+def decode_fused_merges(B: int, KV: int, n_splits: int) -> bool:
+    """Whether the one-launch form also merges (small steps), or leaves the merge to a launch of its own."""
+    return B * KV * n_splits <= FUSED_DECODE_MAX_CTAS
 
 
 # Whether the pages' kernel of the tensor-core decode attention also merges (the CTA that finishes a sequence's

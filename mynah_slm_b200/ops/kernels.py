@@ -370,18 +370,20 @@ def attn_decode_fused(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: 
                       cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], tok_pos: torch.Tensor,
                       k_cache: torch.Tensor, v_cache: torch.Tensor, write_kv: bool, kv_len: torch.Tensor,
                       pages: PageTableView, window: int, n_splits: int, scratch: torch.Tensor,
-                      counters: torch.Tensor, status: torch.Tensor) -> None:
+                      counters: Optional[torch.Tensor], status: torch.Tensor) -> None:
     """Per-head norm, rotation, cache write and attention of a decode step in one launch (bfloat16, head_dim 64
     or 128, whole-head rotation or none). `qkv` holds the projection's rows; with write_kv False only q is read."""
     _chk(qkv, "qkv", torch.bfloat16, 2)
     _chk(out, "attention output", torch.bfloat16, 2)
     _chk(scratch, "scratch", torch.float32)
-    _chk(counters, "counters", torch.int32)
+    # counters None: the pages' CTAs do not merge, the merge follows as a launch of its own (the same bits)
     need = B * H * n_splits * (HD + 2)
     if scratch.numel() < need:
         raise KernelError(f"attn_decode_fused: scratch holds {scratch.numel()} floats, {need} are needed")
-    if counters.numel() < B * KV:
-        raise KernelError(f"attn_decode_fused: {counters.numel()} counters, {B * KV} are needed")
+    if counters is not None:
+        _chk(counters, "counters", torch.int32)
+        if counters.numel() < B * KV:
+            raise KernelError(f"attn_decode_fused: {counters.numel()} counters, {B * KV} are needed")
     if cos is not None and cos.shape[1] * 2 != HD:
         raise KernelError("attn_decode_fused: the rotation must cover the whole head")
     call("mynah_attn_decode_fused", ptr(qkv), ptr(out), B, H, KV, HD, qkv.shape[1], out.shape[1],

@@ -119,7 +119,8 @@ class GQAttention(Mixer):
                         qkv, out, ctx.B, H, KV, HD, self.q_gain, self.k_gain, self.qk_eps, cos, sin, ctx.tok_pos,
                         cache.k, cache.v, writes, ctx.kv_len, pages, self.window or 0, ctx.decode_splits,
                         self.runtime.attn_scratch(ctx.B, H, HD, ctx.decode_splits),
-                        self.runtime.attn_counters(ctx.B * KV), ctx.status)
+                        self.runtime.attn_counters(ctx.B * KV)
+                        if attention_dispatch.decode_fused_merges(ctx.B, KV, ctx.decode_splits) else None, ctx.status)
                     return kernels.linear(out, self.w_o)
         else:
             q_view = qkv[:, : H * HD].view(T, H, HD)
