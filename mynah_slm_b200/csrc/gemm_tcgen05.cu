@@ -90,6 +90,63 @@ struct GemmShape {
     int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
     int up_offset;
     int m_tiles, n_tiles; // m_tiles: tiles of 128 rows (one CTA) or 256 rows (a pair of CTAs)
+    float* sk_part;       // with SK: a CTA's partial accumulator, [CTAs][128][BN] fp32
+    int* sk_flag;         // with SK: [CTAs][4], set by the warp that wrote its 32 rows, cleared by the warp that read them
+};
+
+// What a unit works on next: a tile of C and a range of its k-blocks. Without SK that is a whole tile (or, with
+// KS, this CTA's half of K), tiles unit, unit + n_units, ... With SK ("stream-K") the k-blocks of all tiles,
+// tile after tile, are dealt out evenly: CTA u takes k-blocks [u * I / U, (u + 1) * I / U) of the I in all, so
+// every CTA has the same work however the number of tiles relates to the number of SMs. A tile that a boundary
+// cuts is accumulated by consecutive CTAs. The one with the tile's first k-block owns it: it finishes the tile.
+// The others (`produce`: their range starts inside the tile, so it is the first thing they do) write their
+// accumulators to their slot of `sk_part` and raise their flags; the owner, for which the tile is the last thing
+// it does, adds the `follow` slots behind its own in order and runs the epilogue. A CTA produces at most once
+// (only its first item can start inside a tile), so a slot a CTA suffices. All CTAs of the launch are resident
+// (at most one per SM is launched), so the producers run whether or not the owner waits. It is used only when
+// there are at least as many tiles as CTAs: a tile then has at most two parts, and the owner fetches the other
+// part with one bulk copy a warp into the operand ring, which is idle by then.
+struct Item {
+    int tile, kb0, kb1;
+    int follow;           // an owner's: how many of the next CTAs hold a part of this tile
+    bool produce;
+};
+
+template <bool SK>
+struct ItemIter {
+    int nk, unit, n_units, total_tiles, kb_begin, kb_end;
+    long long it, it1, total;         // SK: this CTA's range of k-blocks over all tiles
+    int tile;                         // not SK: the next tile
+    __device__ ItemIter(int nk_, int unit_, int n_units_, int total_tiles_, int kb_begin_, int kb_end_)
+        : nk(nk_), unit(unit_), n_units(n_units_), total_tiles(total_tiles_), kb_begin(kb_begin_), kb_end(kb_end_) {
+        total = (long long)total_tiles * nk;
+        it = SK ? (long long)unit * total / n_units : 0;
+        it1 = SK ? (long long)(unit + 1) * total / n_units : 0;
+        tile = unit;
+    }
+    __device__ bool next(Item& w) {
+        if (!SK) {
+            if (tile >= total_tiles) return false;
+            w.tile = tile; w.kb0 = kb_begin; w.kb1 = kb_end; w.follow = 0; w.produce = false;
+            tile += n_units;
+            return true;
+        }
+        if (it >= it1) return false;
+        w.tile = (int)(it / nk);
+        w.kb0 = (int)(it % nk);
+        const long long left = it1 - it;
+        w.kb1 = left < (long long)(nk - w.kb0) ? w.kb0 + (int)left : nk;
+        w.produce = w.kb0 != 0;
+        w.follow = 0;
+        if (!w.produce && w.kb1 < nk) {
+            const long long tile_end = (long long)(w.tile + 1) * nk;
+            int m = 1;
+            while (unit + m + 1 < n_units && (long long)(unit + m + 1) * total / n_units < tile_end) m++;
+            w.follow = m;
+        }
+        it += w.kb1 - w.kb0;
+        return true;
+    }
 };
 
 // CTAS = 2: two CTAs of a cluster share a tile of 256 x BN. Each brings its own 128 rows of A and half of the
@@ -103,7 +160,7 @@ struct GemmShape {
 // tiles, which need fewer operand bytes a flop than the 128-wide ones. When both have accumulated, each sends
 // the 128 accumulator columns that the other will finish to the other's idle operand ring (fp32, through
 // distributed shared memory), adds what it received to its own 128 columns and stores them.
-template <int BN, int EPI, int CTAS, int KS = 1>
+template <int BN, int EPI, int CTAS, int KS = 1, bool SK = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_c, GemmShape g, int* __restrict__ status, const QkvEpilogue qe) {
@@ -122,6 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t fix_bar0 = smem_u32(bars + 2 * STAGES + 5);       // SK: one per epilogue warp, used once
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nk = (g.K + BK - 1) / BK;
@@ -131,6 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         gain_s[EPI == EPI_QKV ? 1 : 0][threadIdx.x] = qe.k_gain.p != nullptr ? qe.k_gain.at(threadIdx.x) : 1.0f;
     }
     static_assert(KS == 1 || (KS == 2 && CTAS == 1 && EPI == EPI_BF16 && BN == 256), "K is split for single CTAs with bf16 rows only");
+    static_assert(!SK || (CTAS == 1 && KS == 1 && EPI != EPI_QKV), "k-blocks are dealt out to single CTAs with the plain epilogues only");
     const int rank = CTAS == 2 ? (int)cluster_ctarank() : 0;         // 0 leads
     const int krank = KS == 2 ? (int)cluster_ctarank() : 0;          // which half of K
     const int unit = blockIdx.x / (CTAS * KS), n_units = gridDim.x / (CTAS * KS);   // a unit walks over tiles: a CTA, a pair, or two halves of K
@@ -145,6 +204,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(acc_full0 + 8 * b, 1);
             mbar_init(acc_empty0 + 8 * b, 4 * CTAS);                 // one arrival per epilogue warp (of both CTAs, on the leader's)
         }
+        if (SK)
+            for (int q = 0; q < 4; q++) mbar_init(fix_bar0 + 8 * q, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -168,9 +229,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {                                             // ---- TMA producer
             int it = 0;                                              // k-blocks issued, over all tiles
             bool ok = true;
-            for (int tile = unit; tile < total_tiles && ok; tile += n_units) {
-                const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+            ItemIter<SK> items(nk, unit, n_units, total_tiles, kb_begin, kb_end);
+            Item w;
+            while (ok && items.next(w)) {
+                const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
+                for (int kb = w.kb0; kb < w.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1) || *abort_flag) {
@@ -211,7 +274,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             constexpr uint32_t idesc = umma_idesc(BM * CTAS, BN);
             int it = 0, local = 0;
             bool ok = true;
-            for (int tile = unit; tile < total_tiles && ok; tile += n_units, local++) {
+            ItemIter<SK> items(nk, unit, n_units, total_tiles, kb_begin, kb_end);
+            Item w;
+            for (; ok && items.next(w); local++) {
                 const int buf = local & 1;
                 const uint32_t use = (local >> 1) & 1;
                 if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1) || *abort_flag) {   // the epilogue has read this buffer out
@@ -221,7 +286,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = kb_begin; kb < kb_end; kb++, it++) {
+                for (int kb = w.kb0; kb < w.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(full0 + 8 * s, ph) || *abort_flag) {
@@ -235,7 +300,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
                         if (CTAS == 2) tc_mma_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb | k) != 0);
-                        else tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, ((kb - kb_begin) | k) != 0);
+                        else tc_mma(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, ((kb - w.kb0) | k) != 0);
                     }
                     // the stage is free (in both CTAs) once these have read it
                     if (CTAS == 2) tc_commit_pair(empty0 + 8 * s); else tc_commit(empty0 + 8 * s);
@@ -255,8 +320,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quad = warp & 3;
         unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
         int local = 0, n_store = 0;
-        for (int tile = unit; tile < total_tiles; tile += n_units, local++) {
-            const int m_tile = tile % g.m_tiles, n_tile = tile / g.m_tiles;
+        ItemIter<SK> items(nk, unit, n_units, total_tiles, kb_begin, kb_end);
+        Item w;
+        for (; items.next(w); local++) {
+            const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
             const int buf = local & 1;
             const uint32_t use = (local >> 1) & 1;
             if (!mbar_wait(acc_full0 + 8 * buf, use) || *abort_flag) {
@@ -269,6 +336,77 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             const int row0 = (m_tile * CTAS + rank) * BM + quad * 32;
+            if (SK && w.produce) {
+                // this CTA's part of a tile that the CTA before it owns: the accumulator goes to this CTA's slot
+                float* mine = g.sk_part + ((size_t)unit * BM + quad * 32 + lane) * BN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tc_ld32(t_row + c0, r);
+                    // 16-byte pieces, eight at a time swizzled by the row: the owner reads them from shared memory a
+                    // thread a row without meeting in a bank
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        __stcg(reinterpret_cast<float4*>(mine + c0) + (j ^ (lane & 7)), make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();                                 // the warp's rows before its flag
+                    atomicExch(g.sk_flag + unit * 4 + quad, 1);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+                continue;
+            }
+            const float* part_s = reinterpret_cast<const float*>(smem) + (size_t)(quad * 32 + lane) * BN;   // this thread's row of the fetched part
+            if (SK && w.follow > 0) {
+                // The owner of a tile whose other part the next CTA holds: when that CTA's warp of this quadrant has
+                // raised its flag, its 32 rows (one contiguous block) come into the operand ring, which is idle now
+                // (this is the CTA's last item and its products are done), with one bulk copy.
+                int got = 1;
+                if (lane == 0) {
+                    const unsigned long long t0 = now_ns();
+                    const volatile int* f = g.sk_flag + (unit + 1) * 4 + quad;
+                    for (uint32_t spin = 0; *f == 0; spin++) {
+                        if ((spin & 255u) == 255u && (now_ns() - t0 > WAIT_LIMIT_NS || *abort_flag)) {
+                            got = 0;
+                            break;
+                        }
+                    }
+                    if (got && w.follow == 1) {
+                        __threadfence();                             // the flag before the rows it announces
+                        constexpr uint32_t BYTES = 32 * BN * 4;
+                        mbar_expect_tx(fix_bar0 + 8 * quad, BYTES);
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(smem_u32(smem) + quad * BYTES), "l"(g.sk_part + ((size_t)(unit + 1) * BM + quad * 32) * BN),
+                                       "r"(BYTES), "r"(fix_bar0 + 8 * quad) : "memory");
+                    } else {
+                        got = 0;                                     // (more than two parts a tile are not launched)
+                    }
+                }
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (got && !mbar_wait(fix_bar0 + 8 * quad, 0)) got = 0;
+                if (!__all_sync(0xffffffffu, got) && lane == 0) {
+                    *abort_flag = 1;
+                    atomicOr(status, MYNAH_ST_TIMEOUT);
+                }
+            }
+            // adds the other part to 32 accumulator columns from `col` on
+            auto add_parts = [&](uint32_t (&r)[32], int col) {
+                if (SK && w.follow > 0) {
+                    const float4* src = reinterpret_cast<const float4*>(part_s + col);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const float4 v = src[j ^ (lane & 7)];
+                        r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                    }
+                }
+            };
             if (EPI == EPI_QKV) {
                 // ---- a token a thread: its heads of this tile, one after the other
                 const int row = row0 + lane;
@@ -349,6 +487,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (EPI == EPI_F32) {
                     uint32_t r[32];
                     tc_ld32(t_row + c0, r);
+                    add_parts(r, c0);
 #pragma unroll
                     for (int j = 0; j < 8; j++)
                         *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) * 16)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
@@ -357,6 +496,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int half = 0; half < 2; half++) {
                         uint32_t r[32];
                         tc_ld32(t_row + c0 + half * 32, r);
+                        add_parts(r, c0 + half * 32);
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             const uint4 v = make_uint4(pack2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
@@ -372,6 +512,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         uint32_t gt[32], up[32];
                         tc_ld32(t_row + c0 + half * 32, gt);
                         tc_ld32(t_row + 128 + c0 + half * 32, up);
+                        add_parts(gt, c0 + half * 32);
+                        add_parts(up, 128 + c0 + half * 32);
                         float o[32];
 #pragma unroll
                         for (int e = 0; e < 32; e++) {
@@ -398,6 +540,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
+                if (SK)                                              // the parts are read: their flags are clear for the next launch
+                    for (int p = 1; p <= w.follow; p++) g.sk_flag[(unit + p) * 4 + quad] = 0;
                 if (CTAS == 2) mbar_arrive_leader(acc_empty0 + 8 * buf); else mbar_arrive(acc_empty0 + 8 * buf);
             }
         }
@@ -472,12 +616,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int BN, int EPI, int CTAS, int KS = 1>
+// The stream-K workspace of the current device: a slot of 128 x 256 floats and four flags a CTA, allocated at the
+// first launch that needs it (never during a graph capture: a captured step has run once before).
+int sk_workspace(int n_ctas, float** part, int** flag) {
+    static float* part_d[64] = {};
+    static int* flag_d[64] = {};
+    static int ctas_d[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return mynah_fail("gemm_tcgen05: no current device");
+    if (ctas_d[dev] < n_ctas) {
+        float* pnew = nullptr;
+        int* fnew = nullptr;
+        cudaError_t e = cudaMalloc(&pnew, (size_t)n_ctas * BM * 256 * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&fnew, (size_t)n_ctas * 4 * sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(fnew, 0, (size_t)n_ctas * 4 * sizeof(int));
+        if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: workspace for %d CTAs: %s", n_ctas, cudaGetErrorString(e));
+        // (an earlier, smaller workspace may still be in use by a captured graph: it is kept)
+        part_d[dev] = pnew; flag_d[dev] = fnew; ctas_d[dev] = n_ctas;
+    }
+    *part = part_d[dev];
+    *flag = flag_d[dev];
+    return 0;
+}
+
+template <int BN, int EPI, int CTAS, int KS = 1, bool SK = false>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
                 int sm_count, int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{}) {
     constexpr int STAGES = ring_stages(BN, CTAS);
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2 / CTAS) + 4 * 2 * STAGING_BYTES + 256 + 1024;
-    auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS, KS>;
+    auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS, KS, SK>;
     static bool opted = false;
     if (!opted) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -491,7 +658,10 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     const long long tiles = (long long)g.m_tiles * g.n_tiles;
     MYNAH_REQUIRE(tiles < (1ll << 30), "gemm_tcgen05: too many tiles");
     const int max_units = sm_count / (CTAS * KS);
-    const int units = (int)(tiles < max_units ? tiles : max_units);
+    const int units = (int)(tiles < max_units && !SK ? tiles : max_units);     // with SK every SM takes its share of the k-blocks
+    g.sk_part = nullptr;
+    g.sk_flag = nullptr;
+    if (SK && sk_workspace(units, &g.sk_part, &g.sk_flag)) return -1;
     MYNAH_REQUIRE(KS == 1 || tiles <= max_units, "gemm_tcgen05: K is split only when every tile has a cluster of its own");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units * CTAS * KS);
@@ -554,6 +724,30 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * (epilogue == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, 256));
     const bool pair = M >= 2 * BM && sm_count >= 2 &&
                       (pair_mode() == 2 || (pair_mode() == 1 && pair_tiles >= 2 * (sm_count / 2)));
+    // The k-blocks of all tiles dealt out evenly (stream-K) where whole tiles would leave SMs idle in their last
+    // wave and the k-blocks saved are worth more than the fix-up. MYNAH_GEMM_SK=0: never, 2: wherever it can run.
+    static const int sk_mode = [] { const char* e = getenv("MYNAH_GEMM_SK"); return e == nullptr ? 1 : (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1)); }();
+    if (epilogue != EPI_SWIGLU && !pair && sk_mode != 0) {
+        const long long tiles_w = (long long)ceil_div(M, BM) * ceil_div(N, 256);
+        const int nk = ceil_div(K, BK);
+        const long long waves = (tiles_w + sm_count - 1) / sm_count;
+        // k-blocks a CTA with whole tiles and with the k-blocks dealt out; a k-block takes about 0.39 us, the fix-up about 3 us
+        const long long kb_whole = waves * nk, kb_dealt = (tiles_w * nk + sm_count - 1) / sm_count;
+        const bool fits = tiles_w >= sm_count && nk >= 8;            // at most two parts a tile
+        // (dealt out, CTAs no longer walk the same k-blocks of neighbouring tiles at the same time, which costs L2
+        // hits: 2,048 x 4,096 x 12,288 got slower with 13% fewer k-blocks a CTA, 2,048 x 2,560 x 9,728 faster with 45%)
+        if (fits && (sk_mode == 2 || ((kb_whole - kb_dealt) * 39 > 600 && (kb_whole - kb_dealt) * 4 >= kb_whole))) {
+            CUtensorMap ma, mb, mc;
+            if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
+            if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, K, 128, BK)) return -1;
+            if (epilogue == EPI_F32) {
+                if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32)) return -1;
+                return launch_gemm<256, EPI_F32, 1, 1, true>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
+            }
+            if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
+            return launch_gemm<256, EPI_BF16, 1, 1, true>(ma, mb, mc, M, N, K, 0, sm_count, status, stream);
+        }
+    }
     // Few tiles even at 256 columns (a narrow N): two CTAs a tile, a half of K each.
     if (epilogue == EPI_BF16 && !pair && mynah_gemm_tcgen05_splits_k(M, N, K, sm_count)) {
         CUtensorMap ma, mb, mc;

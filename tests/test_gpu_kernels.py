@@ -768,6 +768,7 @@ def test_attn_prefill_tensor_cores(H, KV, HD, window, which):
 @pytest.mark.parametrize("M,N,K", [(2048, 4096, 1024), (2048, 1024, 2048), (130, 1000, 96), (17, 264, 64), (128, 128, 8),
                                    (300, 6144, 1024), (1000, 1024, 3072),
                                    (1500, 1096, 2112), (300, 520, 2048), (2048, 1024, 3072),   # few tiles: K in two halves
+                                   (2048, 2560, 2048), (1900, 2600, 2120), (2304, 2304, 1024), # a last wave with idle SMs: k-blocks dealt out
                                    (4900, 2048, 64), (9000, 1096, 96)])    # enough tiles for pairs of CTAs; ragged edges
 def test_gemm_tcgen05(M, N, K):
     """The tensor-memory product against float64, and against the library's product of the same operands."""
