@@ -618,10 +618,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // The stream-K workspace of the current device: a slot of 128 x 256 floats and four flags a CTA, allocated at the
 // first launch that needs it (never during a graph capture: a captured step has run once before).
+// (One workspace a device: stream-K products of one device must not overlap in time, which holds for the
+// single stream that the engine launches on.)
+float* part_d[64] = {};
+int* flag_d[64] = {};
+int ctas_d[64] = {};
+
 int sk_workspace(int n_ctas, float** part, int** flag) {
-    static float* part_d[64] = {};
-    static int* flag_d[64] = {};
-    static int ctas_d[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return mynah_fail("gemm_tcgen05: no current device");
     if (ctas_d[dev] < n_ctas) {
@@ -692,6 +695,16 @@ int pair_mode() {
 }
 
 }  // namespace
+
+// After a launch that gave up on a wait (status bit 16) a stream-K flag may have been left raised: clears them,
+// behind whatever the stream still holds.
+MYNAH_API int mynah_gemm_tcgen05_reset(cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || flag_d[dev] == nullptr) return 0;
+    const cudaError_t e = cudaMemsetAsync(flag_d[dev], 0, (size_t)ctas_d[dev] * 4 * sizeof(int), stream);
+    if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
+    return 0;
+}
 
 MYNAH_API int mynah_gemm_tcgen05_supported(int M, int N, int K) {
     return M >= 1 && N >= 8 && N % 8 == 0 && K >= 8 && K % 8 == 0;      // rows of 16-byte multiples for TMA

@@ -579,6 +579,9 @@ class Engine:
             word.zero_()
             if self.fused is not None:
                 self.fused.reset_after_abort()
+            if st & 16:
+                from ..ops.lib import call, stream_ptr
+                call("mynah_gemm_tcgen05_reset", stream_ptr())       # flags that a product which gave up may have left raised
             what = [name for bit, name in ((kernels.ST_PAGE_RANGE, "a position without a page"),
                                            (kernels.ST_POS_RANGE, "a position outside the rotation table"),
                                            (kernels.ST_TOKEN_RANGE, "a token id outside the vocabulary"),

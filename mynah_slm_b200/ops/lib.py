@@ -75,6 +75,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_gemm_tcgen05": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_argmax": [P, c_int, c_int, c_int, P, P],
     "mynah_set_pdl": [c_int],
+    "mynah_gemm_tcgen05_reset": [P],
     "mynah_sample": [P, c_int, c_int, c_int, P, P, P, P, P, P, P],
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
     "mynah_decode_advance": [P, P, P, P, P, c_int, P],

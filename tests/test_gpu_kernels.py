@@ -793,6 +793,12 @@ def test_gemm_tcgen05(M, N, K):
         assert torch.equal(c16, c32.to(torch.bfloat16))                   # the same accumulator, rounded once
     lib32 = torch.mm(ad, wd.t(), out_dtype=torch.float32)
     assert rel_err(lib32.cpu().numpy(), c32.cpu().numpy()) < 2e-5
+    # the same product again (workspace flags are left clear by every launch, and clearing them by hand is harmless)
+    from mynah_slm_b200.ops import lib as klib
+    klib.call("mynah_gemm_tcgen05_reset", klib.stream_ptr())
+    again = torch.empty_like(c16)
+    gemm_bf16.gemm_tcgen05(ad, wd, N, 0, again)
+    assert torch.equal(again, c16) and gemm_bf16.status_word(torch.device(DEV)).item() == 0
     # through the dispatcher: more rows than one tile take this kernel, fewer the library's
     before = dict(gemm_bf16.counters)
     got = _k().linear(ad, wd)
