@@ -450,7 +450,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, FusedArgs a,
                          float* __restrict__ part_o, float* __restrict__ part_ml, unsigned* __restrict__ counters,
                          bf16* __restrict__ out, int* __restrict__ status) {
-    constexpr int CH = HD / 8, KSTEPS = HD / 16, NT = HD / 32;
+    constexpr int CH = HD / 8, KSTEPS = HD / 16;
     constexpr int QLD = HD + 8;                       // padded row of the query tile: no bank conflicts on its loads
     __shared__ __align__(128) unsigned char k_s[KEYS * HD * 2];     // reused by the merge for the pages' weights
     __shared__ __align__(128) unsigned char v_s[KEYS * HD * 2];     // reused by the merge for its series
@@ -566,99 +566,12 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
                 qa[ks][3] = *reinterpret_cast<const uint32_t*>(q_s + (r0 + 8) * QLD + col + 8);
             }
         }
-        float sc[2][4] = {};
-        {
-            const int mat = lane >> 3, rr = lane & 7;
-            const int key = warp * 16 + (mat >> 1) * 8 + rr;
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ks++) {
-                uint32_t kb[4];
-                ldmatrix_x4(kb, k_base + swz<CH>(key, ks * 2 + (mat & 1)));
-                mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
-                mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
-            }
-        }
-        const int hrow = lane >> 2;
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int t = 0; t < 2; t++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int key = warp * 16 + t * 8 + (lane & 3) * 2 + (e & 1);
-                const bool vis = key >= k_first && key <= k_last;
-                sc[t][e] = vis ? sc[t][e] * a.scale : -INFINITY;
-                mx[e >> 1] = fmaxf(mx[e >> 1], sc[t][e]);
-            }
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 1));
-            mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 2));
-        }
-        if ((lane & 3) == 0) {
-            red_m[warp][hrow] = mx[0];
-            red_m[warp][hrow + 8] = mx[1];
-        }
-        __syncthreads();
-        float m[2], l[2] = {0.f, 0.f};
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int h = hrow + 8 * j;
-            m[j] = fmaxf(fmaxf(red_m[0][h], red_m[1][h]), fmaxf(red_m[2][h], red_m[3][h]));
-        }
-#pragma unroll
-        for (int t = 0; t < 2; t++)
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const float p0 = expf(sc[t][2 * j] - m[j]), p1 = expf(sc[t][2 * j + 1] - m[j]);
-                l[j] += p0 + p1;
-                const int h = hrow + 8 * j, key = warp * 16 + t * 8 + (lane & 3) * 2;
-                *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<unsigned char*>(p_s) + swz<8>(h, key >> 3) + (key & 7) * 2) =
-                    __floats2bfloat162_rn(p0, p1);
-            }
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            l[j] += __shfl_xor_sync(0xffffffffu, l[j], 1);
-            l[j] += __shfl_xor_sync(0xffffffffu, l[j], 2);
-        }
-        if ((lane & 3) == 0) {
-            red_l[warp][hrow] = l[0];
-            red_l[warp][hrow + 8] = l[1];
-        }
-        cp_async_wait<0>();
-        __syncthreads();
-
-        float oc[NT][4] = {};
-        {
-            const uint32_t p_base = smem_u32(p_s);
-            const int mat = lane >> 3, rr = lane & 7;
-#pragma unroll
-            for (int ks = 0; ks < KEYS / 16; ks++) {
-                uint32_t pa[4];
-                ldmatrix_x4(pa, p_base + swz<8>((mat & 1) * 8 + rr, ks * 2 + (mat >> 1)));
-#pragma unroll
-                for (int nt = 0; nt < NT; nt += 2) {
-                    uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, v_base + swz<CH>(ks * 16 + (mat & 1) * 8 + rr, warp * (HD / 32) + nt + (mat >> 1)));
-                    mma_bf16(oc[nt], pa, vb[0], vb[1]);
-                    mma_bf16(oc[nt + 1], pa, vb[2], vb[3]);
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int h = hrow + 8 * j;
-            if (h < G) {
-                float* o = part_o + (row0 + (size_t)h * a.S) * HD;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-                    *reinterpret_cast<float2*>(o + warp * (HD / 4) + nt * 8 + (lane & 3) * 2) = make_float2(oc[nt][2 * j], oc[nt][2 * j + 1]);
-            }
-        }
-        if (tid < G) {
-            part_ml[(row0 + (size_t)tid * a.S) * 2] =
-                fmaxf(fmaxf(red_m[0][tid], red_m[1][tid]), fmaxf(red_m[2][tid], red_m[3][tid]));
-            part_ml[(row0 + (size_t)tid * a.S) * 2 + 1] = (red_l[0][tid] + red_l[1][tid]) + (red_l[2][tid] + red_l[3][tid]);
-        }
+        // the page's partial result: the same code as the pages' kernel (the probabilities go where the queries were)
+        PageJob job;
+        job.s = s; job.g = g; job.b = b; job.page = page;
+        job.k_first = k_first; job.k_last = k_last; job.row0 = row0; job.empty = false;
+        const TcArgs ta{a.H, a.KV, a.ldq, a.window, a.S, a.scale};
+        compute_page<HD, 1, 0>(job, qa, ta, k_base, v_base, p_s, red_m, red_l, part_o, part_ml);
     }
 
     if (!MERGE) return;                               // the merge is a launch of its own (a CTA a head)
