@@ -139,6 +139,10 @@ class _PromptGraph:
     last_use: int = 0
 
 
+# Granularity of the page splits of captured decode steps beyond this many pages (0: powers of two throughout).
+# Measured at 33 pages a sequence: splits of 64 / 48 / 40 give 1.371 / 1.364 / 1.355 ms a step at batch 8 and
+# 3.97 / 3.88 / 3.84 at batch 64; every new size is a capture (a step run twice), so not finer than 16.
+PAGE_BUCKET_STEP = int(os.environ.get("MYNAH_PAGE_BUCKET_STEP", "16"))
 # Decode steps of at most this many rows are captured with programmatic dependent launch (0: none).
 PDL_MAX_ROWS = int(os.environ.get("MYNAH_PDL_MAX_ROWS", "2"))
 
@@ -415,12 +419,20 @@ class Engine:
             b *= 2
         return b
 
+    @classmethod
+    def _pages_bucket(cls, pages: int) -> int:
+        """Page splits of a captured decode step: powers of two up to PAGE_BUCKET_STEP, multiples of it beyond
+        (every split without a page is a CTA that starts only to leave)."""
+        if PAGE_BUCKET_STEP <= 0 or pages <= PAGE_BUCKET_STEP:
+            return cls._bucket(pages)
+        return -(-pages // PAGE_BUCKET_STEP) * PAGE_BUCKET_STEP
+
     def _graph_for(self, B: int, max_kv: int) -> _DecodeGraph:
         """The captured step for this batch size and context: batch sizes and
         page counts are rounded up to powers of two, so a few graphs serve all."""
         bucket = self._bucket(B)
         max_pages_seq = -(-self.spec.max_positions // PAGE_TOKENS)
-        splits = min(max(4, self._bucket(self._decode_pages(max_kv))), max_pages_seq)
+        splits = min(max(4, self._pages_bucket(self._decode_pages(max_kv))), max_pages_seq)
         g = self._graphs.get((bucket, splits))
         if g is not None:
             return g
