@@ -20,9 +20,6 @@ from typing import Iterator, Optional, Sequence
 
 import numpy as np
 
-PAGE_TOKENS = 64
-
-
 class CacheError(RuntimeError):
     pass
 
@@ -38,6 +35,8 @@ def _lib():
         P, I = ctypes.c_void_p, ctypes.c_int
         IP = ctypes.POINTER(ctypes.c_int32)
         lib.mynah_host_last_error.restype = ctypes.c_char_p
+        lib.mynah_page_tokens.restype = I
+        lib.mynah_page_tokens.argtypes = []
         sigs = {
             "mynah_pool_create": (P, [I]), "mynah_pool_destroy": (None, [P]),
             "mynah_pool_take": (I, [P, I, I, IP]), "mynah_pool_give_back": (I, [P, IP, I, I]),
@@ -59,6 +58,10 @@ def _lib():
             fn.restype, fn.argtypes = res, args
         _LIB = lib
     return _LIB
+
+
+# Positions a page holds: defined once, in the native runtime's header, and read from the library.
+PAGE_TOKENS = int(_lib().mynah_page_tokens())
 
 
 def _raise() -> None:

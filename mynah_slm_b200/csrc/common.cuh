@@ -19,6 +19,8 @@ enum MynahDtype : int { MYNAH_F32 = 0, MYNAH_BF16 = 1 };
 int mynah_fail(const char* fmt, ...);
 // Checks the launch that has just been made.
 int mynah_check_launch(const char* what);
+// Multiprocessors of the current device (asked once per device), for launchers whose caller passes none.
+int mynah_sm_count();
 
 #define MYNAH_REQUIRE(cond, ...)                     \
     do {                                             \

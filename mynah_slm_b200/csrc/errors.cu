@@ -34,6 +34,18 @@ MYNAH_API int mynah_device_arch(void) {
     return major * 10 + minor;
 }
 
+int mynah_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // Programmatic dependent launch of the decode-path kernels. Off by default: on this part the decode step
 // measured slower with it (dependents that become resident early take slots from the running kernel).
 static int g_pdl = 0;

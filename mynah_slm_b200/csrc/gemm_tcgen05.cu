@@ -714,7 +714,7 @@ MYNAH_API int mynah_gemm_tcgen05_supported(int M, int N, int K) {
 // the product run whole). MYNAH_GEMM_KSPLIT=0 keeps whole tiles.
 MYNAH_API int mynah_gemm_tcgen05_splits_k(int M, int N, int K, int sm_count) {
     static const bool on = [] { const char* e = getenv("MYNAH_GEMM_KSPLIT"); return !(e != nullptr && e[0] == '0'); }();
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = mynah_sm_count();
     // (the exchange costs about 4 us; a k-block about 0.34 us on a 128-wide tile, 0.39 us on half of a 256-wide one)
     return on && ceil_div(K, BK) >= 32 && (long long)ceil_div(M, BM) * ceil_div(N, 256) <= sm_count / 2;
 }
@@ -731,7 +731,7 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     MYNAH_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0 && (ldc * csize) % 16 == 0,
                   "gemm_tcgen05: operands must be 16-byte aligned and the output pitch a multiple of 16 bytes");
     MYNAH_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = mynah_sm_count();
     // Pairs pay once a unit has tiles to run one after the other (the ring then stays full across tiles); with
     // one tile a unit, as for a 2,048-token prompt of a small model, single CTAs measured the same or better.
     const long long pair_tiles = (long long)ceil_div(M, 2 * BM) * (epilogue == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, 256));
@@ -813,7 +813,7 @@ MYNAH_API int mynah_gemm_qkv_rope(const void* A, const void* W, int M, int H, in
                   ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 && ((uintptr_t)cos_t & 15) == 0 && ((uintptr_t)sin_t & 15) == 0,
                   "gemm_qkv_rope: operands must be 16-byte aligned");
     MYNAH_REQUIRE(status != nullptr, "gemm_qkv_rope: a status word is required");
-    if (sm_count <= 0) sm_count = 148;
+    if (sm_count <= 0) sm_count = mynah_sm_count();
     const int N = (k_cache != nullptr ? H + 2 * KV : H) * HD;
     QkvEpilogue qe;
     qe.H = H; qe.KV = KV; qe.eps = eps; qe.cos_t = cos_t; qe.sin_t = sin_t; qe.n_pos = n_pos;

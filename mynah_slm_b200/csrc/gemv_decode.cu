@@ -282,7 +282,7 @@ MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* 
     a.x_bf16 = (const bf16*)x_bf16; a.x_res = x_res; a.delta = (const bf16*)delta; a.x_res_out = x_res_out;
     a.gain = VecRef{gain, gain_dtype}; a.eps = eps; a.out = out; a.ldo = ldo;
     const int groups = ceil_div(N, 8);
-    const int target = (sm_count > 0 ? sm_count : 148) * 4;          // one group of rows a CTA while that gives at most four CTAs an SM (their registers fill it)
+    const int target = (sm_count > 0 ? sm_count : mynah_sm_count()) * 4;          // one group of rows a CTA while that gives at most four CTAs an SM (their registers fill it)
     a.groups_per_cta = groups <= target ? 1 : ceil_div(groups, target);
     const int n_ctas = ceil_div(groups, a.groups_per_cta);
     const bool norm = x_res != nullptr;

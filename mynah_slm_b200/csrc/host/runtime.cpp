@@ -30,6 +30,8 @@ constexpr int FREE = -1;
 
 }  // namespace
 
+int mynah_page_tokens(void) { return MYNAH_PAGE_TOKENS; }
+
 struct mynah_pool {
     int n_pages;
     std::vector<int32_t> free_stack;   // page 0 is handed out first

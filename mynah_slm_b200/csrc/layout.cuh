@@ -10,8 +10,9 @@
 #pragma once
 
 #include "common.cuh"
+#include "../include/mynah_slm_b200_host.h"      // MYNAH_PAGE_TOKENS: the one definition of a page's size
 
-constexpr int PAGE_TOKENS = 64;
+constexpr int PAGE_TOKENS = MYNAH_PAGE_TOKENS;
 
 // Bits of the status word that kernels set instead of touching memory they
 // were not given. The host reads the word when it fetches a step's results.

@@ -18,7 +18,14 @@
 //     error message, nothing is launched.
 //   * The first call on each device looks the array's device address up
 //     (one cudaGetSymbolAddress, no allocation). Make that first call before
-//     any stream capture begins.
+//     any stream capture begins, and before the process hands the device's
+//     free memory to a pool of its own: with CUDA's lazy module loading the
+//     driver reserves the 16 MiB of the array when this file's code is first
+//     used on a device, which is that first call, and a device with nothing
+//     left makes it fail.
+//   * The address is remembered per device ordinal for the life of the
+//     process. It does not survive a cudaDeviceReset: do not call this entry
+//     point again on a device that has been reset.
 //   * All calls share the one array, and it keeps what the last call left in
 //     it. The kernels write every partial result they later read, so nothing
 //     has to be cleared between calls; but two calls that overlap on the

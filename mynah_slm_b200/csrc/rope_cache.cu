@@ -211,7 +211,7 @@ bool launch_fast(int HD, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, cons
     const int per_pass = 32 / (HD / 8);
     const long long units1 = (long long)a.T * ((heads + per_pass - 1) / per_pass);
     int passes = 1;
-    while (passes < 4 && units1 / passes > 148 * 16) passes *= 2;
+    while (passes < 4 && units1 / passes > (long long)mynah_sm_count() * 16) passes *= 2;
     const int hpw = per_pass * passes;
     const int groups = (heads + hpw - 1) / hpw;
     const unsigned blocks = (unsigned)ceil_div_ll((long long)a.T * groups, WARPS);

@@ -163,7 +163,7 @@ def _prompt_rows_bucket(T: int) -> int:
 class Engine:
     def __init__(self, spec: ModelSpec, checkpoint: Checkpoint, dtype="bfloat16", max_tokens: int = 4096,
                  max_seqs: Optional[int] = None, device="cuda:0", use_graphs: bool = True,
-                 penalty_window: int = 64, fused_decode: bool = False):
+                 penalty_window: int = 64):
         if isinstance(dtype, str):
             if dtype not in DTYPES:
                 raise EngineError(f"dtype {dtype!r} is not one of {sorted(DTYPES)}")
@@ -190,11 +190,6 @@ class Engine:
         self.use_graphs = use_graphs
         # a part that plans on the host (reads ctx.host_*) cannot be replayed from a graph
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.model.parts())
-        # one persistent kernel for the whole decode step, when every layer is the standard block. Off unless
-        # asked for: on this part it measured slower than the separate kernels (a phase plus its grid barrier
-        # costs what a small kernel plus its launch costs, and one CTA per SM hides less latency).
-        from . import fused_decode as _fd
-        self.fused = _fd.plan(self.model, self.cache, self.runtime) if fused_decode else None
         self._staging = _Staging()
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         # prompt steps: a shape is captured the second time it comes; a handful of graphs are kept
@@ -217,7 +212,12 @@ class Engine:
 
     # ----------------------------------------------------------- sequences
     def open_sequence(self) -> int:
-        return self.cache.open()
+        """A free slot for a new sequence. Whatever the slot's last sequence left is gone: its pages were given
+        back when it closed, fixed-size state is zeroed, and the sampler's row (ring of recent tokens, generator)
+        starts empty."""
+        slot = self.cache.open()
+        self.sampler.reset_slot(slot)
+        return slot
 
     def close_sequence(self, slot: int) -> None:
         self.cache.close(slot)
@@ -392,10 +392,7 @@ class Engine:
             self._forward_layers_only(ctx)
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         rows = ctx.want[:len(uniq)]
-        if is_decode and self._fused_ok(B, splits):
-            logits = self.fused.run(ctx)[torch.from_numpy(uniq.astype(np.int64)).to(self.device)]
-        else:
-            logits = self._forward(ctx, rows)
+        logits = self._forward(ctx, rows)
         if len(uniq) != n_want or not np.array_equal(inverse, np.arange(n_want)):
             logits = logits[torch.from_numpy(inverse.astype(np.int64)).to(self.device)]
         return logits
@@ -487,14 +484,8 @@ class Engine:
         lib.add_launches(n_kernels * replays)
         return res
 
-    def _fused_ok(self, rows: int, pages: int) -> bool:
-        return self.fused is not None and rows <= 16 and self.fused.supported(rows, pages)
-
     def _decode_body(self, g: _DecodeGraph, mode: str) -> torch.Tensor:
-        if self._fused_ok(g.bucket, g.splits):
-            logits = self.fused.run(g.ctx)
-        else:
-            logits = self._forward(g.ctx, None)
+        logits = self._forward(g.ctx, None)
         if mode == "plain":
             return logits
         sampled = self.sampler.sample(logits, g.ctx.slots)
@@ -589,8 +580,6 @@ class Engine:
         if st:
             self.runtime.status.zero_()
             word.zero_()
-            if self.fused is not None:
-                self.fused.reset_after_abort()
             if st & 16:
                 from ..ops.lib import call, stream_ptr
                 call("mynah_gemm_tcgen05_reset", stream_ptr())       # flags that a product which gave up may have left raised

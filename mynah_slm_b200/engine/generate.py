@@ -36,7 +36,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Protocol, Sequence
 
-PAGE_TOKENS = 64
+from ..cache.pages import PAGE_TOKENS
 
 
 @dataclass

@@ -19,7 +19,10 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
+/* Positions a page of the cache holds. Defined here and nowhere else: the kernels include this header and
+ * Python asks mynah_page_tokens(). */
 #define MYNAH_PAGE_TOKENS 64
+int mynah_page_tokens(void);
 
 const char* mynah_host_last_error(void);
 

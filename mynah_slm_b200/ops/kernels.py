@@ -15,10 +15,10 @@ from typing import Optional
 
 import torch
 
+from ..cache.pages import PAGE_TOKENS
 from . import lib
 from .lib import KernelError, call, code, ptr, stream_ptr
 
-PAGE_TOKENS = 64
 MAX_HEAD_DIM = 256
 
 ST_PAGE_RANGE, ST_POS_RANGE, ST_TOKEN_RANGE, ST_SPLIT_RANGE = 1, 2, 4, 8

@@ -103,6 +103,13 @@ class SamplerState:
                                        dtype=torch.float32))
         self._params_host = p
 
+    def reset_slot(self, slot: int) -> None:
+        """The state a slot starts with: an empty ring and the generator of stream 0 of seed 0. A caller that
+        wants another stream or the prompt in the ring calls `start_sequences` afterwards."""
+        self.ring_n[slot] = 0
+        self.ring_head[slot] = 0
+        self.rng[slot] = _as_i64(SEED_ZERO)
+
     def start_sequences(self, slots: Sequence[int], states: Sequence[int],
                         prompts: Optional[Sequence[Sequence[int]]] = None, window: Optional[int] = None) -> None:
         """Seed the slots' generators and load their rings with the prompts'
