@@ -52,6 +52,8 @@ def _lib():
             "mynah_step_fill": (I, [P, IP, IP, I, I, I, IP, I, IP, IP, IP, IP, IP, IP]),
             "mynah_decode_prepare": (I, [P, I, IP, IP, I, I, IP, IP, I, I, I, IP]),
             "mynah_books_commit_many": (I, [P, I, IP, I]),
+            "mynah_randn_fill_host": (I, [P, I, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
+                                          ctypes.c_double, ctypes.c_double]),
         }
         for name, (res, args) in sigs.items():
             fn = getattr(lib, name)
@@ -62,6 +64,11 @@ def _lib():
 
 # Positions a page holds: defined once, in the native runtime's header, and read from the library.
 PAGE_TOKENS = int(_lib().mynah_page_tokens())
+
+
+def host_library():
+    """The native host runtime, for the modules that use other parts of it than the cache's books."""
+    return _lib()
 
 
 def _raise() -> None:

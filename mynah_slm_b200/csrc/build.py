@@ -38,7 +38,9 @@ def sources() -> list[str]:
 
 
 def _headers() -> list[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+    inc = os.path.join(os.pardir, "include")
+    return (sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+            + sorted(os.path.join(inc, f) for f in os.listdir(os.path.join(HERE, inc)) if f.endswith(".h")))
 
 
 def _stamp() -> str:
@@ -144,8 +146,10 @@ def _build(out: str, lib: str, verbose: bool) -> None:
 # ---------------------------------------------------------------- the host-side runtime (no CUDA)
 HOST_LIB_NAME = "libmynah_slm_b200_host.so"
 HOST_SOURCES = [os.path.join("host", "runtime.cpp")]
-HOST_HEADERS = [os.path.join(os.pardir, "include", "mynah_slm_b200_host.h")]
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+HOST_HEADERS = [os.path.join(os.pardir, "include", "mynah_slm_b200_host.h"),
+                os.path.join(os.pardir, "include", "mynah_random_normal.h")]
+# -ffp-contract=off: the random-weights arithmetic must round every operation on its own, as the device does
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-ffp-contract=off"]
 
 
 def _find_cxx() -> str:

@@ -32,6 +32,25 @@ constexpr int FREE = -1;
 
 int mynah_page_tokens(void) { return MYNAH_PAGE_TOKENS; }
 
+// ---------------------------------------------------------------- random weights on the host
+// The same numbers as the device's mynah_randn_fill, for writing a model folder where there is no device.
+#include "../../include/mynah_random_normal.h"
+
+int mynah_randn_fill_host(void* out, int dtype, long long n, unsigned long long seed, unsigned long long tensor_key,
+                          double mean, double std) {
+    if (n < 0 || (n > 0 && out == nullptr)) return fail("randn_fill_host: bad size %lld", n);
+    if (dtype != 0 && dtype != 1) return fail("randn_fill_host: unsupported dtype %d (0: float32, 1: bfloat16)", dtype);
+    const uint64_t state = mynah_rn_state(seed, tensor_key);
+    if (dtype == 0) {
+        float* o = static_cast<float*>(out);
+        for (long long i = 0; i < n; i++) o[i] = mynah_rn_value(state, (uint64_t)i, mean, std);
+    } else {
+        uint16_t* o = static_cast<uint16_t*>(out);
+        for (long long i = 0; i < n; i++) o[i] = mynah_rn_bf16_bits(mynah_rn_value(state, (uint64_t)i, mean, std));
+    }
+    return 0;
+}
+
 struct mynah_pool {
     int n_pages;
     std::vector<int32_t> free_stack;   // page 0 is handed out first

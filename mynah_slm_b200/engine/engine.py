@@ -180,7 +180,11 @@ class Engine:
         self.dtype = dtype
         self.model = Model(spec)
         self.runtime = Runtime(self.device, dtype, spec.max_positions)
-        load_into(self.model.tensor_specs(), checkpoint, self.runtime)
+        from ..weights.random_init import RandomWeights, fill_into
+        if isinstance(checkpoint, RandomWeights):
+            fill_into(self.model.tensor_specs(), checkpoint, self.runtime)
+        else:
+            load_into(self.model.tensor_specs(), checkpoint, self.runtime)
         self.n_pages = max(1, -(-int(max_tokens) // PAGE_TOKENS))
         self.max_seqs = int(max_seqs) if max_seqs else min(self.n_pages, 1024)
         self.cache = Cache(self.model.cache_plan(), self.n_pages, self.max_seqs, dtype, self.device)
@@ -209,6 +213,23 @@ class Engine:
             return cls(typed.model_spec(), ckpt, **kw)
         finally:
             ckpt.close()
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype="bfloat16", stored_dtype=None, **kw) -> "Engine":
+        """An engine with random weights made on the device: no file is written or read. `config` is a typed
+        configuration, a config.json dictionary or the path of a config.json; the weights are those that
+        `write_random_model(folder, config, seed, stored_dtype)` writes (stored_dtype: the run's type unless
+        given)."""
+        import json
+        from ..registry import parse_config
+        from ..weights.random_init import RandomWeights
+        if isinstance(config, (str, os.PathLike)):
+            with open(config) as f:
+                config = json.load(f)
+        typed = parse_config(config) if isinstance(config, dict) else config
+        run = DTYPES[dtype] if isinstance(dtype, str) and dtype in DTYPES else dtype
+        stored = run if stored_dtype is None else (DTYPES[stored_dtype] if isinstance(stored_dtype, str) else stored_dtype)
+        return cls(typed.model_spec(), RandomWeights(seed, stored), dtype=dtype, **kw)
 
     # ----------------------------------------------------------- sequences
     def open_sequence(self) -> int:

@@ -26,6 +26,12 @@ int mynah_page_tokens(void);
 
 const char* mynah_host_last_error(void);
 
+/* out[i] = (float)(mean + std * normal(seed, tensor_key, i)), i < n, stored as float32 (dtype 0) or bfloat16
+ * (dtype 1): the random-weights mode on the host. The numbers are those of mynah_random_normal.h, which the
+ * device's mynah_randn_fill evaluates too. */
+int mynah_randn_fill_host(void* out, int dtype, long long n, unsigned long long seed, unsigned long long tensor_key,
+                          double mean, double std);
+
 /* ---- a pool of pages 0..n-1: freed pages are the next handed out; every page knows its owner */
 typedef struct mynah_pool mynah_pool;
 mynah_pool* mynah_pool_create(int n_pages);
