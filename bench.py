@@ -4,6 +4,7 @@ Qwen3-0.6B shape with random weights (batch 8 by default, 2,048-token prompts,
 and 64.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload 4b|8b      (the two larger workloads, a JSON line of their own each)
 
 One JSON line on stdout. A step is one decode step of the batch.
   value     decoded tokens per second, timed on the device with CUDA events
@@ -15,8 +16,19 @@ One JSON line on stdout. A step is one decode step of the batch.
   prefill   one 2,048-token prompt in one step; frac = flops / time / peak
   roofline  bytes a decode step has to read (every weight once, the cache of
             the live requests) / its time, against the HBM peak
+  points    decode at batch 1 and 64 behind the 2,048-token prompts, and all three
+            batch sizes again in the middle and at the end of the range the
+            configuration names (2,048 generated tokens behind the prompt): after
+            untimed steps up to 3,072 and 4,096 positions, 64 timed steps each;
+            point_fracs gives each point's share of the HBM peak for its bytes
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from
-the stated fallback.
+the stated fallback. The weights are made on the device from the seed; no file is
+written.
+
+--workload 4b: 16 prompts of lengths uniform in [16, 2048], 256 generated tokens
+each, greedy and at temperature 0.7, at the Qwen3-4B layer sizes, through
+LLM.generate. --workload 8b: 64 prompts of 2,048 tokens and 2,048 generated tokens
+each at the Qwen3-8B layer sizes (bf16 cache of 38.65 GB), through LLM.generate.
 """
 from __future__ import annotations
 
@@ -47,6 +59,7 @@ SHAPES = {
                tie_word_embeddings=False),
 }
 PROMPT_LEN, CTX_LEN, PREFILL_TOKENS = 2048, 4096, 2048
+FAR_STEPS = 64            # timed steps of the points in the middle and at the end of the context range
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -129,6 +142,57 @@ def decode_bytes(c: dict, layers: int, batch: int, ctx: float) -> float:
     return layers * per_layer + head + 2 * D + kv
 
 
+def run_workload(which: str, layers_override: int = 0) -> int:
+    """The two larger workloads, end to end through LLM.generate (host token ids in and out every step)."""
+    import numpy as np
+    import torch
+
+    from mynah_slm_b200 import LLM
+
+    cfg = dict(QWEN3_0_6B)
+    cfg.update(SHAPES[which])
+    layers_model = cfg["num_hidden_layers"]
+    layers = layers_override or layers_model
+    cfg["num_hidden_layers"] = layers
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(3 if which == "4b" else 4)
+    V = cfg["vocab_size"]
+    if which == "4b":
+        lens = rng.integers(16, 2049, size=16).tolist()
+        n_new, runs = 256, [("greedy", 0.0), ("temp_0.7", 0.7)]
+        max_tokens = sum(-(-(n + n_new) // 64) * 64 for n in lens)
+    else:
+        lens = [PROMPT_LEN] * 64
+        n_new, runs = CTX_LEN - PROMPT_LEN, [("greedy", 0.0)]
+        max_tokens = 64 * CTX_LEN
+    prompts = [rng.integers(0, V, size=n).tolist() for n in lens]
+    llm = LLM.random(cfg, seed=3 if which == "4b" else 4, dtype="bfloat16", max_tokens=max_tokens, max_seqs=len(lens))
+    llm.generate([p[:64] for p in prompts], max_new=4, temp=0.0, ignore_eos=True, max_batch=len(lens))    # warm-up
+    out = {"workload": which, "model": f"Qwen3-{which.upper()} shape", "layers": layers, "layers_of_model": layers_model,
+           "batch": len(lens), "prompt_tokens": int(sum(lens)), "new_tokens_each": n_new, "dtype": "bf16",
+           "data": f"synthetic: random weights (seed {3 if which == '4b' else 4}), uniform random token ids",
+           "cache_gb": round(max_tokens * layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2 / 1e9, 2),
+           "peaks": f"{pk_src}: {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s", "runs": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, temp in runs:
+        res = llm.generate(prompts, max_new=n_new, temp=temp, top_k=0, top_p=1.0, seed=1, ignore_eos=True, max_batch=len(lens))
+        t = llm.last_timing
+        assert all(len(r.tokens) == n_new for r in res)
+        steps = n_new - 1                                   # the first token of each request comes from the prompt step
+        mean_ctx = sum(lens) / len(lens) + n_new / 2.0
+        step_s = t.decode_s / steps
+        gbs = decode_bytes(cfg, layers, len(lens), mean_ctx) / step_s / 1e9
+        flops = sum(model_flops_prefill(cfg, n, layers) for n in lens)
+        out["runs"][name] = {"decode_tokens_per_s": round(len(lens) * steps / t.decode_s, 1), "ms_per_step": round(step_s * 1e3, 3),
+                             "GBps": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 4),
+                             "prefill_tokens_per_s": round(sum(lens) / t.prefill_s, 1), "prefill_ms": round(t.prefill_s * 1e3, 1),
+                             "prefill_frac": round(flops / t.prefill_s / (pk["bf16_tflops"] * 1e12), 4)}
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,6 +206,7 @@ def main() -> int:
                     help="run one small phase and print a short line (for profiling a kernel on a small case)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
+    ap.add_argument("--workload", default="", choices=["", "4b", "8b"], help="run one of the two larger workloads instead")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -163,7 +228,9 @@ def main() -> int:
     from mynah_slm_b200.engine.engine import StepEntry
     from mynah_slm_b200.ops import gemm_bf16, lib
     from mynah_slm_b200.sampling.sampler import SamplingParams
-    from mynah_slm_b200.weights.random_init import write_random_model
+
+    if args.workload:
+        return run_workload(args.workload, args.layers)
 
     cfg = dict(QWEN3_0_6B)
     if args.only:
@@ -178,15 +245,14 @@ def main() -> int:
     rng = np.random.default_rng(2)
     V = cfg["vocab_size"]
 
-    with tempfile.TemporaryDirectory() as tmp:
-        folder = write_random_model(os.path.join(tmp, "qwen3_0_6b_random"), parse_config(cfg), seed=2,
-                                    dtype=torch.bfloat16)
-        llm = LLM(folder, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
+    llm = LLM.random(cfg, seed=2, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
     eng = llm.engine
     eng.sampler.set_params(SamplingParams.greedy())
 
-    def device_decode(batch: int, steps: int, warmup: int):
-        """Prompts of PROMPT_LEN, then `warmup` untimed and `steps` timed decode steps on the device."""
+    def device_decode(batch: int, steps: int, warmup: int, far: tuple = ()):
+        """Prompts of PROMPT_LEN, then `warmup` untimed and `steps` timed decode steps on the device. For every
+        length in `far` the sequences then go on untimed until FAR_STEPS steps before that length and those
+        steps are timed: far_ms[length] = (ms, mean context)."""
         prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(batch)]
         slots = [eng.open_sequence() for _ in range(batch)]
         eng.sampler.start_sequences(slots, list(range(1, batch + 1)), prompts)
@@ -198,16 +264,34 @@ def main() -> int:
         n0 = lib.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        eng.decode_loop(slots, toks, steps)
+        last = eng.decode_loop(slots, toks, steps)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
         launches = lib.launch_count() - n0
         eng.check_status()
+        mean_ctx = prompt_len + 1 + warmup + steps / 2.0
+        far_ms = {}
+        length = prompt_len + warmup + steps
+        for target in far:
+            gap = target - FAR_STEPS - length
+            if gap < 0:
+                continue
+            if gap:
+                last = eng.decode_loop(slots, last[:batch].cpu().tolist(), gap)
+            toks = last[:batch].cpu().tolist()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            last = eng.decode_loop(slots, toks, FAR_STEPS)
+            e1.record()
+            torch.cuda.synchronize()
+            far_ms[target] = (e0.elapsed_time(e1), target - FAR_STEPS / 2.0 + 0.5)
+            length = target
+            eng.check_status()
         for s in slots:
             eng.close_sequence(s)
-        mean_ctx = prompt_len + 1 + warmup + steps / 2.0
-        return ms, launches, mean_ctx
+        return ms, launches, mean_ctx, far_ms
 
     def time_prefill(n_timed: int = 5):
         p = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
@@ -226,7 +310,7 @@ def main() -> int:
         return statistics.median(times)
 
     if args.only == "decode":
-        ms, launches, mean_ctx = device_decode(B, K, W)
+        ms, launches, mean_ctx, _ = device_decode(B, K, W)
         gbs = decode_bytes(cfg, layers, B, mean_ctx) / (ms / K / 1e3) / 1e9
         print(json.dumps({"only": "decode", "shape": args.shape, "batch": B, "layers": layers, "prompt_len": prompt_len, "steps": K,
                           "ms_per_step": round(ms / K, 4), "tokens_per_s": round(B * K / (ms / 1e3), 1),
@@ -242,7 +326,8 @@ def main() -> int:
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, mean_ctx = device_decode(B, K, W)
+    far = () if (args.no_points or prompt_len + W + K + FAR_STEPS > 3072) else (3072, CTX_LEN)
+    ms, launches, mean_ctx, far_ms = device_decode(B, K, W, far)
     clock_info = clocks.stop()
     value = B * K / (ms / 1e3)
     bytes_step = decode_bytes(cfg, layers, B, mean_ctx)
@@ -265,11 +350,21 @@ def main() -> int:
     prefill = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
                "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
-    points = {}
+    points, point_fracs = {}, {}
+
+    def add_far(b: int, far_ms: dict) -> None:
+        for target, (fms, fctx) in far_ms.items():
+            name = f"decode_b{b}_ctx{target if target != CTX_LEN else CTX_LEN - 1}"
+            points[name] = round(b * FAR_STEPS / (fms / 1e3), 1)
+            point_fracs[name] = round(decode_bytes(cfg, layers, b, fctx) / (fms / FAR_STEPS / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    add_far(B, far_ms)
     if not args.no_points:
         for b, steps in ((1, max(64, K)), (64, min(K, 64))):
-            pms, _, _ = device_decode(b, steps, W)
+            pms, _, pctx, pfar = device_decode(b, steps, W, far)
             points[f"decode_b{b}"] = round(b * steps / (pms / 1e3), 1)
+            point_fracs[f"decode_b{b}"] = round(decode_bytes(cfg, layers, b, pctx) / (pms / steps / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            add_far(b, pfar)
 
     out = {
         "metric": "decode tok/s at batch 8, 2,048-token prompts, 4,096 context (Qwen3-0.6B shape)",
@@ -288,7 +383,7 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clock_info,
+        "points": points, "point_fracs": point_fracs, "clocks": clock_info,
         "matmul_calls": dict(gemm_bf16.counters),
     }
     print(json.dumps(out))

@@ -1,9 +1,10 @@
 """Command line in the manner of the reference's `mynah-slm run`
 (mynah-slm cli/main.c:22-46, :317-365).
 
-    mynah-slm run -m <model folder> --tokens 1,2,3 [-n 128] [--temp T] [--top-k K]
-                  [--top-p P] [--min-p M] [--seed S] [--repeat-penalty R]
-                  [--no-stream] [--quiet] [--ctx N]
+    mynah-slm run (-m <model folder> | --random <config.json> [--weights-seed S]) --tokens 1,2,3
+                  [-n 128] [--temp T] [--top-k K] [--top-p P] [--min-p M] [--seed S] [--repeat-penalty R]
+                  [--no-stream] [--quiet] [--ctx N] [--dtype bfloat16|float32] [--batch B] [--ignore-eos]
+                  [--logits-out <file.npy>]
     mynah-slm random -o <folder> --config <config.json> [--seed S] [--dtype bfloat16|float32]
     mynah-slm --version
 
@@ -16,6 +17,13 @@ counterpart: prompts are token ids, given with --tokens (repeatable: several
 prompts make a batch) or --tokens-file (one prompt per line). Generated ids
 go to stdout, one line per prompt; the timing line goes to stderr
 (src/timing.c:56-62), so stdout stays pipeable.
+
+--random <config.json> runs a model whose weights are made on the device from
+the configuration and a seed (--weights-seed, else --seed), without a folder.
+--logits-out <file.npy> first runs every prompt whole, one after another, and
+writes the fp32 logits of all their positions as one array [positions, vocab]
+in the .npy format of the reference's parity tool (tests/test_parity.c:140-146,
+tests/npy.c:17-48: version 1.0, '<f4').
 """
 from __future__ import annotations
 
@@ -36,16 +44,31 @@ def _parse_ids(text: str) -> list[int]:
     return [int(t) for t in text.replace(",", " ").split()]
 
 
+def _write_logits(llm, prompts: list[list[int]], path: str) -> None:
+    """Every prompt whole in a step of its own; the logits of all positions, in the order of the prompts."""
+    import numpy as np
+    from .engine.engine import StepEntry
+    rows = []
+    for p in prompts:
+        slot = llm.engine.open_sequence()
+        rows.append(llm.engine.step([StepEntry(slot, p, range(len(p)))]).cpu().numpy())
+        llm.engine.check_status()
+        llm.engine.close_sequence(slot)
+    with open(path, "wb") as f:
+        np.lib.format.write_array(f, np.ascontiguousarray(np.concatenate(rows), dtype="<f4"), version=(1, 0))
+
+
 def cmd_run(argv: list[str]) -> int:
     o = {"model": None, "max_new": 128, "ctx": 0, "temp": 0.6, "top_k": 20, "top_p": 0.95, "min_p": 0.0, "seed": 0,
          "repeat_penalty": 1.0, "stream": True, "quiet": False, "dtype": "bfloat16", "ignore_eos": False,
-         "batch": 64, "device": "cuda:0"}
+         "batch": 64, "device": "cuda:0", "random": None, "weights_seed": None, "logits_out": None}
     prompts: list[list[int]] = []
     i = 0
     valued = {"-m": ("model", str), "-n": ("max_new", int), "--ctx": ("ctx", int), "--temp": ("temp", float),
               "--top-k": ("top_k", int), "--top-p": ("top_p", float), "--min-p": ("min_p", float),
               "--seed": ("seed", int), "--repeat-penalty": ("repeat_penalty", float), "--dtype": ("dtype", str),
-              "--batch": ("batch", int), "--device": ("device", str)}
+              "--batch": ("batch", int), "--device": ("device", str), "--random": ("random", str),
+              "--weights-seed": ("weights_seed", int), "--logits-out": ("logits_out", str)}
     while i < len(argv):
         a = argv[i]
         if a in valued or a in ("--tokens", "--tokens-file"):
@@ -75,8 +98,9 @@ def cmd_run(argv: list[str]) -> int:
             i += 1
         else:
             return _fail(f"unknown option '{a}'")
-    if not o["model"] or not prompts:
-        return _fail("run needs -m <model folder> and --tokens <ids> (or --tokens-file <file>)")
+    if bool(o["model"]) == bool(o["random"]) or not prompts:
+        return _fail("run needs -m <model folder> or --random <config.json> (one of them), and --tokens <ids> "
+                     "(or --tokens-file <file>)")
     if any(not p for p in prompts):
         return _fail("empty prompt")
 
@@ -85,7 +109,14 @@ def cmd_run(argv: list[str]) -> int:
     per_seq = o["ctx"] if o["ctx"] > 0 else longest + o["max_new"] + 8       # cli/main.c:264-265
     per_seq = -(-per_seq // 64) * 64
     try:
-        llm = LLM(o["model"], dtype=o["dtype"], max_tokens=per_seq * min(len(prompts), o["batch"]), device=o["device"])
+        max_tokens = per_seq * min(len(prompts), o["batch"])
+        if o["random"]:
+            wseed = o["seed"] if o["weights_seed"] is None else o["weights_seed"]
+            llm = LLM.random(o["random"], seed=wseed, dtype=o["dtype"], max_tokens=max_tokens, device=o["device"])
+        else:
+            llm = LLM(o["model"], dtype=o["dtype"], max_tokens=max_tokens, device=o["device"])
+        if o["logits_out"]:
+            _write_logits(llm, prompts, o["logits_out"])
     except Exception as e:                                                    # noqa: BLE001 - report, as the reference does
         print(f"mynah-slm: {e}", file=sys.stderr)
         return 1

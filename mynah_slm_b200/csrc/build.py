@@ -149,7 +149,7 @@ HOST_SOURCES = [os.path.join("host", "runtime.cpp")]
 HOST_HEADERS = [os.path.join(os.pardir, "include", "mynah_slm_b200_host.h"),
                 os.path.join(os.pardir, "include", "mynah_random_normal.h")]
 # -ffp-contract=off: the random-weights arithmetic must round every operation on its own, as the device does
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-ffp-contract=off"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-ffp-contract=off", "-pthread"]
 
 
 def _find_cxx() -> str:

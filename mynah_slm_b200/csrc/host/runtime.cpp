@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <map>
 #include <new>
+#include <thread>
 #include <vector>
 
 namespace {
@@ -41,12 +42,25 @@ int mynah_randn_fill_host(void* out, int dtype, long long n, unsigned long long 
     if (n < 0 || (n > 0 && out == nullptr)) return fail("randn_fill_host: bad size %lld", n);
     if (dtype != 0 && dtype != 1) return fail("randn_fill_host: unsupported dtype %d (0: float32, 1: bfloat16)", dtype);
     const uint64_t state = mynah_rn_state(seed, tensor_key);
-    if (dtype == 0) {
-        float* o = static_cast<float*>(out);
-        for (long long i = 0; i < n; i++) o[i] = mynah_rn_value(state, (uint64_t)i, mean, std);
+    auto fill = [=](long long lo, long long hi) {
+        if (dtype == 0) {
+            float* o = static_cast<float*>(out);
+            for (long long i = lo; i < hi; i++) o[i] = mynah_rn_value(state, (uint64_t)i, mean, std);
+        } else {
+            uint16_t* o = static_cast<uint16_t*>(out);
+            for (long long i = lo; i < hi; i++) o[i] = mynah_rn_bf16_bits(mynah_rn_value(state, (uint64_t)i, mean, std));
+        }
+    };
+    // every element stands alone, so large tensors are shared out among threads
+    const unsigned hw = std::thread::hardware_concurrency();
+    const int n_threads = n < (1 << 20) ? 1 : (int)std::min<long long>(std::max(1u, std::min(hw, 32u)), n >> 18);
+    if (n_threads <= 1) {
+        fill(0, n);
     } else {
-        uint16_t* o = static_cast<uint16_t*>(out);
-        for (long long i = 0; i < n; i++) o[i] = mynah_rn_bf16_bits(mynah_rn_value(state, (uint64_t)i, mean, std));
+        std::vector<std::thread> pool;
+        const long long per = (n + n_threads - 1) / n_threads;
+        for (int t = 0; t < n_threads; t++) pool.emplace_back(fill, std::min(n, t * per), std::min(n, (t + 1) * per));
+        for (auto& th : pool) th.join();
     }
     return 0;
 }

@@ -97,6 +97,20 @@ class LLM:
         self.load_s = time.perf_counter() - t0
         self.last_timing: Optional[Timing] = None
 
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 65536,
+               max_seqs: Optional[int] = None, device: str = "cuda:0", use_graphs: bool = True) -> "LLM":
+        """A model with random weights made on the device from `config` (a typed configuration, a config.json
+        dictionary or the path of one) and `seed`; no file is written or read."""
+        t0 = time.perf_counter()
+        self = cls.__new__(cls)
+        self.engine = Engine.random(config, seed=seed, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs,
+                                    device=device, use_graphs=use_graphs)
+        torch.cuda.synchronize()
+        self.load_s = time.perf_counter() - t0
+        self.last_timing = None
+        return self
+
     @property
     def eos_token_ids(self) -> tuple[int, ...]:
         return self.engine.spec.eos_token_ids

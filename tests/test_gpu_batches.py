@@ -165,3 +165,25 @@ def test_a_further_piece_of_a_prompt_from_a_replayed_graph(tmp_path, name):
             eng.close_sequence(s)
         assert n_before == (1 if rnd >= 2 else 0), f"round {rnd}: {n_before} captured prompt steps before it"
     assert len(eng._prompt_graphs) == 1, "the five steps did not share one padded shape"
+
+
+def test_layers_of_the_8b_shape(tmp_path):
+    """Two layers with the layer sizes of the largest workload (width 4,096, 32 query heads over 8 kv heads of
+    128, feed-forward 12,288, a head of its own): prompts of unequal lengths in one step, then decode steps, against
+    the plain implementation."""
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=4096,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=2056,
+               rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+               hidden_act="silu", attention_bias=False, rope_scaling=None, use_sliding_window=False, sliding_window=None,
+               max_window_layers=2, eos_token_id=1)
+    folder = make_folder(tmp_path, "shape8b", torch.bfloat16, config=cfg, seed=8)
+    plain = PlainQwen3.from_folder(folder)
+    rng = np.random.default_rng(8)
+    prompt_lens, n_decode = [300, 1, 150, 70, 129], [4, 4, 2, 4, 1]
+    seqs = [rng.integers(0, cfg["vocab_size"], size=p + d).tolist() for p, d in zip(prompt_lens, n_decode)]
+    need = sum(-(-(p + d) // 64) * 64 for p, d in zip(prompt_lens, n_decode))
+    eng = _engine(folder, "bfloat16", need)
+    _, places, got = run_batch(eng, seqs, prompt_lens, n_decode, lambda p: sorted({0, p // 2, p - 1}))
+    for i, q in enumerate(seqs):
+        assert_close(plain.forward(q)[places[i]], got[i], BF16_REL, f"request {i} (prompt {prompt_lens[i]}, decoded {n_decode[i]})")
+    assert eng.free_tokens() == eng.n_pages * 64, "pages were lost"

@@ -472,6 +472,20 @@ def test_command_line(folders, tmp_path):
     q = subprocess.run(cli + ["run", "-m", folder, "--tokens", "5,17,3", "-n", "6", "--temp", "0", "--dtype", "float32",
                               "--ignore-eos", "--quiet"], capture_output=True, text=True, timeout=600)
     assert q.returncode == 0 and q.stdout.split() == lines[0] and "prefill" not in q.stderr
+    # a model made from a configuration and a seed, with no folder; and the prompts' logits written beside
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TINY["A"]))
+    npy = tmp_path / "logits.npy"
+    r = subprocess.run(cli + ["run", "--random", str(cfg_path), "--weights-seed", "0", "--tokens", "5,17,3", "--tokens", "9",
+                              "-n", "6", "--temp", "0", "--dtype", "float32", "--ignore-eos", "--quiet",
+                              "--logits-out", str(npy)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l.split() for l in r.stdout.strip().splitlines()] == lines      # the folder was written from seed 0 too
+    from plain.model import PlainQwen3
+    plain = PlainQwen3.from_folder(folder)
+    assert_close(np.concatenate([plain.forward([5, 17, 3]), plain.forward([9])]), np.load(npy), FP32_REL, "--logits-out")
+    both = subprocess.run(cli + ["run", "-m", folder, "--random", str(cfg_path), "--tokens", "1"], capture_output=True, text=True)
+    assert both.returncode == 2 and "one of them" in both.stderr
     bad = subprocess.run(cli + ["run", "-m", folder, "--bogus"], capture_output=True, text=True)
     assert bad.returncode == 2 and "unknown option '--bogus'" in bad.stderr
     assert subprocess.run(cli + ["--version"], capture_output=True, text=True).stdout.strip()
