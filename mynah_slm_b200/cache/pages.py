@@ -161,6 +161,7 @@ class GroupPlan:
     head_dim: int
     window: Optional[int]          # None: every position is kept
     entries: list[int] = field(default_factory=list)    # schedule indices stored here
+    v_head_dim: Optional[int] = None                     # width of the values; None: head_dim; 0: keys only
 
 
 class _Lengths:

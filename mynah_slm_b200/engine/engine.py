@@ -291,27 +291,44 @@ class Engine:
             [e.want for e in entries] if with_want else None)
 
     # ------------------------------------------------------------- forward
-    def _forward(self, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
+    def _forward(self, ctx: StepContext, want_rows: Optional[torch.Tensor], taps: Optional[dict] = None) -> torch.Tensor:
         """embedding -> layers in schedule order -> final norm of the wanted
-        rows -> head. Returns fp32 logits [rows, vocab]."""
+        rows -> head. Returns fp32 logits [rows, vocab]. `taps`, a dictionary,
+        receives copies of the residual stream on the way (see `step`)."""
         x = self.model.embedding.forward(ctx.tokens)
         stream = Residual(x)
+        if taps is not None:
+            taps["embed"] = x.clone()
         views = self.cache.views
         for i, e in enumerate(self.model.schedule):
             self.model.layers[e.layer].forward(stream, ctx, views[i])
-        h = self.model.final_norm.apply(stream, rows=want_rows, lazy=want_rows is None)
+            if taps is not None:
+                taps[f"layer{i}"] = stream.flush().clone()
+        h = self.model.final_norm.apply(stream, rows=want_rows, lazy=want_rows is None and taps is None)
+        if taps is not None:
+            taps["final_norm"] = h.float()
         return self.model.head.forward(h)
 
     # ---------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], taps: Optional[dict] = None) -> torch.Tensor:
         """Run the tokens of `entries` and return fp32 logits [n_want, vocab]
-        (device), in the order of the entries and of their `want`."""
+        (device), in the order of the entries and of their `want`.
+
+        `taps`, when a dictionary is given, is filled with fp32 copies (device) of the step's intermediate
+        results, the debugging taps of the reference (mynah-slm src/arch_qwen3.h:15-18, 46-49: on_embed,
+        on_layer, on_final): "embed" [T, hidden], "layer<i>" [T, hidden] for run i of the schedule (the residual
+        stream behind it), "final_norm" [wanted rows, hidden] (each wanted row once, ascending). Such a step
+        runs kernel by kernel, not from a captured graph, and needs at least one wanted place."""
         self._validate(entries)
+        if taps is not None and not any(len(e.want) for e in entries):
+            raise EngineError("a step with taps needs at least one wanted place")
         pages = self.cache.pages
         for e in entries:
             pages.reserve(e.slot, len(e.tokens))
         is_decode = all(len(e.tokens) == 1 for e in entries)
-        if is_decode and self.use_graphs and self.graph_safe:
+        if taps is not None:
+            out = self._eager_step(entries, is_decode, taps)
+        elif is_decode and self.use_graphs and self.graph_safe:
             logits = self._decode_graph_step(entries, "plain")
             rows = [b for b, e in enumerate(entries) for _ in e.want]
             if rows == list(range(len(entries))):
@@ -388,7 +405,7 @@ class Engine:
             return logits[:n_want].clone()                    # the graph's output buffer is reused by the next replay
         return logits[torch.from_numpy(inverse.astype(np.int64)).to(self.device)]
 
-    def _eager_step(self, entries: Sequence[StepEntry], is_decode: bool) -> torch.Tensor:
+    def _eager_step(self, entries: Sequence[StepEntry], is_decode: bool, taps: Optional[dict] = None) -> torch.Tensor:
         B = len(entries)
         T = sum(len(e.tokens) for e in entries)
         wants = [(b, int(w)) for b, e in enumerate(entries) for w in e.want]
@@ -413,7 +430,7 @@ class Engine:
             self._forward_layers_only(ctx)
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         rows = ctx.want[:len(uniq)]
-        logits = self._forward(ctx, rows)
+        logits = self._forward(ctx, rows, taps)
         if len(uniq) != n_want or not np.array_equal(inverse, np.arange(n_want)):
             logits = logits[torch.from_numpy(inverse.astype(np.int64)).to(self.device)]
         return logits

@@ -15,7 +15,7 @@ import torch
 from ..cache.pages import GroupPlan
 from ..config.keys import ConfigError
 from ..config.spec import ModelSpec
-from ..parts import LinearHead, TokenEmbedding, build_part
+from ..parts import build_part
 from ..parts.base import Block, KVRequest, Part, StateRequest, TensorSpec
 
 
@@ -38,9 +38,9 @@ class Model:
     def __init__(self, spec: ModelSpec):
         spec.validate()
         self.spec = spec
-        self.embedding = TokenEmbedding(spec.embedding)
+        self.embedding = build_part("embedding", spec.embedding)
         self.final_norm = build_part("norm", spec.final_norm)
-        self.head = LinearHead(spec.head, self.embedding)
+        self.head = build_part("head", spec.head, self.embedding)
         self.layers: list[Block] = []
         for ls in spec.layers:
             mixer = build_part("mixer", ls.mixer)
@@ -77,15 +77,15 @@ class Model:
                 continue
             ep = EntryPlan(state=st)
             if kv is not None:
-                key = (kv.kv_heads, kv.head_dim, kv.window)
+                key = (kv.kv_heads, kv.head_dim, kv.window, kv.value_dim)
                 if key not in keys:
                     keys[key] = len(plan.groups)
-                    plan.groups.append(GroupPlan(kv.kv_heads, kv.head_dim, kv.window))
+                    plan.groups.append(GroupPlan(kv.kv_heads, kv.head_dim, kv.window, v_head_dim=kv.value_dim))
                 g = keys[key]
                 ep.group, ep.index_in_group = g, len(plan.groups[g].entries)
                 plan.groups[g].entries.append(i)
             plan.entries.append(ep)
         if not plan.groups:
             # the page lists double as the record of each sequence's length
-            plan.groups.append(GroupPlan(0, 0, None))
+            plan.groups.append(GroupPlan(0, 0, None, v_head_dim=0))
         return plan

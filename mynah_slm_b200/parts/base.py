@@ -1,7 +1,7 @@
 """Interfaces of the parts a layer is put together from, and their registries.
 
 A part is built from a `PartSpec` (its kind and its sizes and constants) and
-knows nothing of the model it sits in. Five families:
+knows nothing of the model it sits in. Seven families:
 
   mixer       mixes information along the sequence (attention here); may ask
               for key/value storage and for fixed-size per-sequence state
@@ -10,6 +10,9 @@ knows nothing of the model it sits in. Five families:
   position    position encoding that a mixer applies to its queries and keys
   block       the arrangement of norms, mixer and feed-forward around the
               residual stream
+  embedding   token ids -> the first residual stream (fp32 rows)
+  head        normalised rows -> fp32 logits; is handed the model's embedding
+              part, whose matrix it may share
 
 Each family has a registry from `kind` to a class; `register_*` adds to it,
 from inside this package or from outside. The engine only ever talks to
@@ -55,11 +58,21 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values per position: kv_heads x head_dim each. window=None
-    keeps every position; window=W keeps the last W."""
+    """What a mixer keeps per position: keys of kv_heads x head_dim and, unless
+    `values` is False, values of kv_heads x v_head_dim (head_dim when None). A
+    mixer that keeps one vector per position (a latent that serves as key and
+    value) asks for values=False. window=None keeps every position; window=W
+    keeps the last W. Runs that ask for the same thing share a storage group
+    and its page lists."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    values: bool = True
+
+    @property
+    def value_dim(self) -> int:
+        return 0 if not self.values else (self.head_dim if self.v_head_dim is None else self.v_head_dim)
 
 
 @dataclass(frozen=True)
@@ -74,9 +87,15 @@ class CacheView:
     """What one run of a layer sees of the cache.
 
     group: id of the storage group whose page lists apply (ctx.pages[group]).
-    k, v: this entry's storage [n_pages, kv_heads, 64, head_dim], or None.
+    k: this entry's keys [n_pages, kv_heads, 64, head_dim], or None.
+    v: its values [n_pages, kv_heads, 64, v_head_dim], or None (also when the
+       mixer asked for no values).
     writes: False when this run reads the cache another run wrote.
-    state: [max_seqs, *shape] fixed-size state of this entry, or None.
+    state: [max_seqs + 1, *shape] fixed-size state of this entry, or None. Row
+       `slot` belongs to the sequence in that slot; the last row belongs to no
+       sequence: rows of a step that are padding (slot -1) may read and write
+       it, so that a part can index with `where(slots >= 0, slots, max_seqs)`
+       on the device and run from a captured graph.
     """
     group: Optional[int] = None
     k: Optional[torch.Tensor] = None
@@ -143,6 +162,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens: int32 [T] -> the first residual stream, fp32 [T, hidden]."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Built as Head(spec, embedding): the model's embedding part comes along, for a head that shares its matrix."""
+
+    def forward(self, h) -> torch.Tensor:
+        """h: the final norm's rows (or its unrun handle, see Norm.apply) -> fp32 logits [rows, vocab]."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """Arrangement of a layer's parts around the residual stream."""
 
@@ -182,7 +215,7 @@ class Residual:
 # -------------------------------------------------------------- registries
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
 }
 
 
@@ -211,6 +244,14 @@ def register_position(kind: str, cls, replace: bool = False) -> None:
 
 def register_block(kind: str, cls, replace: bool = False) -> None:
     _register("block", kind, cls, replace)
+
+
+def register_embedding(kind: str, cls, replace: bool = False) -> None:
+    _register("embedding", kind, cls, replace)
+
+
+def register_head(kind: str, cls, replace: bool = False) -> None:
+    _register("head", kind, cls, replace)
 
 
 def build_part(family: str, spec: PartSpec, *args, **kwargs) -> Part:

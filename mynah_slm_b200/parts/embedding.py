@@ -14,10 +14,10 @@ from typing import Mapping, Optional
 import torch
 
 from ..ops import kernels
-from .base import Part, TensorSpec
+from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     def __init__(self, spec):
         super().__init__(spec)
         self.name = str(spec["name"])
@@ -34,8 +34,8 @@ class TokenEmbedding(Part):
         return kernels.embed_gather(self.table, tokens)
 
 
-class LinearHead(Part):
-    def __init__(self, spec, embedding: TokenEmbedding):
+class LinearHead(Head):
+    def __init__(self, spec, embedding):
         super().__init__(spec)
         self.tied = bool(spec["tied"])
         self.name = str(spec["name"])
@@ -48,7 +48,14 @@ class LinearHead(Part):
         return [TensorSpec(self.name, (self.V, self.D), ignorable=self.tied)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor], runtime) -> None:
+        if self.tied and getattr(self.embedding, "table", None) is None:
+            from ..config.keys import ConfigError
+            raise ConfigError("linear_head: a tied head needs an embedding part that keeps its matrix as `table`")
         self.weight = self.embedding.table if self.tied else tensors[self.name]
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return kernels.linear(h, self.weight, out_dtype=torch.float32)
+
+
+register_embedding("token_embedding", TokenEmbedding)
+register_head("linear_head", LinearHead)

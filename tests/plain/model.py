@@ -62,6 +62,14 @@ def read_folder(folder: str):
 
 # --------------------------------------------------------------------- parts
 
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float32 -> the nearest bfloat16 (ties to even) -> float32: what a value is after the bfloat16 engine has
+    stored it (third_party/ingot/src/dtype.c:276-284 rounds the same way)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    u = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
+    return u.view(np.float32)
+
+
 def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
     """out = x * (1/sqrt(mean(x^2)+eps)) * w over the last axis; the sum of
     squares is kept in double and the scale cast to float before use.
@@ -126,7 +134,7 @@ def softmax_rows(s: np.ndarray) -> np.ndarray:
     return (e * inv).astype(np.float32)
 
 
-def gqa_attention(q, k, v, window: int | None = None, q_pos=None, k_pos=None):
+def gqa_attention(q, k, v, window: int | None = None, q_pos=None, k_pos=None, round_p=None):
     """Causal grouped-query attention over whole sequences.
 
     q [Tq, H, HD]; k, v [Tk, KV, HD]. Query head h reads kv head h // (H/KV);
@@ -137,6 +145,10 @@ def gqa_attention(q, k, v, window: int | None = None, q_pos=None, k_pos=None):
 
     `window` (not in the reference, which has full attention only) restricts
     the visible keys further to p - window < t <= p.
+
+    `round_p` (the bfloat16 mode): the function that rounds the unnormalised
+    probabilities e^(s-max) for the second product, as a tensor-core kernel
+    does; the sum that normalises stays the sum of the unrounded ones.
     """
     tq, n_heads, hd = q.shape
     tk, n_kv, _ = k.shape
@@ -152,8 +164,13 @@ def gqa_attention(q, k, v, window: int | None = None, q_pos=None, k_pos=None):
         g = h // group
         s = (q[:, h, :].astype(np.float64) @ k[:, g, :].astype(np.float64).T).astype(np.float32) * scale
         s = np.where(vis, s, -np.inf).astype(np.float32)
-        p = softmax_rows(s)
-        out[:, h, :] = (p.astype(np.float64) @ v[:, g, :].astype(np.float64)).astype(np.float32)
+        if round_p is None:
+            p = softmax_rows(s)
+            out[:, h, :] = (p.astype(np.float64) @ v[:, g, :].astype(np.float64)).astype(np.float32)
+        else:
+            e = np.exp((s - np.max(s, axis=-1, keepdims=True)).astype(np.float32)).astype(np.float32)
+            inv = (1.0 / np.sum(e.astype(np.float64), axis=-1, keepdims=True)).astype(np.float32)
+            out[:, h, :] = (round_p(e).astype(np.float64) @ v[:, g, :].astype(np.float64)).astype(np.float32) * inv
     return out
 
 
@@ -163,10 +180,21 @@ class PlainQwen3:
     """Qwen3 dense decoder from a config.json dict and a name->array dict.
 
     Order of operations per docs/qwen3-arch.md:33-47 and src/arch_qwen3.c:178-252.
+
+    With `bf16` the model rounds to bfloat16 wherever a bfloat16 engine stores a
+    value: every norm's output, every product's output (the gate and up products
+    are activated from their unrounded sums, then rounded once), queries, keys and
+    values after the per-head norm and the rotation (the cache), the attention's
+    output, and the probabilities for the second product when the head size is one
+    a tensor-core kernel takes (64 or 128). Sums, softmax, norms, rotation and the
+    residual stream stay as they are. The reference has no such mode; a test may
+    hold a bfloat16 engine to it far more tightly than to the unrounded model.
     """
 
-    def __init__(self, cfg: dict, tensors: dict[str, np.ndarray]):
+    def __init__(self, cfg: dict, tensors: dict[str, np.ndarray], bf16: bool = False):
         self.cfg = cfg
+        self.bf16 = bool(bf16)
+        self.r = bf16_round if bf16 else (lambda a: a)
         self.t = {k: np.asarray(v, dtype=np.float32) for k, v in tensors.items()}
         self.L = int(cfg["num_hidden_layers"])
         self.D = int(cfg["hidden_size"])
@@ -179,9 +207,9 @@ class PlainQwen3:
         self.V = int(cfg["vocab_size"])
 
     @classmethod
-    def from_folder(cls, folder: str) -> "PlainQwen3":
+    def from_folder(cls, folder: str, bf16: bool = False) -> "PlainQwen3":
         cfg, tensors = read_folder(folder)
-        return cls(cfg, tensors)
+        return cls(cfg, tensors, bf16=bf16)
 
     def layer_window(self, i: int) -> int | None:
         """Window of layer i, from the config keys use_sliding_window,
@@ -196,21 +224,22 @@ class PlainQwen3:
         return None
 
     def block(self, i: int, x: np.ndarray, cos, sin, taps=None) -> np.ndarray:
-        t, p = self.t, f"model.layers.{i}."
-        h = rms_norm(x, t[p + "input_layernorm.weight"], self.eps)            # arch_qwen3.c:201
-        q = linear(h, t[p + "self_attn.q_proj.weight"]).reshape(-1, self.H, self.HD)   # :204
-        k = linear(h, t[p + "self_attn.k_proj.weight"]).reshape(-1, self.KV, self.HD)  # :205
-        v = linear(h, t[p + "self_attn.v_proj.weight"]).reshape(-1, self.KV, self.HD)  # :206
+        t, p, r = self.t, f"model.layers.{i}.", self.r
+        h = r(rms_norm(x, t[p + "input_layernorm.weight"], self.eps))         # arch_qwen3.c:201
+        q = r(linear(h, t[p + "self_attn.q_proj.weight"])).reshape(-1, self.H, self.HD)   # :204
+        k = r(linear(h, t[p + "self_attn.k_proj.weight"])).reshape(-1, self.KV, self.HD)  # :205
+        v = r(linear(h, t[p + "self_attn.v_proj.weight"])).reshape(-1, self.KV, self.HD)  # :206
         q = rms_norm(q, t[p + "self_attn.q_norm.weight"], self.eps)           # :209-214, per head
         k = rms_norm(k, t[p + "self_attn.k_norm.weight"], self.eps)
-        q = rope_apply(q, cos, sin)                                           # :217-218
-        k = rope_apply(k, cos, sin)
-        a = gqa_attention(q, k, v, window=self.layer_window(i))               # :220-221
-        x = x + linear(a.reshape(-1, self.H * self.HD), t[p + "self_attn.o_proj.weight"])  # :223-224
-        h = rms_norm(x, t[p + "post_attention_layernorm.weight"], self.eps)   # :226
+        q = r(rope_apply(q, cos, sin))                                        # :217-218
+        k = r(rope_apply(k, cos, sin))
+        round_p = bf16_round if self.bf16 and self.HD in (64, 128) else None
+        a = r(gqa_attention(q, k, v, window=self.layer_window(i), round_p=round_p))      # :220-221
+        x = x + r(linear(a.reshape(-1, self.H * self.HD), t[p + "self_attn.o_proj.weight"]))  # :223-224
+        h = r(rms_norm(x, t[p + "post_attention_layernorm.weight"], self.eps))  # :226
         g = linear(h, t[p + "mlp.gate_proj.weight"])                          # :229
         u = linear(h, t[p + "mlp.up_proj.weight"])                            # :230
-        x = x + linear(swiglu(g, u), t[p + "mlp.down_proj.weight"])           # :231-234
+        x = x + r(linear(r(swiglu(g, u)), t[p + "mlp.down_proj.weight"]))     # :231-234
         return x.astype(np.float32)
 
     def forward(self, tokens, taps: dict | None = None) -> np.ndarray:
@@ -225,7 +254,7 @@ class PlainQwen3:
             x = self.block(i, x, cos, sin)
             if taps is not None:
                 taps[f"layer{i}"] = x.copy()
-        h = rms_norm(x, self.t["model.norm.weight"], self.eps)                # :239
+        h = self.r(rms_norm(x, self.t["model.norm.weight"], self.eps))        # :239
         if taps is not None:
             taps["final_norm"] = h.copy()
         head = self.t["model.embed_tokens.weight"] if self.tied else self.t["lm_head.weight"]  # :243-247

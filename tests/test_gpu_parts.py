@@ -535,3 +535,276 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
     eng.check_status()
     for i, r in enumerate(refs):
         assert_close(r, np.concatenate(got[i]), FP32_REL, f"routed request {i} in a batch, last 4 one by one")
+
+
+# ------------- a toy model whose every part is the test's own: embedding, head, a state mixer that runs from graphs
+
+WIDE_ARCH = "ToyWideForCausalLM"
+
+
+def _register_wide():
+    """An embedding with a scale, a head with a soft cap, a mixer with fixed-size state that indexes the state by
+    the step's slots on the device (so its decode steps replay from captured graphs), and a mixer that keeps one
+    latent vector per position (keys only, no values) in the paged cache: all defined here."""
+    from dataclasses import dataclass
+
+    from mynah_slm_b200.config.keys import req_float, req_int
+    from mynah_slm_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from mynah_slm_b200.parts import (Embedding, Head, KVRequest, Mixer, StateRequest, TensorSpec, register_embedding,
+                                      register_head, register_mixer)
+    from mynah_slm_b200.registry import known_architectures, register_architecture
+
+    class ScaledEmbedding(Embedding):
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.V, self.D, self.scale = spec["vocab_size"], spec["dim"], float(spec["scale"])
+
+        def tensor_specs(self):
+            return [TensorSpec("embed.weight", (self.V, self.D))]
+
+        def bind(self, tensors, runtime):
+            self.table = tensors["embed.weight"]
+
+        def forward(self, tokens):
+            return self.table[tokens.long()].float() * self.scale
+
+    class SoftcapHead(Head):
+        """logits = cap * tanh((W h) / cap), W of its own."""
+
+        def __init__(self, spec, embedding):
+            super().__init__(spec)
+            self.V, self.D, self.cap = spec["vocab_size"], spec["dim"], float(spec["cap"])
+
+        def tensor_specs(self):
+            return [TensorSpec("head.weight", (self.V, self.D), std=0.3)]
+
+        def bind(self, tensors, runtime):
+            self.w = tensors["head.weight"]
+
+        def forward(self, h):
+            if hasattr(h, "materialize"):
+                h = h.materialize()
+            return self.cap * torch.tanh((h.float() @ self.w.float().t()) / self.cap)
+
+    class DecayOnDevice(Mixer):
+        """s_t = decay * s_{t-1} + W_in h_t ; out_t = W_out s_t, with everything it needs to know about the batch
+        read on the device: the rows of a sequence are summed with a [T, T] matrix of powers of the decay, the old
+        state comes from cache.state[slot], padding rows use the state's last row."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.D, self.S, self.decay, self.prefix = spec["hidden_size"], spec["state_size"], float(spec["decay"]), spec["prefix"]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "in.weight", (self.S, self.D), std=0.2),
+                    TensorSpec(self.prefix + "out.weight", (self.D, self.S), std=0.2)]
+
+        def bind(self, tensors, runtime):
+            self.w_in, self.w_out = tensors[self.prefix + "in.weight"], tensors[self.prefix + "out.weight"]
+
+        def state_request(self):
+            return StateRequest((self.S,), torch.float32)
+
+        def forward(self, h, ctx, cache):
+            u = (h.float() @ self.w_in.float().t()).double()
+            seq = ctx.tok_seq.long()
+            valid = seq >= 0
+            seqc = seq.clamp(min=0)
+            slots = ctx.slots.long()
+            rows = torch.where(slots >= 0, slots, cache.state.shape[0] - 1)
+            q_len = (ctx.cu_q[1:] - ctx.cu_q[:-1]).long()
+            rel = ctx.tok_pos.long() - (ctx.kv_len.long() - q_len)[seqc]              # place within this step's piece
+            together = (seq[:, None] == seq[None, :]) & valid[:, None] & valid[None, :] & (rel[None, :] <= rel[:, None])
+            powers = torch.where(together, self.decay ** (rel[:, None] - rel[None, :]).clamp(min=0).double(), 0.0)
+            old = cache.state[rows].double()
+            s = powers @ u + (self.decay ** (rel + 1).clamp(min=0).double())[:, None] * old[seqc]
+            s = torch.where(valid[:, None], s, 0.0)
+            last = (ctx.cu_q[1:].long() - 1).clamp(min=0)
+            cache.state[rows] = torch.where((q_len > 0)[:, None], s[last].float(), cache.state[rows])
+            return (s.float() @ self.w_out.float().t()).to(h.dtype)
+
+    class LatentMixer(Mixer):
+        """Keeps one vector c_t = W_c h_t per position (no values); out_t = W_out sum_j softmax_j(q_t . c_j / sqrt(R)) c_j
+        over the positions j <= t. Plans on the host: it reads its pages' numbers back."""
+        graph_safe = False
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.D, self.R, self.prefix = spec["hidden_size"], spec["latent_size"], spec["prefix"]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "c.weight", (self.R, self.D), std=0.3), TensorSpec(self.prefix + "q.weight", (self.R, self.D), std=0.3),
+                    TensorSpec(self.prefix + "out.weight", (self.D, self.R), std=0.3)]
+
+        def bind(self, tensors, runtime):
+            self.w_c, self.w_q, self.w_out = (tensors[self.prefix + n] for n in ("c.weight", "q.weight", "out.weight"))
+
+        def kv_request(self):
+            return KVRequest(1, self.R, None, values=False)
+
+        def forward(self, h, ctx, cache):
+            assert cache.v is None and tuple(cache.k.shape[1:]) == (1, 64, self.R)
+            c, q = h.float() @ self.w_c.float().t(), h.float() @ self.w_q.float().t()
+            pt = ctx.pages[cache.group]
+            indptr, ids = pt.indptr.cpu().tolist(), pt.ids.cpu().tolist()
+            out = torch.empty_like(c)
+            row = 0
+            for b, (n, past) in enumerate(zip(ctx.host_q_lens, ctx.host_past)):
+                mine = ids[indptr[b]:indptr[b + 1]]
+                for t in range(n):
+                    cache.k[mine[(past + t) // 64], 0, (past + t) % 64] = c[row + t].to(cache.k.dtype)
+                every = torch.cat([cache.k[p, 0] for p in mine])[:past + n].float()
+                sc = (q[row:row + n] @ every.t()) / (self.R ** 0.5)
+                pos = torch.arange(past, past + n, device=sc.device)
+                sc = sc.masked_fill(torch.arange(past + n, device=sc.device)[None, :] > pos[:, None], float("-inf"))
+                out[row:row + n] = torch.softmax(sc, dim=-1) @ every
+                row += n
+            return (out @ self.w_out.float().t()).to(h.dtype)
+
+    @dataclass(frozen=True)
+    class WideConfig:
+        raw: tuple
+
+        @classmethod
+        def from_dict(cls, d, generation=None):
+            for k in ("hidden_size", "vocab_size", "state_size", "latent_size", "num_heads", "num_kv_heads", "head_dim",
+                      "ffn_size", "max_positions"):
+                req_int(d, k)
+            for k in ("decay", "eps", "theta", "scale", "cap"):
+                req_float(d, k)
+            return cls(tuple(sorted((k, json.dumps(v)) for k, v in d.items())))
+
+        def to_dict(self):
+            return {k: json.loads(v) for k, v in self.raw}
+
+        def model_spec(self):
+            d = self.to_dict()
+            D = d["hidden_size"]
+            layers = []
+            for i, kind in enumerate(d["mixers"]):
+                p = f"layers.{i}."
+                mixer = {"decay": PartSpec("toy_decay_on_device", {"hidden_size": D, "state_size": d["state_size"], "decay": d["decay"], "prefix": p + "mix."}),
+                         "latent": PartSpec("toy_latent", {"hidden_size": D, "latent_size": d["latent_size"], "prefix": p + "lat."}),
+                         "attn": PartSpec("gqa_attention", {"hidden_size": D, "num_heads": d["num_heads"], "num_kv_heads": d["num_kv_heads"],
+                                                            "head_dim": d["head_dim"], "qk_norm": None, "window": None, "prefix": p + "attn.",
+                                                            "position": PartSpec("rope_neox", {"theta": d["theta"], "rotary_dim": d["head_dim"]})})}[kind]
+                norms = {k: PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": f"{p}{k}_norm.weight"}) for k in ("mixer", "ffn")}
+                ffn = PartSpec("swiglu_dense", {"hidden_size": D, "intermediate_size": d["ffn_size"], "prefix": p + "mlp."})
+                layers.append(LayerSpec(PartSpec("prenorm_residual", {}), mixer, ffn, norms, p))
+            return ModelSpec(WIDE_ARCH, d["vocab_size"], D, d["max_positions"], tuple(layers),
+                             tuple(ScheduleEntry(i, None) for i in range(len(layers))),
+                             PartSpec("toy_scaled_embedding", {"vocab_size": d["vocab_size"], "dim": D, "scale": d["scale"]}),
+                             PartSpec("rmsnorm", {"eps": d["eps"], "dim": D, "name": "final_norm.weight"}),
+                             PartSpec("toy_softcap_head", {"vocab_size": d["vocab_size"], "dim": D, "cap": d["cap"]}))
+
+    register_embedding("toy_scaled_embedding", ScaledEmbedding, replace=True)
+    register_head("toy_softcap_head", SoftcapHead, replace=True)
+    register_mixer("toy_decay_on_device", DecayOnDevice, replace=True)
+    register_mixer("toy_latent", LatentMixer, replace=True)
+    if WIDE_ARCH not in known_architectures():
+        register_architecture(WIDE_ARCH, WideConfig.from_dict)
+
+
+WIDE = dict(architectures=[WIDE_ARCH], hidden_size=40, vocab_size=230, state_size=24, latent_size=12, num_heads=4,
+            num_kv_heads=2, head_dim=16, ffn_size=72, max_positions=256, decay=0.9, eps=1e-5, theta=500.0, scale=3.0,
+            cap=2.0, mixers=["decay", "attn", "decay"])
+
+
+def _wide_plain(cfg, t, tokens):
+    D, H, KV, HD, R = cfg["hidden_size"], cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"], cfg["latent_size"]
+    n = len(tokens)
+    x = t["embed.weight"][np.asarray(tokens)] * np.float32(cfg["scale"])
+    cs, sn = rope_table(HD, np.arange(n), cfg["theta"])
+    for l, kind in enumerate(cfg["mixers"]):
+        p = f"layers.{l}."
+        h = rms_norm(x, t[p + "mixer_norm.weight"], cfg["eps"])
+        if kind == "decay":
+            u = linear(h, t[p + "mix.in.weight"])
+            st, rows = np.zeros(cfg["state_size"], dtype=np.float32), []
+            for i in range(n):
+                st = np.float32(cfg["decay"]) * st + u[i]
+                rows.append(st.copy())
+            m = linear(np.stack(rows), t[p + "mix.out.weight"])
+        elif kind == "latent":
+            c, q = linear(h, t[p + "lat.c.weight"]), linear(h, t[p + "lat.q.weight"])
+            sc = (q.astype(np.float64) @ c.astype(np.float64).T) / np.sqrt(R)
+            sc = np.where(np.arange(n)[None, :] > np.arange(n)[:, None], -np.inf, sc)
+            pr = np.exp(sc - sc.max(axis=-1, keepdims=True))
+            m = linear(((pr / pr.sum(axis=-1, keepdims=True)) @ c.astype(np.float64)).astype(np.float32), t[p + "lat.out.weight"])
+        else:
+            q = rope_apply(linear(h, t[p + "attn.q_proj.weight"]).reshape(n, H, HD), cs, sn)
+            k = rope_apply(linear(h, t[p + "attn.k_proj.weight"]).reshape(n, KV, HD), cs, sn)
+            v = linear(h, t[p + "attn.v_proj.weight"]).reshape(n, KV, HD)
+            m = linear(gqa_attention(q, k, v).reshape(n, H * HD), t[p + "attn.o_proj.weight"])
+        x = x + m
+        h = rms_norm(x, t[p + "ffn_norm.weight"], cfg["eps"])
+        x = x + linear(swiglu(linear(h, t[p + "mlp.gate_proj.weight"]), linear(h, t[p + "mlp.up_proj.weight"])), t[p + "mlp.down_proj.weight"])
+    z = linear(rms_norm(x, t["final_norm.weight"], cfg["eps"]), t["head.weight"])
+    return (np.float32(cfg["cap"]) * np.tanh(z.astype(np.float64) / cfg["cap"])).astype(np.float32)
+
+
+def _batch_then_one_by_one(eng, seqs, tail):
+    from mynah_slm_b200.engine.engine import StepEntry
+    slots = [eng.open_sequence() for _ in seqs]
+    heads = [len(s) - tail for s in seqs]
+    out = eng.step([StepEntry(sl, s[:h], range(h)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+    got, row = [[] for _ in seqs], 0
+    for i, h in enumerate(heads):
+        got[i].append(out[row:row + h]); row += h
+    for t in range(tail):
+        out = eng.step([StepEntry(sl, [s[h + t]], (0,)) for sl, s, h in zip(slots, seqs, heads)]).cpu().numpy()
+        for i in range(len(seqs)):
+            got[i].append(out[i:i + 1])
+    eng.check_status()
+    for sl in slots:
+        eng.close_sequence(sl)
+    return slots, [np.concatenate(g) for g in got]
+
+
+def test_toy_embedding_head_and_a_state_mixer_that_runs_from_graphs(tmp_path):
+    """An embedding with a scale, a head with a soft cap and a mixer with state, registered from here, in a model
+    whose decode steps replay from captured graphs (no part plans on the host): three sequences and a padding row
+    in a bucket of four, the state carried from the prompt step through the replayed steps; a second batch in the
+    same slots starts from zero state."""
+    _register_wide()
+    from mynah_slm_b200.engine.engine import Engine
+    from mynah_slm_b200.registry import parse_config
+    from mynah_slm_b200.weights.random_init import write_random_model
+    folder = write_random_model(str(tmp_path / "wide"), parse_config(WIDE), seed=7, dtype=torch.float32)
+    cfg, tensors = read_folder(folder)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 6)
+    assert eng.graph_safe and eng.use_graphs
+    rng = np.random.default_rng(8)
+    first = None
+    for rnd in range(2):
+        seqs = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in (70, 12, 33)]
+        slots, got = _batch_then_one_by_one(eng, seqs, 6)
+        first = first or slots
+        assert sorted(slots) == sorted(first)
+        for i, s in enumerate(seqs):
+            assert_close(_wide_plain(cfg, tensors, s), got[i], FP32_REL, f"round {rnd}, request {i}")
+    assert any(g.graphs for g in eng._graphs.values()), "no decode step was replayed from a graph"
+    ref = _wide_plain(cfg, tensors, seqs[0])
+    assert np.abs(ref).max() < cfg["cap"] and np.abs(ref).max() > 0.5 * cfg["cap"]      # the cap does cap
+
+
+def test_toy_mixer_that_keeps_one_vector_per_position(tmp_path):
+    """A mixer that asks the cache for keys only (one latent vector per position, no values) beside an attention
+    layer with keys and values: two storage groups with page lists of their own, the latent group without a value
+    tensor."""
+    _register_wide()
+    from mynah_slm_b200.engine.engine import Engine
+    from mynah_slm_b200.registry import parse_config
+    from mynah_slm_b200.weights.random_init import write_random_model
+    cfg_in = dict(WIDE, mixers=["latent", "attn", "latent"])
+    folder = write_random_model(str(tmp_path / "latent"), parse_config(cfg_in), seed=9, dtype=torch.float32)
+    cfg, tensors = read_folder(folder)
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 6)
+    groups = eng.cache.plan.groups
+    assert [(g.kv_heads, g.head_dim, g.v_head_dim) for g in groups] == [(1, 12, 0), (2, 16, 16)]
+    assert eng.cache.values[0] is None and tuple(eng.cache.keys[0].shape) == (2, eng.n_pages, 1, 64, 12)
+    rng = np.random.default_rng(10)
+    seqs = [rng.integers(0, cfg["vocab_size"], size=n).tolist() for n in (70, 12, 130)]
+    _, got = _batch_then_one_by_one(eng, seqs, 4)
+    for i, s in enumerate(seqs):
+        assert_close(_wide_plain(cfg, tensors, s), got[i], FP32_REL, f"request {i}")

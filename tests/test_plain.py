@@ -57,6 +57,27 @@ def test_gate_rejects_wrong_models():
     finally:
         pm.rope_apply = orig
 
+    # a residual stream kept in 16 bits (tools/eval/test_gate.py:106-109)
+    real = pm.rms_norm
+    pm.rms_norm = lambda x, w, eps: real(x.astype(np.float16).astype(np.float32), w, eps)
+    try:
+        assert rel_err(ref, PlainQwen3(dict(c), tensors).forward(tokens)) > 1e-4
+    finally:
+        pm.rms_norm = real
+
+    # head_dim derived as hidden / heads instead of read from its own key (tests/test_model.c:99-113: "128, not
+    # d_model/n_heads"): on B, whose heads are 32 wide while hidden / heads is 16, such a model cannot even be
+    # put together, or gives other logits
+    cb, tb, tokb = build("B")
+    derived = dict(cb, head_dim=cb["hidden_size"] // cb["num_attention_heads"])
+    assert derived["head_dim"] != cb["head_dim"]
+    try:
+        wrong = PlainQwen3(derived, tb).forward(tokb)
+        shows = wrong.shape != gold["B_logits"].shape or rel_err(gold["B_logits"], wrong) > 1e-3
+    except (ValueError, IndexError):
+        shows = True
+    assert shows
+
 
 def test_rms_norm_properties():
     rng = np.random.default_rng(0)
