@@ -100,7 +100,8 @@ def library_path(verbose: bool = False) -> str:
 
 
 def _say(msg: str) -> None:
-    print(f"[mynah_slm_b200] {msg}", file=sys.stderr, flush=True)
+    if os.environ.get("MYNAH_QUIET", "0") in ("", "0"):          # the C interface sets it: that library never prints
+        print(f"[mynah_slm_b200] {msg}", file=sys.stderr, flush=True)
 
 
 def _build(out: str, lib: str, verbose: bool) -> None:
@@ -186,6 +187,51 @@ def host_library_path() -> str:
     return lib
 
 
+# ---------------------------------------------------------------- the C interface (hosts a Python interpreter)
+CAPI_LIB_NAME = "libmynah_slm_b200_capi.so"
+CAPI_SOURCES = [os.path.join("host", "capi.c")]
+CAPI_HEADERS = [os.path.join(os.pardir, "include", "mynah_slm_b200.h"), os.path.join(os.pardir, "include", "mynah_slm_b200_host.h")]
+
+
+def capi_library_path() -> str:
+    """Path of the up-to-date library behind `include/mynah_slm_b200.h`, building it first if need be. It links
+    the Python library of the interpreter that builds it and remembers that interpreter and this checkout as the
+    defaults it starts with (MYNAH_PYTHON and MYNAH_SLM_B200_ROOT override them)."""
+    import sysconfig
+    out = build_dir()
+    lib = os.path.join(out, CAPI_LIB_NAME)
+    stamp_file = os.path.join(out, "capi_stamp")
+    root = os.path.dirname(os.path.dirname(HERE))
+    inc, libdir = sysconfig.get_paths()["include"], sysconfig.get_config_var("LIBDIR") or ""
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_python_version()
+    if not os.path.isfile(os.path.join(inc, "Python.h")):
+        raise BuildError(f"Python.h is not under {inc}: the C interface of mynah_slm_b200 needs Python's headers")
+    flags = ["-O2", "-std=c11", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", f"-I{inc}",
+             f'-DMYNAH_DEFAULT_PYTHON="{sys.executable}"', f'-DMYNAH_DEFAULT_ROOT="{root}"']
+    link = [f"-L{libdir}", f"-Wl,-rpath,{libdir}", f"-lpython{ver}"] if libdir else [f"-lpython{ver}"]
+    h = hashlib.sha256(" ".join(flags + link).encode())
+    for f in CAPI_SOURCES + CAPI_HEADERS:
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(fh.read())
+    stamp = h.hexdigest()
+    if os.path.isfile(lib) and os.path.isfile(stamp_file):
+        with open(stamp_file) as f:
+            if f.read().strip() == stamp:
+                return lib
+    cc = next((c for c in (os.environ.get("CC"), shutil.which("gcc"), shutil.which("cc"), shutil.which("clang")) if c and os.path.isfile(c)), None)
+    if cc is None:
+        raise BuildError("no C compiler found (looked at $CC, gcc, cc, clang): the C interface cannot be built")
+    tmp = lib + f".tmp{os.getpid()}"
+    r = subprocess.run([cc, *flags, "-o", tmp, *[os.path.join(HERE, f) for f in CAPI_SOURCES], *link], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"compiling the C interface failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib)
+    with open(stamp_file, "w") as f:
+        f.write(stamp)
+    return lib
+
+
 if __name__ == "__main__":
     print(host_library_path())
+    print(capi_library_path())
     print(library_path(verbose="-v" in sys.argv))
