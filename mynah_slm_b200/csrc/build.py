@@ -208,7 +208,7 @@ def capi_library_path() -> str:
         raise BuildError(f"Python.h is not under {inc}: the C interface of mynah_slm_b200 needs Python's headers")
     flags = ["-O2", "-std=c11", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", f"-I{inc}",
              f'-DMYNAH_DEFAULT_PYTHON="{sys.executable}"', f'-DMYNAH_DEFAULT_ROOT="{root}"']
-    link = [f"-L{libdir}", f"-Wl,-rpath,{libdir}", f"-lpython{ver}"] if libdir else [f"-lpython{ver}"]
+    link = [f"-Wl,-soname,{CAPI_LIB_NAME}"] + ([f"-L{libdir}", f"-Wl,-rpath,{libdir}"] if libdir else []) + [f"-lpython{ver}"]
     h = hashlib.sha256(" ".join(flags + link).encode())
     for f in CAPI_SOURCES + CAPI_HEADERS:
         with open(os.path.join(HERE, f), "rb") as fh:
