@@ -127,10 +127,10 @@ def test_c_program_generates(program, tmp_path):
     assert lines[4] == "stopped rc 7 finish 3 n 3"
     # a stop token ends a request before it is emitted
     first = plain_generate(plain, prompts[0], 8, PlainSampler(temp=0))[0]
-    stop_at = next(j for j in range(1, 8) if first[j] not in first[:j])
+    stop_at = next((j for j in range(1, 8) if first[j] not in first[:j]), 0)
     p = _run(program, ["generate", folder, "float32", str(64 * 4), str(path), "8", "0", "0", str(first[stop_at])], tmp_path)
     line = p.stdout.strip().splitlines()[0]
-    assert line == f"request 0 finish 0 produced {stop_at + 1} tokens " + " ".join(str(t) for t in first[:stop_at])
+    assert line == f"request 0 finish 0 produced {stop_at + 1} tokens" + "".join(f" {t}" for t in first[:stop_at])
 
 
 def test_c_program_meets_errors_with_codes_and_messages(program, tmp_path):
