@@ -17,6 +17,9 @@
 // (mynah-slm src/kernels.c:228-250, :207-220).
 #include "layout.cuh"
 #include "head_prep.cuh"
+#include "tcgen05.cuh"
+
+#include <stdlib.h>
 
 namespace {
 
@@ -58,6 +61,24 @@ struct TcArgs {
 // the low three bits of the chunk index are xor-ed with the row, so the eight
 // rows of an 8x8 matrix fall into eight different bank groups.
 template <int CH> __device__ __forceinline__ int swz(int r, int c) { return (r * CH + (c ^ (r & 7))) * 16; }
+
+// Where 16-byte chunk c of row r of a [64 keys x HD] tile lies in shared memory.
+// TileSwz: as the 16-byte asynchronous copies of this file lay it out (rows of HD / 8 chunks).
+// TileTma: as a TMA copy with the 128-byte swizzle leaves it: halves of 64 columns one after the other, rows of 128 bytes.
+template <int HD> struct TileSwz {
+    static __device__ __forceinline__ int off(int r, int c) { return swz<HD / 8>(r, c); }
+};
+template <int HD> struct TileTma {
+    static __device__ __forceinline__ int off(int r, int c) { return (c >> 3) * (KEYS * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4); }
+};
+// Who works on a page together: the whole CTA, or the four consumer warps of the streaming kernel (its fifth warp
+// feeds them and must not be waited for).
+struct SyncCta {
+    static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+struct SyncConsumers {
+    static __device__ __forceinline__ void sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+};
 
 // One visible page of one (sequence, kv head): what a CTA of the one-shot kernel, or one turn of the persistent
 // kernel's loop, works on.
@@ -145,34 +166,32 @@ __device__ __forceinline__ void load_q_fragments(const PageJob& j, const bf16* _
     }
 }
 
-// The page's partial result from its tiles in shared memory. PENDING_K / PENDING_V: copy groups that may still be
-// in flight when the K tile, then the V tile, are needed (those of later pages). Ends with the CTA in step.
-template <int HD, int PENDING_K, int PENDING_V>
-__device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t (&qa)[HD / 16][4], const TcArgs& a,
-                                             uint32_t k_base, uint32_t v_base, bf16* p_s, float (*red_m)[MAX_G], float (*red_l)[MAX_G],
-                                             float* __restrict__ part_o, float* __restrict__ part_ml) {
-    constexpr int CH = HD / 8, KSTEPS = HD / 16, NT = HD / 32;
+// The page's partial result. Where the K and V fragments come from is the caller's business: k_frag(ks, kb) gives
+// the B fragments of this warp's 16 keys for dims [16 ks, 16 ks + 16), v_frag(ks, nt, vb) those of keys
+// [16 ks, 16 ks + 16) for this warp's n-tiles nt and nt + 1; before_k() and before_v() run before the first use of
+// each (waits and barriers, if the fragments still lie in shared memory). The arithmetic, and so every bit of the
+// result, is the same whoever provides them.
+template <int HD, class SYNC, class KFRAG, class VFRAG, class BEFORE_K, class BEFORE_V>
+__device__ __forceinline__ void compute_page_core(const PageJob& job, const uint32_t (&qa)[HD / 16][4], const TcArgs& a,
+                                                  KFRAG k_frag, VFRAG v_frag, BEFORE_K before_k, BEFORE_V before_v,
+                                                  bf16* p_s, float (*red_m)[MAX_G], float (*red_l)[MAX_G],
+                                                  float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int KSTEPS = HD / 16, NT = HD / 32;
     const int G = a.H / a.KV;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k_first = job.k_first, k_last = job.k_last;
     const size_t row0 = job.row0;
 
-    cp_async_wait<PENDING_K>();                       // K has landed (V may still be in flight)
-    __syncthreads();
+    before_k();
 
     // ---- scores: warp w takes keys [16w, 16w+16): two n-tiles of 8 keys
     float sc[2][4] = {};
-    {
-        const int mat = lane >> 3, rr = lane & 7;     // ldmatrix: thread -> (matrix, row)
-        // matrices: 0: keys 0-7, dims k0..k0+7; 1: keys 0-7, dims +8; 2: keys 8-15, dims k0; 3: keys 8-15, dims +8
-        const int key = warp * 16 + (mat >> 1) * 8 + rr;
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ks++) {
-            uint32_t kb[4];
-            ldmatrix_x4(kb, k_base + swz<CH>(key, ks * 2 + (mat & 1)));
-            mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
-            mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
-        }
+    for (int ks = 0; ks < KSTEPS; ks++) {
+        uint32_t kb[4];
+        k_frag(ks, kb);
+        mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
+        mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
     }
     // C layout: sc[t][0..1] -> head lane/4, keys 16w + 8t + (lane%4)*2 + {0,1}; sc[t][2..3] -> head lane/4 + 8
     const int hrow = lane >> 2;
@@ -195,7 +214,7 @@ __device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t 
         red_m[warp][hrow] = mx[0];
         red_m[warp][hrow + 8] = mx[1];
     }
-    __syncthreads();
+    SYNC::sync();
     float m[2], l[2] = {0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < 2; j++) {
@@ -224,8 +243,7 @@ __device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t 
         red_l[warp][hrow] = l[0];
         red_l[warp][hrow + 8] = l[1];
     }
-    cp_async_wait<PENDING_V>();                       // V has landed
-    __syncthreads();
+    before_v();                                       // (a barrier: the probabilities and the sums are in shared memory)
 
     // ---- output: warp w takes dims [w*HD/4, (w+1)*HD/4): HD/32 n-tiles of 8, four k-steps of 16 keys
     float oc[NT][4] = {};
@@ -241,11 +259,7 @@ __device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t 
 #pragma unroll
             for (int nt = 0; nt < NT; nt += 2) {
                 uint32_t vb[4];
-                // B operand from V [key][dim] (transposed load): matrices 0: keys k0..+7, dims n0..+7; 1: keys +8, same dims;
-                // 2: keys k0..+7, dims n0+8; 3: keys +8, dims n0+8
-                const int key = ks * 16 + (mat & 1) * 8 + rr;
-                const int chunk = warp * (HD / 32) + nt + (mat >> 1);
-                ldmatrix_x4_trans(vb, v_base + swz<CH>(key, chunk));
+                v_frag(ks, nt, vb);
                 mma_bf16(oc[nt], pa, vb[0], vb[1]);
                 mma_bf16(oc[nt + 1], pa, vb[2], vb[3]);
             }
@@ -270,6 +284,38 @@ __device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t 
         part_ml[(row0 + (size_t)tid * a.S) * 2] = mm;
         part_ml[(row0 + (size_t)tid * a.S) * 2 + 1] = ls;
     }
+}
+
+// The fragments of a page's tiles in shared memory, as compute_page_core wants them.
+// K (non-transposed load): matrices 0: keys 0-7 of the warp's 16, dims k0..k0+7; 1: keys 0-7, dims +8; 2: keys 8-15,
+// dims k0; 3: keys 8-15, dims +8. V [key][dim] (transposed load): matrices 0: keys k0..+7, dims n0..+7; 1: keys +8,
+// same dims; 2: keys k0..+7, dims n0+8; 3: keys +8, dims n0+8.
+template <int HD, class TILE>
+__device__ __forceinline__ void load_k_frag(uint32_t k_base, int ks, uint32_t (&kb)[4]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mat = lane >> 3, rr = lane & 7;
+    ldmatrix_x4(kb, k_base + TILE::off(warp * 16 + (mat >> 1) * 8 + rr, ks * 2 + (mat & 1)));
+}
+template <int HD, class TILE>
+__device__ __forceinline__ void load_v_frag(uint32_t v_base, int ks, int nt, uint32_t (&vb)[4]) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mat = lane >> 3, rr = lane & 7;
+    ldmatrix_x4_trans(vb, v_base + TILE::off(ks * 16 + (mat & 1) * 8 + rr, warp * (HD / 32) + nt + (mat >> 1)));
+}
+
+// From the tiles in shared memory. PENDING_K / PENDING_V: copy groups that may still be in flight when the K tile,
+// then the V tile, are needed (those of later pages). Ends with the CTA in step.
+template <int HD, int PENDING_K, int PENDING_V>
+__device__ __forceinline__ void compute_page(const PageJob& job, const uint32_t (&qa)[HD / 16][4], const TcArgs& a,
+                                             uint32_t k_base, uint32_t v_base, bf16* p_s, float (*red_m)[MAX_G], float (*red_l)[MAX_G],
+                                             float* __restrict__ part_o, float* __restrict__ part_ml) {
+    compute_page_core<HD, SyncCta>(
+        job, qa, a,
+        [&](int ks, uint32_t (&kb)[4]) { load_k_frag<HD, TileSwz<HD>>(k_base, ks, kb); },
+        [&](int ks, int nt, uint32_t (&vb)[4]) { load_v_frag<HD, TileSwz<HD>>(v_base, ks, nt, vb); },
+        [&]() { cp_async_wait<PENDING_K>(); __syncthreads(); },       // K has landed (V may still be in flight)
+        [&]() { cp_async_wait<PENDING_V>(); __syncthreads(); },       // V has landed
+        p_s, red_m, red_l, part_o, part_ml);
 }
 
 // One CTA a page; six CTAs an SM cover one another's waits. (Persistent CTAs that prefetch their next page were
@@ -589,7 +635,252 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
                     G, a.S, n_vis, reinterpret_cast<float*>(k_s), reinterpret_cast<float*>(v_s), red_m[0]);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// The pages' kernel as a stream: persistent CTAs, fed by TMA.
+//
+// The same partial results as attn_decode_tc_kernel, page by page and bit for bit (the same compute_page on the
+// same numbers), so the same merge follows. What differs is who fetches: a fifth warp walks the CTA's share of the
+// step's pages (every sequence's visible pages times the kv heads, dealt out round-robin) ahead of the four
+// warps that compute, looks each page up and has the TMA unit copy its K and V tiles (two boxes of 64 x 64 each for
+// a head size of 128) and the group's query heads into the next free stage of a ring; an mbarrier per stage
+// counts the bytes in. The computing warps never wait for a table lookup, and the memory system always has the
+// next pages' requests while a page is worked on: that is what the one-page CTAs get from six CTAs an SM
+// covering one another, without their launch, drain and tail. Keys outside the visible range arrive with the page
+// (a copy is a whole tile): their scores are masked as before, and their rows of V are zeroed in shared memory
+// before the second product, so that stale contents of a page cannot reach it.
+struct StreamJob {
+    int b, g, k_first, k_last, empty, partial;
+    unsigned long long row0;
+};
+
+constexpr int STREAM_THREADS = (WARPS + 1) * 32;
+constexpr int STREAM_MAX_SEQS = 1024;             // sequences whose page counts a CTA keeps in shared memory
+
+template <int HD>
+__host__ __device__ constexpr int stream_q_stride(int G) { return ((G * HD * 2 + 127) / 128) * 128; }
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(STREAM_THREADS)
+attn_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                          const bf16* __restrict__ q, const int* __restrict__ kv_len, PageTable pt, TcArgs a, int B,
+                          float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
+    using namespace tc5;
+    constexpr int TILE = KEYS * HD * 2;
+    constexpr int CH = HD / 8;
+    const int G = a.H / a.KV;
+    const int q_stride = stream_q_stride<HD>(G);
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* tiles = smem;                                   // [STAGES][K tile, V tile]
+    unsigned char* q_area = tiles + STAGES * 2 * TILE;             // [STAGES][q_stride]
+    bf16* p_s = reinterpret_cast<bf16*>(q_area + STAGES * q_stride);
+    float (*red_m)[MAX_G] = reinterpret_cast<float (*)[MAX_G]>(p_s + MAX_G * KEYS);
+    float (*red_l)[MAX_G] = red_m + WARPS;
+    StreamJob* jobs = reinterpret_cast<StreamJob*>(red_l + WARPS);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(jobs + STAGES);   // full[STAGES], empty[STAGES]
+    int* cum = reinterpret_cast<int*>(bars + 2 * STAGES);          // cum[b]: visible pages of the sequences before b
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < STAGES; i++) {
+            mbar_init(smem_u32(&bars[i]), 1);
+            mbar_init(smem_u32(&bars[STAGES + i]), WARPS);        // every computing warp gives a stage back itself
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    griddep_launch();
+    griddep_wait();
+    for (int b = tid; b < B; b += STREAM_THREADS) {
+        const int hi = kv_len[b];
+        const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+        int n = 0;
+        if (hi > 0) {
+            n = (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS;
+            if (n > a.S) {
+                if (blockIdx.x == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
+                n = a.S;
+            }
+        }
+        cum[b + 1] = n;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        cum[0] = 0;
+        for (int b = 0; b < B; b++) cum[b + 1] += cum[b];
+    }
+    __syncthreads();
+    const long long n_items = (long long)cum[B] * a.KV;             // kv head fastest: neighbours in memory go to neighbouring CTAs
+
+    if (warp == WARPS) {
+        // ---- the feeder
+        if (lane == 0) {
+            int b = 0;
+            long long it = 0;
+            for (long long item = blockIdx.x; item < n_items; item += gridDim.x, it++) {
+                const int st = (int)(it % STAGES);
+                const uint32_t parity = (uint32_t)((it / STAGES) & 1);
+                if (!mbar_wait(smem_u32(&bars[STAGES + st]), parity ^ 1u)) {
+                    atomicOr(status, MYNAH_ST_TIMEOUT);
+                    break;
+                }
+                const int g = (int)(item % a.KV);
+                const int pg = (int)(item / a.KV);
+                while (pg >= cum[b + 1]) b++;
+                const PageJob j = page_job<HD>(pg - cum[b], g, b, kv_len, pt, a, status, true);
+                StreamJob sj;
+                sj.b = b; sj.g = g; sj.k_first = j.k_first; sj.k_last = j.k_last; sj.empty = j.empty ? 1 : 0;
+                sj.partial = (j.k_first > 0 || j.k_last < KEYS - 1) ? 1 : 0;
+                sj.row0 = (unsigned long long)j.row0;
+                jobs[st] = sj;
+                const uint32_t full = smem_u32(&bars[st]);
+                if (j.empty) {
+                    mbar_arrive(full);
+                    continue;
+                }
+                const uint32_t k_dst = smem_u32(tiles + (size_t)st * 2 * TILE), v_dst = k_dst + TILE;
+                const uint32_t q_dst = smem_u32(q_area + (size_t)st * q_stride);
+                const uint32_t q_bytes = (uint32_t)(G * HD * 2);
+                mbar_expect_tx(full, 2 * TILE + q_bytes);
+                const int y = (j.page * a.KV + g) * PAGE_TOKENS;
+#pragma unroll
+                for (int h = 0; h < HD / 64; h++) {
+                    tma_load_2d(k_dst + h * (KEYS * 128), &map_k, h * 64, y, full);
+                    tma_load_2d(v_dst + h * (KEYS * 128), &map_v, h * 64, y, full);
+                }
+                const bf16* q_src = q + (size_t)b * a.ldq + (size_t)(g * G) * HD;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(q_dst), "l"(q_src), "r"(q_bytes), "r"(full) : "memory");
+            }
+        }
+        return;
+    }
+
+    // ---- the four warps that compute
+    long long it = 0;
+    for (long long item = blockIdx.x; item < n_items; item += gridDim.x, it++) {
+        const int st = (int)(it % STAGES);
+        const uint32_t parity = (uint32_t)((it / STAGES) & 1);
+        if (!mbar_wait(smem_u32(&bars[st]), parity)) {
+            if (tid == 0) atomicOr(status, MYNAH_ST_TIMEOUT);
+            break;
+        }
+        const StreamJob sj = jobs[st];
+        bool released = false;
+        PageJob job;
+        job.s = 0; job.g = sj.g; job.b = sj.b; job.page = 0;
+        job.k_first = sj.k_first; job.k_last = sj.k_last; job.row0 = (size_t)sj.row0; job.empty = sj.empty != 0;
+        if (job.empty) {
+            for (int i = tid; i < G; i += WARPS * 32) {
+                part_ml[(job.row0 + (size_t)i * a.S) * 2] = -INFINITY;
+                part_ml[(job.row0 + (size_t)i * a.S) * 2 + 1] = 0.f;
+            }
+        } else {
+            unsigned char* k_t = tiles + (size_t)st * 2 * TILE;
+            unsigned char* v_t = k_t + TILE;
+            if (sj.partial) {
+                for (int i = tid; i < KEYS * CH; i += WARPS * 32) {
+                    const int r = i / CH, c = i % CH;
+                    if (r < job.k_first || r > job.k_last)
+                        *reinterpret_cast<uint4*>(v_t + TileTma<HD>::off(r, c)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            // Q as the A operand, from the stage (rows beyond the group are zero)
+            uint32_t qa[HD / 16][4];
+            {
+                const bf16* q0 = reinterpret_cast<const bf16*>(q_area + (size_t)st * q_stride);
+                const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ks++) {
+                    const int col = ks * 16 + c0;
+                    qa[ks][0] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)r0 * HD + col) : 0u;
+                    qa[ks][1] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(r0 + 8) * HD + col) : 0u;
+                    qa[ks][2] = r0 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)r0 * HD + col + 8) : 0u;
+                    qa[ks][3] = r0 + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(r0 + 8) * HD + col + 8) : 0u;
+                }
+            }
+            if (sj.partial) SyncConsumers::sync();                 // the zeroed rows of V are in place
+            // this warp's fragments of both tiles into registers, and the stage goes back to the feeder at once: a
+            // stage that is being computed on is a stage without a copy in flight
+            uint32_t kf[HD / 16][4], vf[KEYS / 16][HD / 64][4];
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ks++) load_k_frag<HD, TileTma<HD>>(smem_u32(k_t), ks, kf[ks]);
+#pragma unroll
+            for (int ks = 0; ks < KEYS / 16; ks++)
+#pragma unroll
+                for (int nt = 0; nt < HD / 32; nt += 2) load_v_frag<HD, TileTma<HD>>(smem_u32(v_t), ks, nt, vf[ks][nt / 2]);
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[STAGES + st]));
+            released = true;
+            compute_page_core<HD, SyncConsumers>(
+                job, qa, a,
+                [&](int ks, uint32_t (&kb)[4]) { kb[0] = kf[ks][0]; kb[1] = kf[ks][1]; kb[2] = kf[ks][2]; kb[3] = kf[ks][3]; },
+                [&](int ks, int nt, uint32_t (&vb)[4]) { vb[0] = vf[ks][nt / 2][0]; vb[1] = vf[ks][nt / 2][1]; vb[2] = vf[ks][nt / 2][2]; vb[3] = vf[ks][nt / 2][3]; },
+                []() {}, []() { SyncConsumers::sync(); },
+                p_s, red_m, red_l, part_o, part_ml);
+        }
+        if (!released && lane == 0) mbar_arrive(smem_u32(&bars[STAGES + st]));
+        SyncConsumers::sync();                                     // the page's scratch (probabilities, sums) is free again
+    }
+}
+
+template <int HD>
+size_t stream_smem_bytes(int G, int stages, int B) {
+    return 1024 + (size_t)stages * 2 * KEYS * HD * 2 + (size_t)stages * stream_q_stride<HD>(G) + MAX_G * KEYS * 2 +
+           2 * WARPS * MAX_G * sizeof(float) + (size_t)stages * sizeof(StreamJob) + 2 * (size_t)stages * 8 + (size_t)(B + 1) * sizeof(int) + 16;
+}
+
+// 0: never, 1: where it pays (the default), 2: wherever it can run. MYNAH_ATTN_STREAM sets it at start,
+// mynah_attn_decode_stream_mode() later (tests compare the two routes).
+int g_stream_mode = -1;
+int stream_mode() {
+    if (g_stream_mode < 0) {
+        const char* e = getenv("MYNAH_ATTN_STREAM");
+        g_stream_mode = e != nullptr && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 1;
+    }
+    return g_stream_mode;
+}
+int stream_stages() {
+    static const int n = [] {
+        const char* e = getenv("MYNAH_ATTN_STREAM_STAGES");
+        return e != nullptr && e[0] == '3' ? 3 : 2;
+    }();
+    return n;
+}
+
+template <int HD, int STAGES>
+int launch_stream(const void* q, const void* k_cache, const void* v_cache, const int* kv_len, const PageTable& pt, const TcArgs& a,
+                  int B, int n_pages, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+    auto kern = attn_decode_stream_kernel<HD, STAGES>;
+    const int G = a.H / a.KV;
+    const size_t smem = stream_smem_bytes<HD>(G, STAGES, B);
+    static size_t allowed = 0;
+    if (smem > allowed) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return mynah_fail("attn_decode_tc (stream): %s", cudaGetErrorString(e));
+        allowed = smem;
+    }
+    CUtensorMap mk, mv;
+    if (tc5::make_map(&mk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * a.KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
+    if (tc5::make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * a.KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
+    const int per_sm = (int)((227 * 1024) / (smem + 1024));
+    const long long items = (long long)B * a.KV * a.S;
+    const long long want = (long long)mynah_sm_count() * (per_sm < 1 ? 1 : per_sm);
+    const unsigned grid = (unsigned)(items < want ? items : want);
+    mynah_launch(kern, dim3(grid), dim3(STREAM_THREADS), smem, stream, mk, mv, (const bf16*)q, kv_len, pt, a, B, part_o, part_ml, status);
+    return mynah_check_launch("attn_decode_tc (stream)");
+}
+
 }  // namespace
+
+// Chooses between the one-page CTAs and the streaming kernel for the pages of a decode step: 0 never the stream,
+// 1 where it pays, 2 wherever it can run. Returns the mode that was set before.
+MYNAH_API int mynah_attn_decode_stream_mode(int mode) {
+    const int before = stream_mode();
+    if (mode >= 0 && mode <= 2) g_stream_mode = mode;
+    return before;
+}
 
 // Whether the tensor-core kernel takes these sizes (bfloat16 only).
 MYNAH_API int mynah_attn_decode_tc_supported(int H, int KV, int HD) {
@@ -625,13 +916,30 @@ MYNAH_API int mynah_attn_decode_tc(
                          kv_len, pt, a, part_o, part_ml, status, counters, (bf16*)out, ldo);
         return mynah_check_launch("attn_decode_tc (merging)");
     }
-    if (HD == 128)
-        mynah_launch(attn_decode_tc_kernel<128, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                     kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
-    else
-        mynah_launch(attn_decode_tc_kernel<64, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                     kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
-    if (mynah_check_launch("attn_decode_tc")) return -1;
+    // The pages as a stream through persistent CTAs once there are many waves of one-page CTAs (six an SM); the
+    // partial results are the same bits either way. Measured at the 0.6B shape: 64 sequences of 2,060 positions
+    // 3.69 -> 3.63 ms a step, of 3,900 positions 6.03 -> 5.73; 16 sequences of 2,060 positions 1.74 -> 1.76 (so not there).
+    const long long n_ctas = (long long)n_splits * KV * B;
+    const bool as_stream = stream_mode() != 0 && B <= STREAM_MAX_SEQS && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
+                           ((uintptr_t)v_cache & 15) == 0 && (stream_mode() == 2 || n_ctas >= (long long)mynah_sm_count() * 6 * 16);
+    if (as_stream) {
+        int rc;
+        if (HD == 128)
+            rc = stream_stages() == 3 ? launch_stream<128, 3>(q, k_cache, v_cache, kv_len, pt, a, B, n_pages, part_o, part_ml, status, stream)
+                                      : launch_stream<128, 2>(q, k_cache, v_cache, kv_len, pt, a, B, n_pages, part_o, part_ml, status, stream);
+        else
+            rc = stream_stages() == 3 ? launch_stream<64, 3>(q, k_cache, v_cache, kv_len, pt, a, B, n_pages, part_o, part_ml, status, stream)
+                                      : launch_stream<64, 2>(q, k_cache, v_cache, kv_len, pt, a, B, n_pages, part_o, part_ml, status, stream);
+        if (rc) return rc;
+    } else {
+        if (HD == 128)
+            mynah_launch(attn_decode_tc_kernel<128, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                         kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
+        else
+            mynah_launch(attn_decode_tc_kernel<64, false>, grid, dim3(WARPS * 32), 0, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                         kv_len, pt, a, part_o, part_ml, status, (unsigned*)nullptr, (bf16*)nullptr, 0);
+        if (mynah_check_launch("attn_decode_tc")) return -1;
+    }
     const size_t dyn = (size_t)n_splits * sizeof(float);
     MYNAH_REQUIRE(dyn <= MERGE_MAX_BYTES, "attn_decode_tc: %d pages a sequence exceed what the merge holds", n_splits);
     if (HD == 128)

@@ -91,6 +91,34 @@ class Runtime:
         return self._counters
 
 
+class _Ahead:
+    """A second stream beside the step's own, on which the memory system is asked for the weights of the layer
+    after the running one (`kernels.l2_prefetch`). Inside a graph capture the events become edges of the graph:
+    the request for layer i+1 may start when layer i starts, and the step ends only when every request has."""
+
+    def __init__(self, device):
+        self.side = torch.cuda.Stream(device=device)
+        self.used = False
+
+    def issue(self, tensors) -> None:
+        if not tensors:
+            return
+        main = torch.cuda.current_stream()
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            kernels.l2_prefetch(tensors)
+        self.used = True
+
+    def join(self) -> None:
+        if self.used:
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+            torch.cuda.current_stream().wait_event(ev)
+            self.used = False
+
+
 class _Staging:
     """A few pinned buffers used in turn for the batch description, so that
     the host can write the next one while an earlier copy is still in flight."""
@@ -143,6 +171,10 @@ class _PromptGraph:
 # Measured at 33 pages a sequence: splits of 64 / 48 / 40 give 1.371 / 1.364 / 1.355 ms a step at batch 8 and
 # 3.97 / 3.88 / 3.84 at batch 64; every new size is a capture (a step run twice), so not finer than 16.
 PAGE_BUCKET_STEP = int(os.environ.get("MYNAH_PAGE_BUCKET_STEP", "16"))
+# Captured decode steps of at most this many rows ask for the next layer's weights ahead of time (0: never).
+# Measured at the 0.6B shape: one row 0.988 -> 0.969 ms a step; eight rows 1.355 -> 1.569 ms (the second stream's
+# edges into the chain cost more than the L2 hits save, and the attention's pages push the weights out again).
+L2_PREFETCH_MAX_ROWS = int(os.environ.get("MYNAH_L2_PREFETCH_MAX_ROWS", "2"))
 # Decode steps of at most this many rows are captured with programmatic dependent launch (0: none).
 PDL_MAX_ROWS = int(os.environ.get("MYNAH_PDL_MAX_ROWS", "2"))
 
@@ -201,6 +233,10 @@ class Engine:
         self._prompt_seen: dict[tuple, int] = {}
         self._prompt_clock = 0
         self.max_prompt_graphs = 6
+        self._ahead = _Ahead(self.device)
+        self._prefetching = False                  # set while a captured decode step's launches are made
+        self._layer_weights = [[t for p in self.model.layers[e.layer].parts() for t in p.streamed_tensors()]
+                               for e in self.model.schedule]
         self.launches = 0                          # kernels of this package launched (see count_launches)
         self.vocab_size = spec.vocab_size
 
@@ -300,10 +336,15 @@ class Engine:
         if taps is not None:
             taps["embed"] = x.clone()
         views = self.cache.views
+        ahead = self._ahead if self._prefetching else None
         for i, e in enumerate(self.model.schedule):
+            if ahead is not None and i + 1 < len(self.model.schedule):
+                ahead.issue(self._layer_weights[i + 1])
             self.model.layers[e.layer].forward(stream, ctx, views[i])
             if taps is not None:
                 taps[f"layer{i}"] = stream.flush().clone()
+        if ahead is not None:
+            ahead.join()
         h = self.model.final_norm.apply(stream, rows=want_rows, lazy=want_rows is None and taps is None)
         if taps is not None:
             taps["final_norm"] = h.float()
@@ -523,7 +564,11 @@ class Engine:
         return res
 
     def _decode_body(self, g: _DecodeGraph, mode: str) -> torch.Tensor:
-        logits = self._forward(g.ctx, None)
+        self._prefetching = g.bucket <= L2_PREFETCH_MAX_ROWS
+        try:
+            logits = self._forward(g.ctx, None)
+        finally:
+            self._prefetching = False
         if mode == "plain":
             return logits
         sampled = self.sampler.sample(logits, g.ctx.slots)

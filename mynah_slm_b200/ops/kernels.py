@@ -342,6 +342,13 @@ def attn_decode_tc_supported(dtype: torch.dtype, H: int, KV: int, HD: int) -> bo
     return dtype == torch.bfloat16 and bool(lib.load().mynah_attn_decode_tc_supported(H, KV, HD))
 
 
+def attn_decode_stream_mode(mode: int) -> int:
+    """How the tensor-core decode attention walks a step's pages: 0 one page a CTA, 2 persistent CTAs fed by TMA
+    wherever that can run, 1 (the default) whichever pays. Returns the mode set before; the results are the same
+    bits either way."""
+    return int(lib.load().mynah_attn_decode_stream_mode(int(mode)))
+
+
 def attn_decode_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, H: int, KV: int, HD: int,
                    k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor, pages: PageTableView,
                    window: int, n_splits: int, scratch: torch.Tensor, status: torch.Tensor,
@@ -457,3 +464,15 @@ def decode_advance(tokens: torch.Tensor, sampled: torch.Tensor, tok_pos: torch.T
                    slots: torch.Tensor) -> None:
     call("mynah_decode_advance", ptr(tokens), ptr(sampled), ptr(tok_pos), ptr(kv_len), ptr(slots),
          tokens.numel(), stream_ptr())
+
+
+def l2_prefetch(tensors) -> None:
+    """Ask the memory system to bring these tensors (contiguous, at most 8) into L2; returns at once and computes
+    nothing. Meant for a second stream beside a chain of kernels that will read the tensors shortly."""
+    import ctypes
+    ts = [t for t in tensors if t is not None and t.is_cuda and t.is_contiguous() and t.numel()]
+    for i in range(0, len(ts), 8):
+        part = ts[i:i + 8]
+        ptrs = (ctypes.c_void_p * len(part))(*[t.data_ptr() for t in part])
+        sizes = (ctypes.c_ulonglong * len(part))(*[t.numel() * t.element_size() for t in part])
+        call("mynah_l2_prefetch", ptrs, sizes, len(part), stream_ptr())

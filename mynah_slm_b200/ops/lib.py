@@ -80,6 +80,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_apply_penalties": [P, c_int, c_int, c_int, P, P, c_int, P, P, P],
     "mynah_decode_advance": [P, P, P, P, P, c_int, P],
     "mynah_sampler_accept": [P, c_int, P, P, P, c_int, P, P, P],
+    "mynah_l2_prefetch": [P, P, c_int, P],
     "mynah_randn_fill": [P, c_int, c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong, c_double, c_double, P],
 }
 
@@ -102,6 +103,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_device_arch.argtypes = []
     lib.mynah_attn_decode_scratch_floats.restype = c_longlong
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mynah_attn_decode_stream_mode.restype = c_int
+    lib.mynah_attn_decode_stream_mode.argtypes = [c_int]
     lib.mynah_attn_decode_tc_supported.restype = c_int
     lib.mynah_attn_decode_tc_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_gemm_qkv_rope_supported.restype = c_int

@@ -80,6 +80,9 @@ class GQAttention(Mixer):
         self.position.prepare(runtime)
         self.runtime = runtime
 
+    def streamed_tensors(self) -> list:
+        return [self.w_qkv, self.w_o]
+
     # -------------------------------------------------------------- cache
     def kv_request(self) -> KVRequest:
         return KVRequest(self.KV, self.HD, self.window)

@@ -117,6 +117,12 @@ class Part:
         """`tensors` holds exactly the tensors named by tensor_specs() that the
         checkpoint has, already on the device in their kept types."""
 
+    def streamed_tensors(self) -> list:
+        """The bound tensors that every step reads from end to end (the matrices of its products). The engine
+        may ask the memory system for them ahead of the part's turn; a part that names none is simply not
+        helped."""
+        return []
+
 
 class Norm(Part):
     def apply(self, stream: "Residual", rows: Optional[torch.Tensor] = None, lazy: bool = False):

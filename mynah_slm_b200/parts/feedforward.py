@@ -41,6 +41,9 @@ class SwiGLUDense(FeedForward):
         self.w_gate_up = torch.cat([tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors[p + "down_proj.weight"]
 
+    def streamed_tensors(self) -> list:
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         return kernels.linear(kernels.linear_swiglu(h, self.w_gate_up), self.w_down)
 

@@ -507,6 +507,72 @@ def test_attn_decode_tensor_cores(H, KV, HD, window):
     status.zero_()
 
 
+@pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (8, 1, 64, 100), (32, 8, 128, 0), (16, 1, 128, 0), (6, 2, 64, 70),
+                                             (4, 4, 128, 130), (64, 8, 64, 0)])
+def test_attn_decode_streamed_pages_give_the_same_bits(H, KV, HD, window):
+    """The pages of a step through persistent CTAs fed by TMA against the same pages one CTA each: the same bits in
+    every output row and in every partial result, with NaN bit patterns in the unused tails of the pages (the
+    stream copies whole tiles), empty sequences among the others, windows whose first page is cut, and more
+    sequences than CTAs."""
+    k = _k()
+    rng = np.random.default_rng(41)
+    lens = [1, 64, 65, 300, 0, 517, 128, 63, 2, 191] + rng.integers(1, 200, size=30).tolist()
+    B = len(lens)
+    n_pages = sum(-(-n // 64) for n in lens) + 3
+    free = list(np.random.default_rng(42).permutation(n_pages))
+    kc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    vc = torch.full((n_pages, KV, 64, HD), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lists, seqs = [], []
+    for n in lens:
+        kk, vv = _round(rng.standard_normal((n, KV, HD)), "bf16"), _round(rng.standard_normal((n, KV, HD)), "bf16")
+        pages = [int(free.pop()) for _ in range(-(-n // 64))]
+        lists.append(pages)
+        seqs.append((kk, vv))
+        for i, pg in enumerate(pages):
+            m = min(64, n - i * 64)
+            kc[pg, :, :m] = torch.from_numpy(kk[i * 64:i * 64 + m]).to(torch.bfloat16).to(DEV).transpose(0, 1)
+            vc[pg, :, :m] = torch.from_numpy(vv[i * 64:i * 64 + m]).to(torch.bfloat16).to(DEV).transpose(0, 1)
+    q = _round(rng.standard_normal((B, H, HD)), "bf16")
+    qd = torch.from_numpy(q.reshape(B, -1)).to(torch.bfloat16).to(DEV)
+    kvl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    splits = 12
+    outs, parts = {}, {}
+    before = k.attn_decode_stream_mode(0)
+    try:
+        for mode in (0, 2, 2):
+            k.attn_decode_stream_mode(mode)
+            out = torch.full((B, H * HD), 7.0, dtype=torch.bfloat16, device=DEV)
+            scratch = torch.zeros((k.attn_decode_scratch_floats(B, H, HD, splits),), dtype=torch.float32, device=DEV)
+            k.attn_decode_tc(qd, out, B, H, KV, HD, kc, vc, kvl, _page_table(lists)(n_pages), window, splits, scratch, status)
+            assert status.item() == 0
+            outs.setdefault(mode, []).append(out)
+            parts.setdefault(mode, []).append(scratch)
+    finally:
+        k.attn_decode_stream_mode(before)
+    assert torch.isfinite(outs[0][0].float()).all()
+    for again in outs[2]:
+        assert torch.equal(outs[0][0], again)
+    # the partial results of every visible page too (what lies beyond a sequence's visible pages is never read)
+    n_o = B * H * splits * HD
+    for again in parts[2]:
+        for b, n in enumerate(lens):
+            lo = max(0, n - window) if window else 0
+            n_vis = min(splits, (n - 1) // 64 + 1 - lo // 64) if n else 0
+            for t, width, off in ((parts[0][0], HD, 0), (parts[0][0], 2, n_o)):
+                one = t[off:off + B * H * splits * width].view(B, H, splits, width)[b, :, :n_vis]
+                other = again[off:off + B * H * splits * width].view(B, H, splits, width)[b, :, :n_vis]
+                assert torch.equal(one, other), (b, n, width)
+    got = outs[2][0].float().cpu().numpy()
+    for b, n in enumerate(lens):
+        if n == 0:
+            assert np.all(got[b] == 0)
+            continue
+        kk, vv = seqs[b]
+        ref = gqa_attention(q[b:b + 1], kk, vv, window=window or None, q_pos=[n - 1], k_pos=np.arange(n))
+        assert rel_err(ref.reshape(1, -1), got[b:b + 1]) < 1e-2, (b, n)
+
+
 def test_attn_decode_tensor_cores_one_far_key():
     k = _k()
     H, KV, HD, n = 4, 2, 128, 400
