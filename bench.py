@@ -193,6 +193,45 @@ def run_workload(which: str, layers_override: int = 0) -> int:
     return 0
 
 
+def run_reference(args) -> int:
+    """The unmodified reference on the same metric: 8 requests with 2,048-token prompts, one after another (it has
+    no batch), token by token (prompts too), on the host's CPU cores (it has no GPU path). See baseline/reference_arm.py."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm
+    except ImportError as e:
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py cannot be imported: {e}"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference runs on the host's CPU cores; there is nothing to run on several GPUs"}))
+        return 0
+    B, K, W = args.batch, max(1, min(args.steps, 32)), max(3, min(args.warmup, 4))
+    try:
+        r = reference_arm.run(dict(QWEN3_0_6B), B, PROMPT_LEN, W, K, budget_s=float(os.environ.get("MYNAH_REFERENCE_BUDGET_S", "900")))
+    except reference_arm.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(e).split())}))
+        return 0
+    except Exception as e:                                    # noqa: BLE001 - the arm must end with a line, not a trace
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference arm failed: {type(e).__name__}: {' '.join(str(e).split())[:300]}"}))
+        return 0
+    value = r["decode_tokens"] / r["decode_s"]
+    c = QWEN3_0_6B
+    print(json.dumps({
+        "metric": "decode tok/s at batch 8, 2,048-token prompts, 4,096 context (Qwen3-0.6B shape)", "value": round(value, 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(r["decode_s"] / K * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 arithmetic on fp16 weights",
+        "data": "synthetic: random weights (seed 2), uniform random token ids", "impl": "reference", "device": "cpu",
+        "config": {"model": "Qwen3-0.6B shape", "layers": c["num_hidden_layers"], "hidden": c["hidden_size"], "heads": c["num_attention_heads"],
+                   "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"], "ffn": c["intermediate_size"], "vocab": c["vocab_size"],
+                   "global_batch": B, "prompt_len": PROMPT_LEN, "seq_len": CTX_LEN, "sampling": "greedy",
+                   "parallelism": f"{r['threads']} CPU threads, the {B} requests one after another (the reference has no batch)"},
+        "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "prefill": {"value": round(r["prompt_tokens"] / r["prompt_s"], 2), "tokens": PROMPT_LEN, "ms": round(r["prompt_s"] / B * 1e3, 1)},
+    }))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,11 +249,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "mynah-slm is a C program built by make with no Python package to install "
-                          "(pip install of the checkout fails: no setup.py or pyproject.toml), and it has no GPU path, "
-                          "no batch and no safetensors loader, so it cannot run this metric on a B200"}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU only (this library does not use several); --gpus {args.gpus} is not run")
         return 2

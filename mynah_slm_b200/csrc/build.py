@@ -27,6 +27,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]
+# further flags for an experiment (e.g. -DMYNAH_PDL_LATE); they are part of the stamp, so a change rebuilds
+NVCC_FLAGS += os.environ.get("MYNAH_NVCC_EXTRA", "").split()
 
 
 class BuildError(RuntimeError):

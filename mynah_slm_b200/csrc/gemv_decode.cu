@@ -193,6 +193,9 @@ gemv_decode_kernel(GemvArgs a) {
                 }
             }
         }
+        // the weights of this CTA have been read: the kernel behind this one may start (it reads its own first
+        // weights while this one adds up and stores, and waits for these stores before it touches the rows)
+        if (gi == a.groups_per_cta - 1 || n0 + 8 >= a.N) griddep_launch_late();
         // ---- add the warps' partial sums in warp order
 #pragma unroll
         for (int e = 0; e < 4; e++) {
