@@ -97,7 +97,8 @@ def write_gguf(path: str, cfg: dict, seed: int) -> None:
     w.add_context_length(cfg["max_position_embeddings"])
     w.add_layer_norm_rms_eps(float(cfg["rms_norm_eps"]))
     w.add_rope_freq_base(float(cfg["rope_theta"]))
-    w.add_eos_token_id(int(cfg.get("eos_token_id", 0)))
+    eos = cfg.get("eos_token_id", 0)
+    w.add_eos_token_id(int(eos[0] if isinstance(eos, (list, tuple)) else eos or 0))
     names = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight", "lm_head.weight": "output.weight"}
     per_layer = {"input_layernorm.weight": "attn_norm.weight", "self_attn.q_proj.weight": "attn_q.weight",
                  "self_attn.k_proj.weight": "attn_k.weight", "self_attn.v_proj.weight": "attn_v.weight",
