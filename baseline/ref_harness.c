@@ -42,7 +42,9 @@ int main(int argc, char** argv) {
         return 2;
     }
     const int n_seqs = atoi(argv[2]), prompt_len = atoi(argv[3]), warmup = atoi(argv[4]), steps = atoi(argv[5]);
-    const int threads = atoi(argv[6]), probe = atoi(argv[7]);
+    const int threads = atoi(argv[6]);
+    int probe = atoi(argv[7]);
+    if (probe > prompt_len + warmup + steps) probe = prompt_len + warmup + steps;      /* the state holds no more */
     const double budget = atof(argv[8]);
     char err[512];
     mynah_slm_model_t* m = mynah_slm_load(argv[1], err, sizeof err);
