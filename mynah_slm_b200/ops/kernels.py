@@ -125,6 +125,13 @@ def _sm_count(device) -> int:
     return _SM_COUNT[device]
 
 
+def gemv_decode_mode(mode: int) -> int:
+    """How the decode products read their weights: 0 straight into registers, 1 through a ring of asynchronous copies
+    in shared memory, 2 (the default) whichever the shape does better with. Returns the mode set before; a row's
+    sums are the same bits either way."""
+    return int(lib.load().mynah_gemv_decode_mode(int(mode)))
+
+
 def gemv_decode_supported(M: int, N: int, K: int) -> bool:
     return bool(lib.load().mynah_gemv_decode_supported(M, N, K))
 
@@ -132,7 +139,7 @@ def gemv_decode_supported(M: int, N: int, K: int) -> bool:
 def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """x: bf16 rows [M, K] or a NormedInput. epilogue 0: bf16, 1: SwiGLU (w holds N gate rows then N up rows), 2: fp32."""
     K = w.shape[1]
-    if isinstance(x, NormedInput) and x._h is None and (x.shape[0] > FUSED_NORM_MAX_ROWS or K > FUSED_NORM_MAX_K):
+    if isinstance(x, NormedInput) and x._h is None and (x.shape[0] > FUSED_NORM_MAX_ROWS or not _norm_prologue_fits(x.shape[0], K)):
         x.materialize()
     if isinstance(x, NormedInput) and x._h is None:
         st = x.stream
@@ -172,7 +179,9 @@ def _fusable(x, w: torch.Tensor, N: int) -> bool:
 # 0.980 ms a step at batch 1) and more from two rows on (1.155 vs 1.045 ms at batch 2), so it is off; the
 # prologue stays in the kernel and in the tests.
 FUSED_NORM_MAX_ROWS = int(os.environ.get("MYNAH_FUSED_NORM_MAX_ROWS", "0"))
-FUSED_NORM_MAX_K = 12288    # the norm prologue keeps its rows in shared memory
+def _norm_prologue_fits(M: int, K: int) -> bool:
+    """The norm prologue keeps its rows (8 or 16 of them, padded) in shared memory beside the 80 KB ring of weights."""
+    return (16 if M > 8 else 8) * (K + 32) * 2 + 80 * 1024 <= 200 * 1024
 GEMV_MAX_OUT_ROWS = 32768   # wider products (the output head) stream better through the library for now
 
 

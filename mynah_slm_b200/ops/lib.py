@@ -103,6 +103,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_device_arch.argtypes = []
     lib.mynah_attn_decode_scratch_floats.restype = c_longlong
     lib.mynah_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mynah_gemv_decode_mode.restype = c_int
+    lib.mynah_gemv_decode_mode.argtypes = [c_int]
     lib.mynah_attn_decode_stream_mode.restype = c_int
     lib.mynah_attn_decode_stream_mode.argtypes = [c_int]
     lib.mynah_attn_decode_tc_supported.restype = c_int
