@@ -193,6 +193,58 @@ def run_workload(which: str, layers_override: int = 0) -> int:
     return 0
 
 
+def time_products(shape: str, rows: int) -> int:
+    """The four matrix products of a decode step of `rows` rows at a shape's layer sizes, each alone: the weights
+    through registers, through the ring of asynchronous copies, and the library's product. Enough different
+    matrices are cycled through that none is found in L2; the launches replay from a graph; CUDA events."""
+    import torch
+
+    from mynah_slm_b200.ops import kernels as k
+
+    cfg = dict(QWEN3_0_6B)
+    cfg.update(SHAPES[shape])
+    D, H, KV, HD, F = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["intermediate_size"]
+    dev = "cuda:0"
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 10 / n * 1e3
+
+    out = {"only": "products", "shape": shape, "rows": rows, "unit": "us (GB/s of weights)", "products": {}}
+    for name, N, K, swiglu in (("qkv", (H + 2 * KV) * HD, D, False), ("o", D, H * HD, False), ("gate_up", F, D, True), ("down", D, F, False)):
+        n_rows = N * (2 if swiglu else 1)
+        n = max(2, int(400e6 / (n_rows * K * 2)) + 1)
+        ws = [torch.randn(n_rows, K, device=dev).bfloat16() for _ in range(n)]
+        x = torch.randn(rows, K, device=dev).bfloat16()
+        mb = n_rows * K * 2 / 1e6
+        res = {}
+        for label, mode in (("registers", 0), ("ring", 1)):
+            k.gemv_decode_mode(mode)
+            f = (lambda: [k.linear_swiglu(x, w) for w in ws]) if swiglu else (lambda: [k.linear(x, w) for w in ws])
+            t = timed(f, n)
+            res[label] = f"{t:.1f} ({mb / t * 1e3:.0f})"
+        k.gemv_decode_mode(2)
+        t = timed(lambda: [torch.mm(x, w.t()) for w in ws], n)
+        res["library" + (" (no activation)" if swiglu else "")] = f"{t:.1f} ({mb / t * 1e3:.0f})"
+        out["products"][f"{name} {N}x{K}"] = res
+        del ws
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args) -> int:
     """The unmodified reference on the same metric: 8 requests with 2,048-token prompts, one after another (it has
     no batch), token by token (prompts too), on the host's CPU cores (it has no GPU path). See baseline/reference_arm.py."""
@@ -241,7 +293,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "products"],
                     help="run one small phase and print a short line (for profiling a kernel on a small case)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
@@ -266,6 +318,8 @@ def main() -> int:
 
     if args.workload:
         return run_workload(args.workload, args.layers)
+    if args.only == "products":
+        return time_products(args.shape, args.batch)
 
     cfg = dict(QWEN3_0_6B)
     if args.only:
@@ -379,12 +433,6 @@ def main() -> int:
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": graph.layout.size * 4,
            "d2h_bytes_per_step": B * 4}
 
-    # prefill of one prompt of 2,048 tokens (logits of the last position)
-    pre_ms = time_prefill()
-    flops = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
-    prefill = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-
     points, point_fracs = {}, {}
 
     def add_far(b: int, far_ms: dict) -> None:
@@ -400,6 +448,13 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b * steps / (pms / 1e3), 1)
             point_fracs[f"decode_b{b}"] = round(decode_bytes(cfg, layers, b, pctx) / (pms / steps / 1e3) / 1e9 / pk["hbm_gbs"], 4)
             add_far(b, pfar)
+
+    # prefill of one prompt of 2,048 tokens (logits of the last position); last, so that its load on the power budget
+    # does not sit in the clocks of the latency-bound decode points
+    pre_ms = time_prefill()
+    flops = model_flops_prefill(cfg, PREFILL_TOKENS, layers)
+    prefill = {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     out = {
         "metric": "decode tok/s at batch 8, 2,048-token prompts, 4,096 context (Qwen3-0.6B shape)",

@@ -158,8 +158,17 @@ def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -
     return out
 
 
+# Many outputs of long rows (the q/k/v and gate/up products of the 4B and 8B shapes): the library's kernels stream such
+# matrices at 5.4 to 5.6 TB/s where gemv_decode reaches 2.8 to 4.4 (`python bench.py --only products --shape 8b`), so
+# they are left to it, as the reference leaves its products to a library. 0 rows: never.
+GEMV_LIBRARY_FROM_ROWS = int(os.environ.get("MYNAH_GEMV_LIBRARY_FROM_ROWS", "6144"))
+GEMV_LIBRARY_FROM_K = 2048
+
+
 def _fusable(x, w: torch.Tensor, N: int) -> bool:
     if w.dtype != torch.bfloat16 or not w.is_contiguous():
+        return False
+    if GEMV_LIBRARY_FROM_ROWS and w.shape[0] >= GEMV_LIBRARY_FROM_ROWS and w.shape[1] >= GEMV_LIBRARY_FROM_K:
         return False
     if isinstance(x, NormedInput):
         if x.act_dtype != torch.bfloat16:
