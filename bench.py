@@ -245,6 +245,36 @@ def time_products(shape: str, rows: int) -> int:
     return 0
 
 
+def time_reader() -> int:
+    """What the device gives a plain reader of shuffled 16 KB pieces (2 GB, nothing done with them) for a given
+    number of bytes in flight an SM: the yardstick for the kernels that stream the cache and the weights."""
+    import numpy as np
+    import torch
+
+    from mynah_slm_b200.ops.lib import call, ptr, stream_ptr
+
+    dev = "cuda:0"
+    n = (2 << 30) // 16384
+    buf = torch.ones((n * 16384,), dtype=torch.uint8, device=dev)
+    order = torch.from_numpy(np.random.default_rng(1).permutation(n).astype(np.int32)).to(dev)
+    sink = torch.zeros((1,), dtype=torch.int64, device=dev)
+    status = torch.zeros((1,), dtype=torch.int32, device=dev)
+    out = {"only": "reader", "bytes": n * 16384, "unit": "GB/s", "rates": {}}
+    for ctas, stages in ((1, 4), (2, 4), (1, 12), (2, 6), (3, 4), (4, 3)):
+        call("mynah_read_probe", ptr(buf), ptr(order), n, ctas, stages, ptr(sink), ptr(status), stream_ptr())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            call("mynah_read_probe", ptr(buf), ptr(order), n, ctas, stages, ptr(sink), ptr(status), stream_ptr())
+        e1.record()
+        torch.cuda.synchronize()
+        out["rates"][f"{ctas * stages * 16} KB in flight an SM ({ctas} CTAs x {stages} copies)"] = round(n * 16384 * 5 / (e0.elapsed_time(e1) / 1e3) / 1e9)
+    assert status.item() == 0, "a wait in the reader ran out"
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args) -> int:
     """The unmodified reference on the same metric: 8 requests with 2,048-token prompts, one after another (it has
     no batch), token by token (prompts too), on the host's CPU cores (it has no GPU path). See baseline/reference_arm.py."""
@@ -293,7 +323,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "products"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "products", "reader"],
                     help="run one small phase and print a short line (for profiling a kernel on a small case)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
@@ -320,6 +350,8 @@ def main() -> int:
         return run_workload(args.workload, args.layers)
     if args.only == "products":
         return time_products(args.shape, args.batch)
+    if args.only == "reader":
+        return time_reader()
 
     cfg = dict(QWEN3_0_6B)
     if args.only:
