@@ -34,7 +34,14 @@ constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int MAX_M = 16;
 constexpr int XPAD = 32;              // elements of padding per row of x in shared memory (bank spread)
-constexpr int STAGES = 5;             // batches of a lane's weights in its ring (four in flight while one is multiplied)
+#ifndef MYNAH_GEMV_STAGES
+#define MYNAH_GEMV_STAGES 5
+#endif
+#ifndef MYNAH_GEMV_CTAS
+#define MYNAH_GEMV_CTAS 2
+#endif
+constexpr int STAGES = MYNAH_GEMV_STAGES;   // batches of a lane's weights in its ring (all but one in flight while that one is multiplied)
+constexpr int CTAS_PER_SM = MYNAH_GEMV_CTAS;
 constexpr int COPIES = 4;             // 16-byte copies a lane and batch: four blocks of a weight row, or two of a gate and two of an up row
 constexpr int RING_BYTES = THREADS * STAGES * COPIES * 16;
 
@@ -77,7 +84,7 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
 }
 
 template <int EPI, int MODE>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
 gemv_decode_kernel(GemvArgs a, int rows_bytes) {
     constexpr bool NORM = MODE == ROWS_NORM;
     constexpr bool STAGED = MODE != ROWS_DIRECT;
@@ -351,7 +358,7 @@ MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* 
     // ring carries a lane's copies across the end of a group, so few fat CTAs stream as well as many thin ones and
     // stage the input rows less often.
     const int groups = ceil_div(N, 8);
-    const int target = (sm_count > 0 ? sm_count : mynah_sm_count()) * 2;
+    const int target = (sm_count > 0 ? sm_count : mynah_sm_count()) * CTAS_PER_SM;
     const int n_ctas = groups < target ? groups : target;
     a.groups_per_cta = ceil_div(groups, n_ctas);
     const bool norm = x_res != nullptr;
