@@ -701,6 +701,41 @@ def test_attn_decode_fused_is_norm_rope_store_and_attention(H, KV, HD, window, w
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 30000, 1024), (2, 20, 64),
+                                   (8, 328, 2560), (2, 264, 9728), (7, 12, 32), (16, 2370, 4096), (1, 6, 12288), (9, 5000, 352)])
+def test_gemv_decode_both_forms_give_the_same_bits(M, N, K):
+    """The decode products with their weights through registers and through the ring of asynchronous copies: every
+    output has the same bits (the same sums in the same order), for plain rows, fp32 rows and the SwiGLU epilogue;
+    sizes that are no multiple of anything, one group of rows and many, rows too long to stage."""
+    k = _k()
+    rng = np.random.default_rng(N + K + M)
+    w = _round(rng.standard_normal((N, K)) * 0.05, "bf16")
+    x = _round(rng.standard_normal((M, K)), "bf16")
+    wd = torch.from_numpy(w).to(torch.bfloat16).to(DEV)
+    xd = torch.from_numpy(x).to(torch.bfloat16).to(DEV)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    outs = {}
+    before = k.gemv_decode_mode(0)
+    saved = k.GEMV_LIBRARY_FROM_ROWS
+    k.GEMV_LIBRARY_FROM_ROWS = 0                     # every size through this kernel
+    try:
+        for mode in (0, 1):
+            k.gemv_decode_mode(mode)
+            outs[mode] = (k.linear(xd, wd), k.linear(xd, wd, out_dtype=torch.float32),
+                          k.linear_swiglu(xd, wd) if N % 2 == 0 else None)
+    finally:
+        k.gemv_decode_mode(before)
+        k.GEMV_LIBRARY_FROM_ROWS = saved
+    for mode in (0, 1):
+        assert rel_err(ref, outs[mode][1].cpu().numpy()) < 2e-5, mode
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    if N % 2 == 0:
+        F = N // 2
+        gu = _round(ref, "bf16")
+        assert torch.equal(outs[0][2], outs[1][2])
+        assert rel_err(plain_swiglu(gu[:, :F], gu[:, F:]), outs[1][2].float().cpu().numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 1024), (3, 1000, 96), (8, 4096, 1024), (16, 1024, 3072), (5, 30000, 1024), (2, 20, 64),
                                    (8, 328, 2560), (2, 264, 9728)])      # rows of 41 KB: just under the opt-in limit; long rows
 def test_gemv_decode_fused_kernels(M, N, K):
     """The decode products with their fusions: plain rows, fp32 rows, the norm
