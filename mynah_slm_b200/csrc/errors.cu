@@ -54,3 +54,26 @@ MYNAH_API int mynah_set_pdl(int on) {
     g_pdl = on ? 1 : 0;
     return 0;
 }
+
+// A bounded wait that runs out, for tests of the host's handling of status bit 16: one thread waits for a word of
+// global memory that nothing sets, for at most `limit_ns` of wall clock (a few tens of microseconds), then sets
+// MYNAH_ST_TIMEOUT in `status` and returns. The same shape as the bounded waits of the tensor-core kernels
+// (a limit, a status bit, nothing left in flight), without any of their machinery.
+#include "layout.cuh"
+
+__global__ void wait_probe_kernel(const volatile int* flag, int* status, unsigned long long limit_ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (unsigned it = 0; it < (1u << 24); it++) {              // a bound on iterations as well as on time
+        if (*flag != 0) return;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > limit_ns) break;
+    }
+    atomicOr(status, MYNAH_ST_TIMEOUT);
+}
+
+MYNAH_API int mynah_wait_probe(const int* flag, int* status, unsigned long long limit_ns, cudaStream_t stream) {
+    MYNAH_REQUIRE(flag != nullptr && status != nullptr && limit_ns <= 1000000ull, "wait_probe: a flag, a status word and a limit of at most 1 ms");
+    wait_probe_kernel<<<1, 1, 0, stream>>>(flag, status, limit_ns);
+    return mynah_check_launch("wait_probe");
+}

@@ -522,3 +522,31 @@ def test_a_reused_slot_starts_with_an_empty_ring(folders):
     again = eng.open_sequence()
     assert again == first
     assert decode(eng, again, mine, 12) == want
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_engine_goes_on(folders, plain_models):
+    """Status bit 16: a bounded wait inside a kernel ran out. The wait here is a probe kernel's (a word of global
+    memory that nothing sets, a limit of 50 microseconds): it sets the bit in the product kernel's status word and
+    returns; `check_status` raises with the reason, clears the word, resets the product kernel's flags, and the next
+    steps give the right logits."""
+    from mynah_slm_b200.engine.engine import EngineError
+    from mynah_slm_b200.ops import gemm_bf16
+    from mynah_slm_b200.ops.lib import call, ptr, stream_ptr
+    key = ("B", torch.bfloat16)
+    eng = _engine(folders[key], "bfloat16", 256)
+    toks = prompts_for("B", [40], seed=2)[0]
+    slot = eng.open_sequence()
+    eng.step([_entry(slot, toks[:30], ())])
+    eng.check_status()                                            # nothing to report
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    call("mynah_wait_probe", ptr(flag), ptr(gemm_bf16.status_word(eng.device)), 50_000, stream_ptr())
+    with pytest.raises(EngineError, match="a bounded wait inside a kernel ran out"):
+        eng.check_status()
+    eng.check_status()                                            # cleared
+    got = eng.step([_entry(slot, toks[30:], range(10))]).cpu().numpy()
+    eng.check_status()
+    assert_close(plain_models[key].forward(toks)[30:], got, BF16_REL, "steps after a reported timeout")
+    # a flag that is set ends the wait without a report
+    flag.fill_(1)
+    call("mynah_wait_probe", ptr(flag), ptr(gemm_bf16.status_word(eng.device)), 50_000, stream_ptr())
+    eng.check_status()
