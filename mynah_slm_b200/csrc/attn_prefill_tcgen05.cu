@@ -146,6 +146,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched behind another kernel with programmatic dependent launch, everything above ran while that kernel was
+    // finishing (it read only the step's description, which no kernel writes); the queries and the cache are not
+    // touched before this returns. A no-op for an ordinary launch.
+    griddep_wait();
 
     // Tile j uses stage j & 1 of K, V and the scores; its barriers are in their (j >> 1)-th use.
     if (warp == 0) {
@@ -195,6 +199,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 v_issued = j + 1;
             }
+            griddep_launch_late();                             // all of this CTA's tiles have been asked for
             // whatever was started still lands in this CTA's shared memory: wait for it before leaving (bounded)
             mbar_wait(q_full, 0);
             for (int j = max(0, k_issued - 2); j < k_issued; j++) mbar_wait(k_full + 8 * (j & 1), (j >> 1) & 1);
@@ -396,7 +401,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         opted = true;
     }
     const dim3 grid(a.H, ceil_div(max_q_len, BQ), B);
-    kern<<<grid, THREADS, smem, stream>>>(mq, mk, mv, cu_q, kv_len, pt, a, out, status);
+    if (mynah_launch(kern, grid, dim3(THREADS), smem, stream, mq, mk, mv, cu_q, kv_len, pt, a, out, status) != cudaSuccess)
+        return mynah_fail("attn_prefill_tcgen05: %s", cudaGetErrorString(cudaGetLastError()));
     return mynah_check_launch("attn_prefill_tcgen05");
 }
 

@@ -224,6 +224,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (CTAS == 2) cluster_sync_all();                               // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched behind another kernel with programmatic dependent launch, everything above ran while that kernel was
+    // finishing; nothing it wrote is touched before this returns (a no-op for an ordinary launch).
+    griddep_wait();
 
     if (warp == 0) {
         if (lane == 0) {                                             // ---- TMA producer
@@ -264,6 +267,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            // every operand of this CTA has been asked for: what follows on the stream may begin its own set-up
+            griddep_launch_late();
             if (!ok && rank == 0) {
                 // copies that were started still land in shared memory: wait for them (bounded)
                 for (int j = max(0, it - STAGES); j < it; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1);
@@ -671,13 +676,22 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS * KS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (CTAS * KS == 2) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = CTAS * KS;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    if (mynah_pdl_enabled()) {                                       // the kernel's set-up may run under the kernel before it
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = CTAS * KS == 2 ? 1 : 0;
+    cfg.numAttrs = n_attr;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, g, status, qe);
     if (e != cudaSuccess) return mynah_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
     return mynah_check_launch("gemm_tcgen05");
