@@ -28,6 +28,8 @@
 // src/kernels.c:193-205.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 constexpr int WARPS = 8;
@@ -327,9 +329,16 @@ int mynah_gemv_decode_regs(const void* W, int N, int K, int M, const void* x_bf1
                            int sm_count, cudaStream_t stream);
 
 // 0: the weights through registers (gemv_decode_regs.cu), 1: through the ring, 2: whichever the shape does better with.
-static int g_gemv_mode = 2;
+static int g_gemv_mode = -1;
+static int gemv_mode() {
+    if (g_gemv_mode < 0) {
+        const char* e = getenv("MYNAH_GEMV_MODE");                   // 0, 1 or 2 at start; mynah_gemv_decode_mode() later
+        g_gemv_mode = e != nullptr && e[0] >= '0' && e[0] <= '2' ? e[0] - '0' : 2;
+    }
+    return g_gemv_mode;
+}
 MYNAH_API int mynah_gemv_decode_mode(int mode) {
-    const int before = g_gemv_mode;
+    const int before = gemv_mode();
     if (mode >= 0 && mode <= 2) g_gemv_mode = mode;
     return before;
 }
@@ -342,7 +351,7 @@ MYNAH_API int mynah_gemv_decode(const void* W, int N, int K, int M, const void* 
     {
         const size_t rb = (size_t)(M > 8 ? 16 : 8) * (K + XPAD) * 2;
         const bool ring_can = x_res == nullptr || rb + RING_BYTES <= 200 * 1024;
-        const bool use_ring = g_gemv_mode == 1 ? ring_can : g_gemv_mode == 0 ? false : ring_can && gemv_ring_pays(M, N, K, epilogue, sm_count);
+        const bool use_ring = gemv_mode() == 1 ? ring_can : gemv_mode() == 0 ? false : ring_can && gemv_ring_pays(M, N, K, epilogue, sm_count);
         if (!use_ring)
             return mynah_gemv_decode_regs(W, N, K, M, x_bf16, x_res, delta, x_res_out, gain, gain_dtype, eps, out, ldo, epilogue, sm_count, stream);
     }
