@@ -47,6 +47,19 @@ struct PfArgs {
     float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e)
 };
 
+// With -DMYNAH_ATTN_STAMPS the CTA of head 0 that walks the most key tiles writes its SM's cycle counter at fixed
+// points of every role's loop (a diagnostic build; mynah_attn_prefill_stamps copies the table out).
+#ifdef MYNAH_ATTN_STAMPS
+constexpr int STAMP_TILES = 32, STAMP_POINTS = 8;
+__device__ long long g_stamps[10][STAMP_TILES][STAMP_POINTS];
+#define STAMP(j, p)                                                                                  \
+    do {                                                                                             \
+        if (stamp_on && lane == 0 && (j) < STAMP_TILES) g_stamps[warp][(j)][(p)] = clock64();       \
+    } while (0)
+#else
+#define STAMP(j, p) do { } while (0)
+#endif
+
 // K-major operand, 128-byte swizzle, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
@@ -123,6 +136,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int n_tiles = kt_hi - kt_lo + 1;
     const int lo_min = a.window > 0 ? max(0, past + q0 - a.window + 1) : 0;    // the first key that any row of the tile sees
     const int kvh = h / (a.H / a.KV);
+#ifdef MYNAH_ATTN_STAMPS
+    const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -226,22 +242,27 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             for (int j = 0; j < n_tiles && ok; j++) {
                 const int st = j & 1;
+                STAMP(j, 0);
                 if (j + 1 < n_tiles) {                         // the next tile's scores, while the softmax works on this one.
                     // Their buffer held the probabilities of tile j-1; the product that read them was issued before.
                     ok = mbar_wait(k_full + 8 * (st ^ 1), ((j + 1) >> 1) & 1);
                     if (!ok) break;
                     tc_fence_after();
+                    STAMP(j, 1);
                     scores(j + 1);
                 }
+                STAMP(j, 2);
                 ok = mbar_wait(p_full + 8 * st, (j >> 1) & 1) && mbar_wait(v_full + 8 * st, (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
+                STAMP(j, 3);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++)             // 16 keys a step: 8 columns of packed probabilities, 16 rows of V
                     tc_mma_ts(t_o, tmem_base + st * BKV + k * 8, desc_mn_major(v_addr + st * TILE_BYTES + k * 16 * 128, HALF_BYTES),
                               idesc_o, (j | k) != 0);
                 tc_commit(v_free + 8 * st);
                 tc_commit(o_done);
+                STAMP(j, 4);
             }
             if (!ok) atomicOr(status, MYNAH_ST_TIMEOUT);
         }
@@ -263,21 +284,28 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t use = (j >> 1) & 1;
             const int key0 = (kt_lo + j) * BKV + grp * HALF_KEYS;     // this thread's first key
             const uint32_t t_s = t_row + st * BKV;
+            STAMP(j, 0);
             if (!warp_wait(s_full + 8 * st, use)) { ok = false; break; }
             tc_fence_after();
+            STAMP(j, 1);
             float s[HALF_KEYS];
 #pragma unroll
             for (int c = 0; c < HALF_KEYS / 32; c++) tc_ld32_nowait(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
 #pragma unroll
             for (int c = 0; c < HALF_KEYS / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+            STAMP(j, 2);
             // does any row of the tile have a key, among this group's, that it must not see?
             const bool need_mask = key0 + HALF_KEYS - 1 > past + q0 || key0 + HALF_KEYS > kvl ||
                                    (a.window > 0 && key0 < past + q0 + BQ - a.window);
-            if (need_mask) {
+            if (need_mask) {                                   // a compare with a constant and a select per score
+                const int hi = min(qpos, kvl - 1) - key0;      // the last of this thread's scores that its row sees
+                if (a.window > 0) {
+                    const int lo = lo_r - key0;
 #pragma unroll
-                for (int e = 0; e < HALF_KEYS; e++) {
-                    const int key = key0 + e;
-                    s[e] = (key <= qpos && key >= lo_r && key < kvl) ? s[e] : -INFINITY;
+                    for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && e >= lo) ? s[e] : -INFINITY;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < HALF_KEYS; e++) s[e] = e <= hi ? s[e] : -INFINITY;
                 }
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -288,8 +316,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // barrier of the next tile, and overwritten only after it)
             xch[(st * 2 + grp) * BQ + row] = mx_own;
             __syncwarp();
+            STAMP(j, 3);
             if (lane == 0) mbar_arrive(x_full + 8 * st);
             if (!warp_wait(x_full + 8 * st, use)) { ok = false; break; }
+            STAMP(j, 4);
             const float m_new = fmaxf(mx_own, xch[(st * 2 + (grp ^ 1)) * BQ + row]) * a.scale_log2;
             // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
             // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
@@ -326,9 +356,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
                 pk[e >> 1] = pack2(p0, p1);
             }
+            STAMP(j, 5);
             // over the scores: both groups have theirs in registers since the exchange above
             tc_st32(t_s + grp * (HALF_KEYS / 2), pk);
             tc_wait_st();
+            STAMP(j, 6);
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // Rows of V that were not brought (beyond the sequence's end, or a first page wholly before the window)
             // hold whatever was there: zero them, a probability of zero times a stale NaN would still be NaN.
@@ -348,6 +380,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * st);
+            STAMP(j, 7);
         }
         // the row sum over both groups, through the same exchange (its barriers are in use n_tiles by now)
         if (ok) {
@@ -407,6 +440,13 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 }
 
 }  // namespace
+
+#ifdef MYNAH_ATTN_STAMPS
+// out: [10 warps][32 tiles][8 points] of the stamped CTA's cycle counts (host memory).
+MYNAH_API int mynah_attn_prefill_stamps(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_stamps, sizeof(g_stamps)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 MYNAH_API int mynah_attn_prefill_tcgen05_supported(int H, int KV, int HD) {
     return (HD == 64 || HD == 128) && KV > 0 && H % KV == 0;

@@ -18,7 +18,8 @@ struct HeadLanes {
     static constexpr int HPW = 32 / LPH;          // heads a warp
 };
 
-// The lane's eight cosines and sines of the token's position (the first half's lanes and their partners read the same).
+// The lane's eight cosines and sines of the token's position. The first half's lanes and their partners read the
+// same entries; the first half's lanes get the sines negated, so that both halves rotate with one expression.
 template <int HD>
 __device__ __forceinline__ void load_rotation(const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pos, int lane,
                                               float (&c)[8], float (&sn)[8]) {
@@ -29,6 +30,10 @@ __device__ __forceinline__ void load_rotation(const float* __restrict__ cos_t, c
     const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
     c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
     sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    if ((lane % LPH) < LPH / 2) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) sn[j] = -sn[j];
+    }
 }
 
 // Eight consecutive gains (stored as fp32 or bfloat16) starting at element i0, a multiple of 8.
@@ -49,6 +54,7 @@ __device__ __forceinline__ void load_gain8(VecRef g, int i0, float (&out)[8]) {
 }
 
 // All 32 lanes must call this together (it shuffles); lanes without a head pass anything and ignore the result.
+// `c` and `sn` come from load_rotation.
 template <int HD>
 __device__ __forceinline__ void head_norm_rotate(float (&v)[8], bool norm, const float (&g)[8], float eps,
                                                  bool rotate, const float (&c)[8], const float (&sn)[8], int lane) {
@@ -64,11 +70,12 @@ __device__ __forceinline__ void head_norm_rotate(float (&v)[8], bool norm, const
         for (int j = 0; j < 8; j++) v[j] = v[j] * (sc * g[j]);
     }
     if (rotate) {
-        const bool first = (lane % LPH) < LPH / 2;
+        // first half: a c - b s; second half: b c + a s; `sn` carries the sign (load_rotation). One rounded
+        // product and one fused multiply-add, written out so that every user rounds alike.
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const float other = __shfl_xor_sync(0xffffffffu, v[j], LPH / 2);
-            v[j] = first ? v[j] * c[j] - other * sn[j] : v[j] * c[j] + other * sn[j];
+            v[j] = fmaf(other, sn[j], __fmul_rn(v[j], c[j]));
         }
     }
 }
@@ -80,6 +87,10 @@ struct Raw8 {
     __device__ __forceinline__ void load(const T* p) {
         q[0] = reinterpret_cast<const uint4*>(p)[0];
         if (sizeof(T) != 2) q[sizeof(T) == 2 ? 0 : 1] = reinterpret_cast<const uint4*>(p)[1];
+    }
+    __device__ __forceinline__ void store(T* p) const {
+        reinterpret_cast<uint4*>(p)[0] = q[0];
+        if (sizeof(T) != 2) reinterpret_cast<uint4*>(p)[1] = q[sizeof(T) == 2 ? 0 : 1];
     }
     __device__ __forceinline__ void to_f32(float (&v)[8]) const {
         if (sizeof(T) == 2) {

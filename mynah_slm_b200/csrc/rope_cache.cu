@@ -122,10 +122,10 @@ qk_norm_rope_store_kernel(TA* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
 // The same pass for head sizes 32, 64, 128 and 256 with the whole head rotated (or none of it): a head lies
 // across head_dim / 8 lanes, eight consecutive elements a lane, so a warp works on 32 / (head_dim / 8) heads
 // with every instruction, nothing goes through shared memory and every access is a 16-byte vector (two for
-// fp32). A warp takes `hpw` consecutive heads of one token, up to four such passes with their loads in flight
-// together; the token's position, page, rotation row and the gains are fetched once for all of them.
+// fp32). A warp takes `hpw` consecutive heads of one token, four passes at a time with their loads in flight
+// together; the token's position, page and rotation row are fetched once for all of them.
 template <typename T, int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, sizeof(T) == 2 ? 7 : 4)
 qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain,
                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
@@ -158,13 +158,9 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
         if (lane == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
         return;
     }
-    float c[8], sn[8], qg[8], kg[8];
+    float c[8], sn[8];
     if (rotate) load_rotation<HD>(cos_t, sin_t, pos, lane, c, sn);
     const bool has_gain = q_gain.p != nullptr;
-    if (has_gain) {
-        load_gain8(q_gain, li * 8, qg);
-        load_gain8(k_gain, li * 8, kg);
-    }
     size_t cache_row = 0;
     if (h1 > a.H) {                                        // some head of this warp goes to the cache
         const int page = page_of(pt, seq, pos);
@@ -187,6 +183,10 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
             if (hb + i * HPW >= h1) break;                 // uniform over the warp
             const int h = hb + i * HPW + sub;              // this lane group's head (may lie beyond the warp's heads)
             const bool mine = h < h1;
+            if (hb + i * HPW >= a.H + a.KV) {              // uniform: a pass of V heads only is a copy of 16 bytes a lane
+                if (mine) in[i].store(v_cache + (cache_row + (size_t)(h - a.H - a.KV) * PAGE_TOKENS) * HD + li * 8);
+                continue;
+            }
             const bool is_q = h < a.H, is_k = !is_q && h < a.H + a.KV;
             float v[8];
             in[i].to_f32(v);                               // (a lane group without a head works on whatever is there)
@@ -195,7 +195,9 @@ qk_norm_rope_store_fast_kernel(T* __restrict__ qkv, VecRef q_gain, VecRef k_gain
                 store8<T>(v_cache + (cache_row + (size_t)kvh * PAGE_TOKENS) * HD + li * 8, v);
             }
             // every lane takes part in the norm and the rotation; what is not a q or k head is dropped afterwards
-            head_norm_rotate<HD>(v, has_gain, is_q ? qg : kg, a.eps, rotate, c, sn, lane);
+            float g[8];                                    // the head's gains: a few hundred bytes that stay in L1
+            if (has_gain) load_gain8(is_q ? q_gain : k_gain, li * 8, g);
+            head_norm_rotate<HD>(v, has_gain, g, a.eps, rotate, c, sn, lane);
             if (mine && is_q) store8<T>(row + (size_t)h * HD, v);
             else if (mine && is_k) store8<T>(k_cache + (cache_row + (size_t)(h - a.H) * PAGE_TOKENS) * HD + li * 8, v);
         }
@@ -206,12 +208,14 @@ template <typename T>
 bool launch_fast(int HD, cudaStream_t stream, T* qkv, VecRef qg, VecRef kg, const float* cos_t,
                  const float* sin_t, const int* tok_seq, const int* tok_pos, PageTable pt, T* kc, T* vc, QkvArgs a, int* status) {
     if (HD != 32 && HD != 64 && HD != 128 && HD != 256) return false;
-    // heads per warp: one pass while the step is small (latency matters), up to four passes when there are many tokens
+    // heads per warp: one pass while the step is small (latency matters), up to eight passes when there are many tokens
+    // (a warp's set-up, the token's position, page and rotation row, is then shared by more heads: 2,048 tokens of 32
+    // heads of 128 take 19.3, 13.9, 11.8, 10.8 and 13.2 us with 1, 2, 4, 8 and 16 passes)
     const int heads = kc != nullptr ? a.H + 2 * a.KV : a.H;
     const int per_pass = 32 / (HD / 8);
     const long long units1 = (long long)a.T * ((heads + per_pass - 1) / per_pass);
     int passes = 1;
-    while (passes < 4 && units1 / passes > (long long)mynah_sm_count() * 16) passes *= 2;
+    while (passes < 8 && units1 / passes > (long long)mynah_sm_count() * 16) passes *= 2;
     const int hpw = per_pass * passes;
     const int groups = (heads + hpw - 1) / hpw;
     const unsigned blocks = (unsigned)ceil_div_ll((long long)a.T * groups, WARPS);
