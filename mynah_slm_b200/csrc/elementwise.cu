@@ -5,6 +5,7 @@
 // scale are fp32; the order of every sum is fixed by the thread layout, so a
 // row's result does not depend on which other rows share the launch.
 #include "common.cuh"
+#include "head_prep.cuh"
 
 // ------------------------------------------------------------- embedding
 // x[t, :] = E[token_t, :]           (mynah-slm src/arch_qwen3.c:186: no scaling)
@@ -108,12 +109,59 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict_
     }
 }
 
+// Eight consecutive elements per thread: the row, the pending delta, the gains and the result all move as 16-byte
+// vectors. Taken when D is a multiple of 8 and fits (D <= 8 * 1024), for any number of rows, so that a row's sum
+// has the same order in every step.
+template <typename TA>
+__global__ void rmsnorm_vec8_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
+                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+    __shared__ float red[32];
+    griddep_launch_small();
+    griddep_wait();
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = x + (size_t)r * D;
+    const int i = threadIdx.x * 8;
+    const bool on = i < D;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (on) {
+        load8(xr + i, v);
+        if (delta) {
+            float d[8];
+            load8(delta + (size_t)r * D + i, d);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] += d[j];
+            if (rows == nullptr) store8(xr + i, v);        // (selected rows may repeat: x is only read)
+        }
+    }
+    float ss = ((v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3])) + ((v[4] * v[4] + v[5] * v[5]) + (v[6] * v[6] + v[7] * v[7]));
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)D + eps);
+    if (on) {
+        float g[8];
+        load_gain8(w, i, g);
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = (v[j] * s) * g[j];
+        store8(out + (size_t)blockIdx.x * D + i, v);
+    }
+}
+
 MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, const int* rows,
                             void* out, int act_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     MYNAH_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: bad sizes rows=%d D=%d", n_rows, D);
     MYNAH_REQUIRE(w_dtype == MYNAH_F32 || w_dtype == MYNAH_BF16, "rmsnorm: unsupported gain dtype %d", w_dtype);
     const VecRef wr{w, w_dtype};
+    const bool aligned16 = (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (D % 8 == 0 && D <= 8192 && D >= 256 && aligned16) {
+        const int threads = ((D / 8 + 31) / 32) * 32;
+        if (act_dtype == MYNAH_F32)
+            mynah_launch(rmsnorm_vec8_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
+        else if (act_dtype == MYNAH_BF16)
+            mynah_launch(rmsnorm_vec8_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+        else
+            return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
+        return mynah_check_launch("rmsnorm");
+    }
     if (D % 4 == 0 && D <= 4096 && D >= 128) {
         const int threads = ((D / 4 + 31) / 32) * 32;
         if (act_dtype == MYNAH_F32)
