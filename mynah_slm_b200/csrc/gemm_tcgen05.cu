@@ -160,6 +160,46 @@ struct ItemIter {
 // tiles, which need fewer operand bytes a flop than the 128-wide ones. When both have accumulated, each sends
 // the 128 accumulator columns that the other will finish to the other's idle operand ring (fp32, through
 // distributed shared memory), adds what it received to its own 128 columns and stores them.
+// With -DMYNAH_GEMM_STAMPS the first CTA of a launch writes its SM's cycle counter at fixed points of every role's
+// loop (a diagnostic build; mynah_gemm_tcgen05_stamps copies the table out).
+#ifdef MYNAH_GEMM_STAMPS
+constexpr int GS_ITEMS = 16, GS_POINTS = 4;
+__device__ long long g_gemm_stamps[8][GS_ITEMS][GS_POINTS];
+__device__ long long g_gemm_spans[1024][2];                          // every CTA's entry and exit on the global timer (ns)
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GSTAMP(role, item, p)                                                                               \
+    do {                                                                                                    \
+        if (blockIdx.x == 0 && (item) < GS_ITEMS) g_gemm_stamps[(role)][(item)][(p)] = clock64();          \
+    } while (0)
+#else
+#define GSTAMP(role, item, p) do { } while (0)
+#endif
+
+// mbar_wait that also gives up when another role of the CTA has: the flag is looked at only once polls have
+// failed, so a wait that finds its phase complete costs one try_wait.
+__device__ __forceinline__ bool mbar_wait_abort(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0;; it++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = now_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+
 template <int BN, int EPI, int CTAS, int KS = 1, bool SK = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -182,6 +222,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t fix_bar0 = smem_u32(bars + 2 * STAGES + 5);       // SK: one per epilogue warp, used once
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) GSTAMP(7, 0, 0);                             // entry
+#ifdef MYNAH_GEMM_STAMPS
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_gemm_spans[blockIdx.x][0] = global_ns();
+#endif
     const int nk = (g.K + BK - 1) / BK;
     const int total_tiles = g.m_tiles * g.n_tiles;
     if (EPI == EPI_QKV && threadIdx.x < HD) {                        // the gains, once (ones when there is no per-head norm)
@@ -227,6 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // Launched behind another kernel with programmatic dependent launch, everything above ran while that kernel was
     // finishing; nothing it wrote is touched before this returns (a no-op for an ordinary launch).
     griddep_wait();
+    if (threadIdx.x == 0) GSTAMP(7, 0, 1);                             // set up
 
     if (warp == 0) {
         if (lane == 0) {                                             // ---- TMA producer
@@ -234,12 +279,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             ItemIter<SK> items(nk, unit, n_units, total_tiles, kb_begin, kb_end);
             Item w;
+            int n_item = 0;
             while (ok && items.next(w)) {
                 const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
+                GSTAMP(0, n_item, 0);
+                n_item++;
                 for (int kb = w.kb0; kb < w.kb1; kb++, it++) {
+                    if (kb == w.kb1 - 1) GSTAMP(0, n_item - 1, 1);
+                    if (kb == w.kb0 + 3) GSTAMP(0, n_item - 1, 2);     // the fourth k-block's turn: the ring was empty until here
+                    if (kb == w.kb0 + 8) GSTAMP(0, n_item - 1, 3);
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1) || *abort_flag) {
+                    if (it >= STAGES && !mbar_wait_abort(empty0 + 8 * s, ph ^ 1, abort_flag)) {   // (the ring starts empty)
                         *abort_flag = 1;
                         atomicOr(status, MYNAH_ST_TIMEOUT);
                         ok = false;
@@ -255,8 +306,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         tma_load_2d_pair(b_dst, &map_b, kb * BK, w_row, full0 + 8 * s);
                         continue;
                     }
+                    if (it == 1) GSTAMP(3, 0, 0);
                     mbar_expect_tx(full0 + 8 * s, STAGE);
+                    if (it == 1) GSTAMP(3, 0, 1);
                     tma_load_2d(a_dst, &map_a, kb * BK, m_tile * BM, full0 + 8 * s);
+                    if (it == 1) GSTAMP(3, 0, 2);
                     if (EPI == EPI_SWIGLU) {                         // 128 gate rows, then their 128 up rows
                         tma_load_2d(b_dst, &map_b, kb * BK, n_tile * 128, full0 + 8 * s);
                         tma_load_2d(b_dst + 128 * BK * 2, &map_b, kb * BK, g.up_offset + n_tile * 128, full0 + 8 * s);
@@ -265,6 +319,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < BN / 128; j++)
                             tma_load_2d(b_dst + j * 128 * BK * 2, &map_b, kb * BK, n_tile * BN + j * 128, full0 + 8 * s);
                     }
+                    if (it == 1) GSTAMP(3, 0, 3);
                 }
             }
             // every operand of this CTA has been asked for: what follows on the stream may begin its own set-up
@@ -284,23 +339,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (; ok && items.next(w); local++) {
                 const int buf = local & 1;
                 const uint32_t use = (local >> 1) & 1;
-                if (!mbar_wait(acc_empty0 + 8 * buf, use ^ 1) || *abort_flag) {   // the epilogue has read this buffer out
+                if (local >= 2 && !mbar_wait_abort(acc_empty0 + 8 * buf, use ^ 1, abort_flag)) {   // the epilogue has read this buffer out
                     *abort_flag = 1;
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
                 }
                 tc_fence_after();
+                GSTAMP(1, local, 0);
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = w.kb0; kb < w.kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(full0 + 8 * s, ph) || *abort_flag) {
+                    if (!mbar_wait_abort(full0 + 8 * s, ph, abort_flag)) {
                         *abort_flag = 1;
                         atomicOr(status, MYNAH_ST_TIMEOUT);
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    if (kb == w.kb0) GSTAMP(1, local, 1);
                     const uint32_t a_addr = smem_u32(smem + s * STAGE), b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
@@ -312,15 +369,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 // arrives when the tile is accumulated
                 if (CTAS == 2) tc_commit_pair(acc_full0 + 8 * buf); else tc_commit(acc_full0 + 8 * buf);
+                GSTAMP(1, local, 2);
             }
         }
     } else if (KS == 2) {                                            // ---- epilogue warps, K split: the tile is accumulated (this half)
-        if (unit < total_tiles && (!mbar_wait(acc_full0, 0) || *abort_flag)) {
+        if (unit < total_tiles && !mbar_wait_abort(acc_full0, 0, abort_flag)) {
             if (lane == 0) {
                 *abort_flag = 1;
                 atomicOr(status, MYNAH_ST_TIMEOUT);
             }
         }
+        if (warp == 2 && lane == 0) GSTAMP(2, 0, 0);
     } else {                                                         // ---- epilogue: warps 2..5 -> lane quadrants 2,3,0,1
         const int quad = warp & 3;
         unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
@@ -331,7 +390,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
             const int buf = local & 1;
             const uint32_t use = (local >> 1) & 1;
-            if (!mbar_wait(acc_full0 + 8 * buf, use) || *abort_flag) {
+            if (!mbar_wait_abort(acc_full0 + 8 * buf, use, abort_flag)) {
                 if (lane == 0) {
                     *abort_flag = 1;
                     atomicOr(status, MYNAH_ST_TIMEOUT);
@@ -339,6 +398,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 break;
             }
             tc_fence_after();
+            if (warp == 2 && lane == 0) GSTAMP(2, local, 0);
             const uint32_t t_row = tmem_base + buf * BN + ((uint32_t)(quad * 32) << 16);
             const int row0 = (m_tile * CTAS + rank) * BM + quad * 32;
             if (SK && w.produce) {
@@ -549,8 +609,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int p = 1; p <= w.follow; p++) g.sk_flag[(unit + p) * 4 + quad] = 0;
                 if (CTAS == 2) mbar_arrive_leader(acc_empty0 + 8 * buf); else mbar_arrive(acc_empty0 + 8 * buf);
             }
+            if (warp == 2 && lane == 0) GSTAMP(2, local, 1);
         }
         if (lane == 0) tma_store_wait_all();
+        if (warp == 2 && lane == 0) GSTAMP(2, 0, 2);
     }
     if (KS == 2) {
         // Both CTAs are past their last product (or gave up): their operand rings are idle and may be written.
@@ -575,7 +637,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     st_cluster_v4(there + (uint32_t)(((c * 8 + j) ^ (lane & 7)) * 16), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
             }
         }
+        if (warp == 2 && lane == 0) GSTAMP(2, 0, 1);
         cluster_sync_all();                                          // what the other CTA sent has arrived
+        if (warp == 2 && lane == 0) GSTAMP(2, 0, 2);
         if (work) {
             const int m_tile = unit % g.m_tiles, n_tile = unit / g.m_tiles;
             const int row0 = m_tile * BM + quad * 32;
@@ -609,10 +673,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
             if (lane == 0) tma_store_wait_all();
+            if (warp == 2 && lane == 0) GSTAMP(2, 0, 3);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) GSTAMP(7, 0, 2);                             // all roles done
+#ifdef MYNAH_GEMM_STAMPS
+    if (threadIdx.x == 0 && blockIdx.x < 1024) g_gemm_spans[blockIdx.x][1] = global_ns();
+#endif
     if (CTAS == 2) cluster_sync_all();                               // neither CTA leaves while the other may still touch it
     if (warp == 1) {
         tc_fence_after();
@@ -620,6 +689,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
+
+#ifdef MYNAH_GEMM_STAMPS
+// out: [8 roles][16 items][4 points] of the stamped CTA's cycle counts (host memory).
+MYNAH_API int mynah_gemm_tcgen05_stamps(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_gemm_stamps, sizeof(g_gemm_stamps)) == cudaSuccess ? 0 : -1;
+}
+// out: [1024 CTAs][entry, exit] in nanoseconds of the device's global timer.
+MYNAH_API int mynah_gemm_tcgen05_spans(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_gemm_spans, sizeof(g_gemm_spans)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 // The stream-K workspace of the current device: a slot of 128 x 256 floats and four flags a CTA, allocated at the
 // first launch that needs it (never during a graph capture: a captured step has run once before).

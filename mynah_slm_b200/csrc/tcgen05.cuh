@@ -25,8 +25,10 @@ static __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for the phase with the given parity. False when the limit ran out.
+// The global timer is read only after 256 polls have failed (a read of it costs hundreds of cycles, and most
+// waits find their phase complete at once or after a few polls): the limit counts from then.
 static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    const unsigned long long t0 = now_ns();
+    unsigned long long t0 = 0;
     for (uint32_t it = 0;; it++) {
         uint32_t done;
         asm volatile(
@@ -35,7 +37,11 @@ static __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) 
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
-        if ((it & 255u) == 255u && now_ns() - t0 > WAIT_LIMIT_NS) return false;
+        if ((it & 255u) == 255u) {
+            const unsigned long long now = now_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) return false;
+        }
     }
 }
 static __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
