@@ -27,6 +27,7 @@
 // (mynah-slm src/arch_qwen3.c:51-52); norm as src/kernels.c:118-128; SwiGLU as
 // src/kernels.c:193-205.
 #include "common.cuh"
+#include "gemv_norm_rows.cuh"
 
 #include <stdlib.h>
 
@@ -150,41 +151,8 @@ gemv_decode_kernel(GemvArgs a, int rows_bytes) {
 
     // ---- the input rows, in bf16, into shared memory
     if (NORM) {
-        // teams of warps share a row: all 8 warps on one row when M = 1, one warp per row from M = 8 on
-        __shared__ float part[WARPS];
-        int mp = 1;
-        while (mp < M && mp < WARPS) mp <<= 1;
-        const int wpr = WARPS / mp;                                  // warps per row
-        const int sub = warp % wpr;                                  // this warp's place in its team
-        for (int m0 = 0; m0 < M; m0 += mp) {
-            const int m = m0 + warp / wpr;
-            const bool on = m < M;
-            const float* xr = a.x_res + (size_t)(on ? m : 0) * K;
-            const bf16* dr = a.delta ? a.delta + (size_t)(on ? m : 0) * K : nullptr;
-            float ss = 0.f;
-            if (on)
-                for (int i = sub * 32 + lane; i < K; i += wpr * 32) {
-                    float v = xr[i];
-                    if (dr) v += to_f32(dr[i]);
-                    ss += v * v;
-                }
-            ss = warp_sum(ss);
-            __syncthreads();
-            if (lane == 0) part[warp] = ss;
-            __syncthreads();
-            float tot = 0.f;
-            for (int w = 0; w < wpr; w++) tot += part[(warp / wpr) * wpr + w];   // fixed order
-            const float s = 1.0f / sqrtf(tot / (float)K + a.eps);
-            if (on)
-                for (int i = sub * 32 + lane; i < K; i += wpr * 32) {
-                    float v = xr[i];
-                    if (dr) {
-                        v += to_f32(dr[i]);
-                        if (blockIdx.x == 0) a.x_res_out[(size_t)m * K + i] = v;
-                    }
-                    xs[m * ldx + i] = __float2bfloat16_rn((v * s) * a.gain.at(i));
-                }
-        }
+        const NormRowsArgs nr{a.x_res, a.delta, a.x_res_out, a.gain, a.eps, M, K};
+        norm_rows_to_smem<WARPS>(nr, xs, ldx, warp, lane);
     } else if (STAGED) {
         for (int i = tid; i < M * (K / 8); i += THREADS) {
             const int m = i / (K / 8), c = i % (K / 8);
