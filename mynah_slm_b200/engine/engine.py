@@ -406,6 +406,8 @@ class Engine:
         g = self._prompt_graphs.get(key)
         if g is None:
             seen = self._prompt_seen.get(key, 0)
+            if len(self._prompt_seen) >= 1024:                # a book of shapes seen once: never larger than this
+                self._prompt_seen.clear()
             self._prompt_seen[key] = seen + 1
             if seen == 0:
                 return None                                   # once: run as it is; twice: worth a graph
