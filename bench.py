@@ -223,17 +223,29 @@ def time_products(shape: str, rows: int) -> int:
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / 10 / n * 1e3
 
-    out = {"only": "products", "shape": shape, "rows": rows, "unit": "us (GB/s of weights)", "products": {}}
+    out = {"only": "products", "shape": shape, "rows": rows, "unit": "us (GB/s of weights)" if rows <= 16 else "us (TFLOP/s)", "products": {}}
     for name, N, K, swiglu in (("qkv", (H + 2 * KV) * HD, D, False), ("o", D, H * HD, False), ("gate_up", F, D, True), ("down", D, F, False)):
         n_rows = N * (2 if swiglu else 1)
         n = max(2, int(400e6 / (n_rows * K * 2)) + 1)
+        if rows > 16:
+            n = min(n, 4)                                           # (the rows and the results are the larger part here)
         ws = [torch.randn(n_rows, K, device=dev).bfloat16() for _ in range(n)]
         x = torch.randn(rows, K, device=dev).bfloat16()
         mb = n_rows * K * 2 / 1e6
         res = {}
+        f = (lambda: [k.linear_swiglu(x, w) for w in ws]) if swiglu else (lambda: [k.linear(x, w) for w in ws])
+        if rows > 16:
+            # a prompt step's product: the package's route (the tensor-core kernel from 129 rows on) against the library
+            tf = 2.0 * rows * n_rows * K / 1e6                      # flop / 1e6: with us, TFLOP/s
+            t = timed(f, n)
+            res["own"] = f"{t:.1f} ({tf / t:.0f} TFLOP/s)"
+            t = timed(lambda: [torch.mm(x, w.t()) for w in ws], n)
+            res["library" + (" (no activation)" if swiglu else "")] = f"{t:.1f} ({tf / t:.0f} TFLOP/s)"
+            out["products"][f"{name} {N}x{K}"] = res
+            del ws
+            continue
         for label, mode in (("registers", 0), ("ring", 1)):
             k.gemv_decode_mode(mode)
-            f = (lambda: [k.linear_swiglu(x, w) for w in ws]) if swiglu else (lambda: [k.linear(x, w) for w in ws])
             t = timed(f, n)
             res[label] = f"{t:.1f} ({mb / t * 1e3:.0f})"
         k.gemv_decode_mode(2)
