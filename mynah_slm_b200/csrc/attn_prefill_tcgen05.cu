@@ -42,7 +42,7 @@ constexpr int THREADS = 320;          // warp 0 TMA, warp 1 MMA, warps 2-9 softm
 constexpr int HALF_BYTES = 128 * 128; // 128 rows of 128 bytes: one 64-column half of a tile
 
 struct PfArgs {
-    int H, KV, ldo;
+    int B, H, KV, ldo;
     int window;
     float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e)
 };
@@ -52,6 +52,8 @@ struct PfArgs {
 #ifdef MYNAH_ATTN_STAMPS
 constexpr int STAMP_TILES = 32, STAMP_POINTS = 8;
 __device__ long long g_stamps[10][STAMP_TILES][STAMP_POINTS];
+constexpr int SPAN_CTAS = 1 << 16;
+__device__ long long g_spans[SPAN_CTAS][2];                          // every CTA's entry and exit on the global timer (ns)
 #define STAMP(j, p)                                                                                  \
     do {                                                                                             \
         if (stamp_on && lane == 0 && (j) < STAMP_TILES) g_stamps[warp][(j)][(p)] = clock64();       \
@@ -123,12 +125,43 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float* xch = reinterpret_cast<float*>(bars + 16);          // [2 buffers][2 groups][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // CTAs start in the order x, y, z: all heads of the last (longest) query tile first, then the tile before, ...
-    const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
-    const int h = blockIdx.x, b = blockIdx.z;
+    // The query tiles of all sequences are numbered one after another, sequence by sequence, a sequence's last
+    // (longest) tile first; blockIdx.y is such a number. The grid has as many as the step's rows can make at most
+    // (rows / 128 + sequences: a captured step knows its rows, not how they are divided), so the numbers beyond the
+    // step's tiles leave at once. Warp 0 finds the tile's sequence with a prefix sum over the sequences' tile counts.
+    __shared__ int found_s[2];
+    if (warp == 0) {
+        const int f = blockIdx.y;
+        int found_b = -1, found_qt = 0, base = 0;
+        for (int b0 = 0; b0 < a.B && found_b < 0; b0 += 32) {
+            const int bb = b0 + lane;
+            const int tiles = bb < a.B ? (cu_q[bb + 1] - cu_q[bb] + BQ - 1) / BQ : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int excl = incl - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && f >= base + excl && f < base + incl);
+            if (hit != 0u) {
+                const int src = __ffs(hit) - 1;
+                found_b = b0 + src;
+                found_qt = __shfl_sync(0xffffffffu, tiles, src) - 1 - (f - base - __shfl_sync(0xffffffffu, excl, src));
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            found_s[0] = found_b;
+            found_s[1] = found_qt;
+        }
+    }
+    __syncthreads();
+    if (found_s[0] < 0) return;                                // the whole CTA: nothing is set up yet
+    const int b = found_s[0], qt = found_s[1];
+    const int h = blockIdx.x;
     const int q_begin = cu_q[b], n_q = cu_q[b + 1] - q_begin;
     const int q0 = qt * BQ;
-    if (q0 >= n_q) return;                                     // the whole CTA: nothing is set up yet
     const int kvl = kv_len[b], past = kvl - n_q;
     const int rows_valid = min(BQ, n_q - q0);
     const int kt_hi = (past + q0 + rows_valid - 1) / BKV;      // tile of the last key that the last row sees
@@ -137,7 +170,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int lo_min = a.window > 0 ? max(0, past + q0 - a.window + 1) : 0;    // the first key that any row of the tile sees
     const int kvh = h / (a.H / a.KV);
 #ifdef MYNAH_ATTN_STAMPS
-    const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0;
+    const unsigned span_id = blockIdx.x + gridDim.x * blockIdx.y;
+    if (threadIdx.x == 0 && span_id < SPAN_CTAS) g_spans[span_id][0] = (long long)now_ns();
 #endif
 
     if (threadIdx.x == 0) {
@@ -420,10 +455,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
+#ifdef MYNAH_ATTN_STAMPS
+    if (threadIdx.x == 0 && span_id < SPAN_CTAS) g_spans[span_id][1] = (long long)now_ns();
+#endif
 }
 
 template <int HD>
-int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int B, int max_q_len, const int* cu_q,
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int n_tokens, int B, int max_q_len, const int* cu_q,
            const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
     constexpr size_t smem = 5 * (size_t)(HD / 64) * HALF_BYTES + 128 + 2 * 2 * BQ * sizeof(float) + 1024;
     auto kern = attn_prefill_tcgen05_kernel<HD>;
@@ -433,7 +471,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return mynah_fail("attn_prefill_tcgen05: %s", cudaGetErrorString(e));
         opted = true;
     }
-    const dim3 grid(a.H, ceil_div(max_q_len, BQ), B);
+    (void)max_q_len;
+    const dim3 grid(a.H, ceil_div(n_tokens, BQ) + B, 1);
     if (mynah_launch(kern, grid, dim3(THREADS), smem, stream, mq, mk, mv, cu_q, kv_len, pt, a, out, status) != cudaSuccess)
         return mynah_fail("attn_prefill_tcgen05: %s", cudaGetErrorString(cudaGetLastError()));
     return mynah_check_launch("attn_prefill_tcgen05");
@@ -445,6 +484,10 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // out: [10 warps][32 tiles][8 points] of the stamped CTA's cycle counts (host memory).
 MYNAH_API int mynah_attn_prefill_stamps(long long* out) {
     return cudaMemcpyFromSymbol(out, g_stamps, sizeof(g_stamps)) == cudaSuccess ? 0 : -1;
+}
+// out: [65536 CTAs][entry, exit] in nanoseconds of the device's global timer (CTA number x + X * (y + Y * z)).
+MYNAH_API int mynah_attn_prefill_spans(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_spans, sizeof(g_spans)) == cudaSuccess ? 0 : -1;
 }
 #endif
 
@@ -464,14 +507,14 @@ MYNAH_API int mynah_attn_prefill_tcgen05(
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                   ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
                   "attn_prefill_tcgen05: rows must be 16-byte aligned (strides %d, %d)", ldq, ldo);
-    MYNAH_REQUIRE(B <= 65535 && ceil_div(max_q_len, BQ) <= 65535 && (long long)n_pages * KV * PAGE_TOKENS < (1ll << 31), "attn_prefill_tcgen05: launch too large");
+    MYNAH_REQUIRE(ceil_div(n_tokens, BQ) + B <= 65535 && (long long)n_pages * KV * PAGE_TOKENS < (1ll << 31), "attn_prefill_tcgen05: launch too large");
     MYNAH_REQUIRE(status != nullptr, "attn_prefill_tcgen05: a status word is required");
     CUtensorMap mq, mk, mv;
     if (make_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_tokens, (long long)H * HD, ldq, BQ, 64)) return -1;
     if (make_map(&mk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
     if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
-    const PfArgs a{H, KV, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
+    const PfArgs a{B, H, KV, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
-    if (HD == 128) return launch<128>(mq, mk, mv, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
-    return launch<64>(mq, mk, mv, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    if (HD == 128) return launch<128>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    return launch<64>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
 }

@@ -86,6 +86,20 @@ struct QkvEpilogue {
     bf16* v_cache;
 };
 
+// Which tile of the output a tile number is. Tiles are numbered band by band: a band is `band` rows of tiles (8 for
+// CTA pairs, 16 for single CTAs), and inside a band the numbers run down a column of tiles first. The CTAs of a
+// launch work on consecutive numbers at any time, so together they touch a block of about as many rows of A as of
+// W, which stays in L2; numbered column by column over all of M, a product of 16,384 rows streamed all of A from
+// DRAM once for every column of tiles.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int band, int& m_tile, int& n_tile) {
+    const int band_tiles = band * n_tiles;
+    const int b = tile / band_tiles, in_band = tile - b * band_tiles;
+    const int m0 = b * band;
+    const int rows = min(band, m_tiles - m0);                        // the last band may be narrower
+    m_tile = m0 + in_band % rows;
+    n_tile = in_band / rows;
+}
+
 struct GemmShape {
     int M, N, K;          // N: output columns (for SwiGLU: gate rows; the up rows follow up_offset rows later)
     int up_offset;
@@ -281,7 +295,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             Item w;
             int n_item = 0;
             while (ok && items.next(w)) {
-                const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
+                int m_tile, n_tile;
+                tile_coords(w.tile, g.m_tiles, g.n_tiles, CTAS == 2 ? 8 : 16, m_tile, n_tile);
                 GSTAMP(0, n_item, 0);
                 n_item++;
                 for (int kb = w.kb0; kb < w.kb1; kb++, it++) {
@@ -387,7 +402,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         ItemIter<SK> items(nk, unit, n_units, total_tiles, kb_begin, kb_end);
         Item w;
         for (; items.next(w); local++) {
-            const int m_tile = w.tile % g.m_tiles, n_tile = w.tile / g.m_tiles;
+            int m_tile, n_tile;
+            tile_coords(w.tile, g.m_tiles, g.n_tiles, CTAS == 2 ? 8 : 16, m_tile, n_tile);
             const int buf = local & 1;
             const uint32_t use = (local >> 1) & 1;
             if (!mbar_wait_abort(acc_full0 + 8 * buf, use, abort_flag)) {
@@ -641,7 +657,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         cluster_sync_all();                                          // what the other CTA sent has arrived
         if (warp == 2 && lane == 0) GSTAMP(2, 0, 2);
         if (work) {
-            const int m_tile = unit % g.m_tiles, n_tile = unit / g.m_tiles;
+            int m_tile, n_tile;
+            tile_coords(unit, g.m_tiles, g.n_tiles, 16, m_tile, n_tile);
             const int row0 = m_tile * BM + quad * 32;
             unsigned char* my_stage = staging + quad * 2 * STAGING_BYTES;
             const unsigned char* got = smem + (size_t)row * 512;
