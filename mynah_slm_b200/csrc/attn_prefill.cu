@@ -25,7 +25,7 @@ constexpr int QPW = QT / WARPS; // queries per warp
 constexpr int MAXC = 8;         // head_dim <= 32 * MAXC
 
 struct PrefillArgs {
-    int H, KV, HD, ldq, ldo;
+    int B, H, KV, HD, ldq, ldo;
     int window;                 // 0: all keys
     float scale;
 };
@@ -42,10 +42,11 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
     float* Vs = Ks + KT * KS;                          // [KT][HD]
     float* Qs = Vs + KT * HD;                          // [QT][HD]
 
-    const int b = blockIdx.z, h = blockIdx.y;
+    int b, tile;
+    if (!find_query_tile(cu_q, a.B, QT, blockIdx.x, b, tile)) return;   // blockIdx.x numbers the step's query tiles
+    const int h = blockIdx.y;
     const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
-    const int tile0 = blockIdx.x * QT;
-    if (tile0 >= q_len) return;
+    const int tile0 = tile * QT;
     const int n_kv = kv_len[b];
     const int past = n_kv - q_len;                     // position of the sequence's first query
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -138,19 +139,21 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
 
 // q: [T, ldq] with head h at columns [h*HD, (h+1)*HD); out: [T, ldo] likewise.
 MYNAH_API int mynah_attn_prefill_generic(
-    const void* q, void* out, int dtype, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int* status, cudaStream_t stream) {
     if (B == 0 || max_q_len == 0) return 0;
     MYNAH_REQUIRE(B > 0 && H > 0 && KV > 0 && HD > 0 && H % KV == 0, "attn_prefill: bad sizes B=%d H=%d KV=%d HD=%d", B, H, KV, HD);
     MYNAH_REQUIRE(HD <= 32 * MAXC, "attn_prefill: head_dim %d exceeds %d", HD, 32 * MAXC);
-    MYNAH_REQUIRE(B <= 65535 && H <= 65535, "attn_prefill: B=%d or H=%d exceeds one launch", B, H);
+    MYNAH_REQUIRE(H <= 65535, "attn_prefill: H=%d exceeds one launch", H);
     MYNAH_REQUIRE(window >= 0, "attn_prefill: negative window");
-    const PrefillArgs a{H, KV, HD, ldq, ldo, window, 1.0f / sqrtf((float)HD)};
+    const PrefillArgs a{B, H, KV, HD, ldq, ldo, window, 1.0f / sqrtf((float)HD)};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const size_t smem = sizeof(float) * ((size_t)KT * (HD + 1) + (size_t)KT * HD + (size_t)QT * HD);
-    const dim3 grid(ceil_div(max_q_len, QT), H, B);
+    (void)max_q_len;
+    MYNAH_REQUIRE(n_tokens >= 0, "attn_prefill: negative row count");
+    const dim3 grid(ceil_div(n_tokens, QT) + B, H, 1);               // the most query tiles that n_tokens rows in B sequences make
     cudaError_t e = cudaSuccess;
     if (dtype == MYNAH_F32) {
         auto kern = attn_prefill_generic_kernel<float, float>;

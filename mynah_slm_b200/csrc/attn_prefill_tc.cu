@@ -49,7 +49,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int CH> __device__ __forceinline__ int swz(int r, int c) { return (r * CH + (c ^ (r & 7))) * 16; }
 
 struct PrefillTcArgs {
-    int H, KV, ldq, ldo;
+    int B, H, KV, ldq, ldo;
     int window;
     float scale_log2;                 // (1/sqrt(head_dim)) * log2(e)
 };
@@ -66,11 +66,10 @@ attn_prefill_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out,
     unsigned char* q_s = smem;                                  // [QT][HD]
     unsigned char* kv_s = smem + QT * HD * 2;                   // 2 stages x (K tile, V tile)
 
-    const int b = blockIdx.z, h = blockIdx.y;
+    int b, tile;
+    if (!find_query_tile(cu_q, a.B, QT, blockIdx.x, b, tile)) return;   // blockIdx.x numbers the step's query tiles, a sequence's long tiles first
+    const int h = blockIdx.y;
     const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
-    const int n_tiles = (q_len + QT - 1) / QT;
-    const int tile = n_tiles - 1 - (int)blockIdx.x;             // long tiles first
-    if (tile < 0) return;
     const int tile0 = tile * QT;
     const int n_kv = kv_len[b];
     const int past = n_kv - q_len;
@@ -257,7 +256,7 @@ MYNAH_API int mynah_attn_prefill_tc_supported(int H, int KV, int HD) {
 
 // Same arguments as mynah_attn_prefill_generic; bfloat16 only.
 MYNAH_API int mynah_attn_prefill_tc(
-    const void* q, void* out, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int* status, cudaStream_t stream) {
@@ -265,9 +264,11 @@ MYNAH_API int mynah_attn_prefill_tc(
     MYNAH_REQUIRE(mynah_attn_prefill_tc_supported(H, KV, HD), "attn_prefill_tc: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 2 == 0, "attn_prefill_tc: row strides %d, %d are not aligned", ldq, ldo);
     MYNAH_REQUIRE(B <= 65535 && H <= 65535 && window >= 0, "attn_prefill_tc: launch too large");
-    const PrefillTcArgs a{H, KV, ldq, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
+    const PrefillTcArgs a{B, H, KV, ldq, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
-    const dim3 grid(ceil_div(max_q_len, QT), H, B);
+    (void)max_q_len;
+    MYNAH_REQUIRE(n_tokens >= 0, "attn_prefill_tc: negative row count");
+    const dim3 grid(ceil_div(n_tokens, QT) + B, H, 1);               // the most query tiles that n_tokens rows in B sequences make
     const size_t smem = (size_t)QT * HD * 2 + 4 * (size_t)KT * HD * 2;
     if (HD == 128)
         return launch_prefill_tc<128>(grid, smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,

@@ -125,40 +125,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float* xch = reinterpret_cast<float*>(bars + 16);          // [2 buffers][2 groups][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // The query tiles of all sequences are numbered one after another, sequence by sequence, a sequence's last
-    // (longest) tile first; blockIdx.y is such a number. The grid has as many as the step's rows can make at most
-    // (rows / 128 + sequences: a captured step knows its rows, not how they are divided), so the numbers beyond the
-    // step's tiles leave at once. Warp 0 finds the tile's sequence with a prefix sum over the sequences' tile counts.
-    __shared__ int found_s[2];
-    if (warp == 0) {
-        const int f = blockIdx.y;
-        int found_b = -1, found_qt = 0, base = 0;
-        for (int b0 = 0; b0 < a.B && found_b < 0; b0 += 32) {
-            const int bb = b0 + lane;
-            const int tiles = bb < a.B ? (cu_q[bb + 1] - cu_q[bb] + BQ - 1) / BQ : 0;
-            int incl = tiles;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
-            }
-            const int excl = incl - tiles;
-            const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && f >= base + excl && f < base + incl);
-            if (hit != 0u) {
-                const int src = __ffs(hit) - 1;
-                found_b = b0 + src;
-                found_qt = __shfl_sync(0xffffffffu, tiles, src) - 1 - (f - base - __shfl_sync(0xffffffffu, excl, src));
-            }
-            base += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) {
-            found_s[0] = found_b;
-            found_s[1] = found_qt;
-        }
-    }
-    __syncthreads();
-    if (found_s[0] < 0) return;                                // the whole CTA: nothing is set up yet
-    const int b = found_s[0], qt = found_s[1];
+    // blockIdx.y numbers the step's query tiles (find_query_tile); numbers beyond them leave at once.
+    int b, qt;
+    if (!find_query_tile(cu_q, a.B, BQ, blockIdx.y, b, qt)) return;    // the whole CTA: nothing is set up yet
     const int h = blockIdx.x;
     const int q_begin = cu_q[b], n_q = cu_q[b + 1] - q_begin;
     const int q0 = qt * BQ;

@@ -31,6 +31,51 @@ struct PageTable {
     int n_pages;          // pages in the pool (bound of every id)
 };
 
+// The query tiles of a step's sequences are numbered one after another, sequence by sequence, a sequence's last
+// (longest) tile first. Finds tile number `flat`: its sequence and its tile within the sequence; false when the step
+// has fewer tiles (a grid is sized for the most tiles that the step's rows can make: rows / tile_rows + sequences,
+// since a captured step knows its rows but not how they divide). Warp 0 takes a prefix sum over the sequences' tile
+// counts, 32 sequences at a time; every thread of the CTA must call this (it synchronises the CTA).
+__device__ __forceinline__ bool find_query_tile(const int* __restrict__ cu_q, int B, int tile_rows, int flat, int& b, int& tile) {
+    __shared__ int found_s[2];
+    if (B == 1) {                                                    // one sequence: nothing to look for
+        const int tiles = (cu_q[1] - cu_q[0] + tile_rows - 1) / tile_rows;
+        b = 0;
+        tile = tiles - 1 - flat;
+        return flat < tiles;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int found_b = -1, found_t = 0, base = 0;
+        for (int b0 = 0; b0 < B && found_b < 0; b0 += 32) {
+            const int bb = b0 + lane;
+            const int tiles = bb < B ? (cu_q[bb + 1] - cu_q[bb] + tile_rows - 1) / tile_rows : 0;
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int excl = incl - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && flat >= base + excl && flat < base + incl);
+            if (hit != 0u) {
+                const int src = __ffs(hit) - 1;
+                found_b = b0 + src;
+                found_t = __shfl_sync(0xffffffffu, tiles, src) - 1 - (flat - base - __shfl_sync(0xffffffffu, excl, src));
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            found_s[0] = found_b;
+            found_s[1] = found_t;
+        }
+    }
+    __syncthreads();
+    b = found_s[0];
+    tile = found_s[1];
+    return b >= 0;
+}
+
 // Index of the physical page that holds position `pos` of sequence b, or -1.
 __device__ __forceinline__ int page_of(const PageTable& pt, int b, int pos) {
     const int lp = pos / PAGE_TOKENS - pt.base[b];

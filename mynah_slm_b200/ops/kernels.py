@@ -298,7 +298,7 @@ def attn_prefill_generic(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len
     """q is read from the first H*HD columns of `qkv` (row stride qkv.shape[1])."""
     _chk(qkv, "q", dim=2)
     _chk(out, "attention output", qkv.dtype, 2)
-    call("mynah_attn_prefill_generic", ptr(qkv), ptr(out), code(qkv.dtype), B, max_q_len, H, KV, HD,
+    call("mynah_attn_prefill_generic", ptr(qkv), ptr(out), code(qkv.dtype), qkv.shape[0], B, max_q_len, H, KV, HD,
          qkv.shape[1], out.shape[1], ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
 
@@ -313,7 +313,7 @@ def attn_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len: int
     """The tensor-core prompt attention (bfloat16, head_dim 64 or 128); same contract as attn_prefill_generic."""
     _chk(qkv, "q", torch.bfloat16, 2)
     _chk(out, "attention output", torch.bfloat16, 2)
-    call("mynah_attn_prefill_tc", ptr(qkv), ptr(out), B, max_q_len, H, KV, HD, qkv.shape[1], out.shape[1],
+    call("mynah_attn_prefill_tc", ptr(qkv), ptr(out), qkv.shape[0], B, max_q_len, H, KV, HD, qkv.shape[1], out.shape[1],
          ptr(k_cache), ptr(v_cache), ptr(cu_q), ptr(kv_len),
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
 

@@ -38,7 +38,7 @@ _SIGNATURES: dict[str, list] = {
                                  P, P,
                                  P, P, P, c_int,
                                  P, P, P, P],
-    "mynah_attn_prefill_generic": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "mynah_attn_prefill_generic": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    P, P, P, P,
                                    P, P, P, c_int,
                                    c_int, P, P],
@@ -46,7 +46,7 @@ _SIGNATURES: dict[str, list] = {
                           P, P, P,
                           P, P, P, c_int,
                           c_int, c_int, P, P, P],
-    "mynah_attn_prefill_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+    "mynah_attn_prefill_tc": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               P, P, P, P,
                               P, P, P, c_int,
                               c_int, P, P],
