@@ -34,6 +34,7 @@ class EngineBackend:
         engine.sampler.set_params(params)
         self._host_rows: list[torch.Tensor] = []
         self._turn = 0
+        self._to_start: list[tuple] = []
         # steps fed from the device are replayed graphs; MYNAH_RUN_AHEAD=0 keeps the step-by-step loop
         self.runs_ahead = bool(engine.use_graphs and engine.graph_safe) and os.environ.get("MYNAH_RUN_AHEAD", "1") != "0"
 
@@ -42,14 +43,23 @@ class EngineBackend:
 
     def open(self, request_index: int, prompt: Sequence[int]) -> int:
         slot = self.engine.open_sequence()
-        self.engine.sampler.start_sequences([slot], [stream_state(self.params.seed, request_index)], [prompt])
+        # the generators and rings of a batch's slots are set in one go, when the batch's prompts run
+        self._to_start.append((slot, stream_state(self.params.seed, request_index), prompt))
         return slot
 
+    def _start_opened(self) -> None:
+        if self._to_start:
+            slots, states, prompts = zip(*self._to_start)
+            self._to_start = []
+            self.engine.sampler.start_sequences(slots, states, prompts)
+
     def close(self, slot: int) -> None:
+        self._to_start = [t for t in self._to_start if t[0] != slot]
         self.engine.close_sequence(slot)
 
     def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> list[int]:
         eng = self.engine
+        self._start_opened()
         logits = eng.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
         slots_t = torch.tensor(list(slots), dtype=torch.int32, device=eng.device)
         toks = eng.sampler.sample(logits, slots_t).cpu().tolist()
@@ -57,6 +67,7 @@ class EngineBackend:
         return toks
 
     def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> list[int]:
+        self._start_opened()
         out = self.engine.decode_sampled(slots, tokens)
         return out[:len(slots)].cpu().tolist()
 
@@ -65,6 +76,7 @@ class EngineBackend:
     # before the host reads them.
     def decode_launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None, feed=None) -> "_InFlight":
         n = len(slots)
+        self._start_opened()
         out = self.engine.decode_sampled(slots, tokens, None if feed is None else (feed[0].device_tokens, feed[1]))
         if not self._host_rows or self._host_rows[0].numel() < n:
             self._host_rows = [torch.empty((max(n, 64),), dtype=torch.int32, pin_memory=True) for _ in range(3)]

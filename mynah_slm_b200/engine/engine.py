@@ -546,6 +546,7 @@ class Engine:
         """mode: "plain" (logits), "sample" (tokens), "loop" (tokens, and each
         sequence's token becomes its next input one position on)."""
         from ..ops import lib
+        self.sampler.flush_resets()                   # the captured launches read the sampler's rows
         if mode not in g.graphs:
             # first use of this bucket: run once for real (this also sizes scratch
             # memory and warms the library), then record the same launches.

@@ -90,6 +90,7 @@ class SamplerState:
         self.params = torch.zeros((8,), dtype=torch.float32, device=device)
         self.active_window = window
         self._params_host: Optional[SamplingParams] = None
+        self._to_reset: list[int] = []               # slots whose rows are set back at the next flush
 
     def set_params(self, p: SamplingParams) -> None:
         p.validate()
@@ -106,14 +107,24 @@ class SamplerState:
     def reset_slot(self, slot: int) -> None:
         """The state a slot starts with: an empty ring and the generator of stream 0 of seed 0. A caller that
         wants another stream or the prompt in the ring calls `start_sequences` afterwards."""
-        self.ring_n[slot] = 0
-        self.ring_head[slot] = 0
-        self.rng[slot] = _as_i64(SEED_ZERO)
+        self._to_reset.append(int(slot))             # (one device operation for all of a batch's slots, not three a slot)
+
+    def flush_resets(self) -> None:
+        """Set the rows of the slots opened since the last call back; called before anything reads or writes
+        the state (a draw, `start_sequences`, a captured step)."""
+        if not self._to_reset:
+            return
+        idx = torch.tensor(self._to_reset, dtype=torch.int64).to(self.device)
+        self._to_reset = []
+        self.ring_n.index_fill_(0, idx, 0)
+        self.ring_head.index_fill_(0, idx, 0)
+        self.rng.index_fill_(0, idx, _as_i64(SEED_ZERO))
 
     def start_sequences(self, slots: Sequence[int], states: Sequence[int],
                         prompts: Optional[Sequence[Sequence[int]]] = None, window: Optional[int] = None) -> None:
         """Seed the slots' generators and load their rings with the prompts'
         last tokens (the reference accepts prompt tokens too, src/generate.c:25-32)."""
+        self.flush_resets()
         idx = torch.tensor(list(slots), dtype=torch.int64, device=self.device)
         self.rng[idx] = torch.tensor([_as_i64(s) for s in states], dtype=torch.int64, device=self.device)
         w = self.active_window if window is None else min(window, self.window)
@@ -135,6 +146,8 @@ class SamplerState:
     def sample(self, logits: torch.Tensor, slots: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Penalties, then the draw, then the accepted token into the ring.
         `logits` [B, V] fp32 is overwritten; `slots` int32 [B] (negative: padding)."""
+        if not torch.cuda.is_current_stream_capturing():
+            self.flush_resets()
         if self.window > 0:
             kernels.apply_penalties(logits, self.ring, self.ring_n, slots, self.params)
         out = kernels.sample(logits, self.params, self.rng, slots, out)
