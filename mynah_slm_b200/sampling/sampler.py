@@ -20,6 +20,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..ops import kernels
@@ -128,18 +129,19 @@ class SamplerState:
         idx = torch.tensor(list(slots), dtype=torch.int64, device=self.device)
         self.rng[idx] = torch.tensor([_as_i64(s) for s in states], dtype=torch.int64, device=self.device)
         w = self.active_window if window is None else min(window, self.window)
-        rows = torch.zeros((len(slots), self.ring.shape[1]), dtype=torch.int32)
+        rows = np.zeros((len(slots), self.ring.shape[1]), dtype=np.int32)
         ns, heads = [], []
         for i, _ in enumerate(slots):
-            toks = list(prompts[i]) if prompts is not None and w > 0 else []
-            # the ring after accepting every prompt token in turn
+            toks = prompts[i] if prompts is not None and w > 0 else []
+            # the ring after accepting every prompt token in turn: token j lies at j % w
             n = min(len(toks), w)
             head = len(toks) % w if w > 0 else 0
-            for j, t in enumerate(toks[len(toks) - n:], start=len(toks) - n):
-                rows[i, j % w] = t
+            if n:
+                first = len(toks) - n
+                rows[i, (np.arange(first, first + n) % w)] = np.asarray(toks[first:], dtype=np.int32)
             ns.append(n)
             heads.append(head)
-        self.ring[idx] = rows.to(self.device)
+        self.ring[idx] = torch.from_numpy(rows).to(self.device)
         self.ring_n[idx] = torch.tensor(ns, dtype=torch.int32, device=self.device)
         self.ring_head[idx] = torch.tensor(heads, dtype=torch.int32, device=self.device)
 
