@@ -383,7 +383,9 @@ def main() -> int:
     rng = np.random.default_rng(2)
     V = cfg["vocab_size"]
 
-    llm = LLM.random(cfg, seed=2, dtype="bfloat16", max_tokens=max_batch * CTX_LEN, max_seqs=max_batch)
+    # the cache: the benchmark's context length a sequence, or more where a longer prompt is asked for
+    ctx_tokens = max(CTX_LEN, -(-(prompt_len + 2 * (W + K) + 8 + 64) // 64) * 64)
+    llm = LLM.random(cfg, seed=2, dtype="bfloat16", max_tokens=max_batch * ctx_tokens, max_seqs=max_batch)
     eng = llm.engine
     eng.sampler.set_params(SamplingParams.greedy())
 
