@@ -163,6 +163,10 @@ def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -
 # they are left to it, as the reference leaves its products to a library. 0 rows: never.
 GEMV_LIBRARY_FROM_ROWS = int(os.environ.get("MYNAH_GEMV_LIBRARY_FROM_ROWS", "6144"))
 GEMV_LIBRARY_FROM_K = 2048
+# From nine rows on (the second half of the tensor cores' sixteen rows is then in use) the library also does better
+# on every large matrix of long rows: 8B down 4,096 x 12,288 at 16 rows takes 21.8 us there against 32.2, 8B o 9.8
+# against 13.6, 4B down 15.3 against 17.3; at 8 rows the own kernels are level or ahead. 0 elements: never.
+GEMV_LIBRARY_FROM_ELEMENTS_9_ROWS = int(os.environ.get("MYNAH_GEMV_LIBRARY_FROM_ELEMENTS_9_ROWS", str(1 << 23)))
 
 
 def _fusable(x, w: torch.Tensor, N: int) -> bool:
@@ -180,6 +184,9 @@ def _fusable(x, w: torch.Tensor, N: int) -> bool:
         if x.dtype != torch.bfloat16 or not x.is_contiguous():
             return False
         M, K = x.shape
+    if (GEMV_LIBRARY_FROM_ELEMENTS_9_ROWS and M > 8 and K >= GEMV_LIBRARY_FROM_K
+            and w.shape[0] * w.shape[1] >= GEMV_LIBRARY_FROM_ELEMENTS_9_ROWS):
+        return False
     return K == w.shape[1] and N <= GEMV_MAX_OUT_ROWS and gemv_decode_supported(M, N, K)
 
 
