@@ -32,6 +32,8 @@
 // its tensor memory and returns.
 #include "tcgen05.cuh"
 
+#include <stdlib.h>
+
 namespace {
 
 using namespace tc5;
@@ -101,8 +103,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+// NS: stages of K, V and the scores. 2: a CTA an SM, the next tile's scores and operands under this tile's softmax.
+// 1: half the shared and tensor memory, so that two CTAs share an SM and one's softmax runs under the other's products.
+template <int HD, int NS>
+__global__ void __launch_bounds__(THREADS, NS == 1 ? 2 : 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ cu_q,
                             const int* __restrict__ kv_len, PageTable pt, PfArgs a, bf16* __restrict__ out,
@@ -110,14 +114,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALVES = HD / 64;
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;            // Q, K and V tiles: 128 rows x HD
     constexpr int PAGE_BYTES = PAGE_TOKENS * 128;              // one page in one half: 64 rows of 128 bytes
-    constexpr int TMEM_COLS = 512;                             // two score buffers of 128 columns, the output at 256
-    constexpr int O_COL = 256;
+    constexpr int TMEM_COLS = NS == 2 ? 512 : 256;             // NS score buffers of 128 columns, the output behind them
+    constexpr int O_COL = NS * 128;
+    auto stage_of = [](int j) { return NS == 2 ? (j & 1) : 0; };
+    auto use_of = [](int j) { return (uint32_t)(NS == 2 ? ((j >> 1) & 1) : (j & 1)); };   // parity of tile j's use of its stage
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
-    unsigned char* k_s = q_s + TILE_BYTES;                     // two stages
-    unsigned char* v_s = k_s + 2 * TILE_BYTES;                 // two stages
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * TILE_BYTES);
+    unsigned char* k_s = q_s + TILE_BYTES;                     // NS stages
+    unsigned char* v_s = k_s + NS * TILE_BYTES;                // NS stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + NS * TILE_BYTES);
     const uint32_t q_full = smem_u32(bars), k_full = smem_u32(bars + 1), v_full = smem_u32(bars + 3);   // [2] each, 8 bytes apart
     const uint32_t s_full = smem_u32(bars + 5), v_free = smem_u32(bars + 7);
     const uint32_t p_full = smem_u32(bars + 9), o_done = smem_u32(bars + 11), x_full = smem_u32(bars + 12);
@@ -180,8 +186,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tma_load_2d(smem_u32(q_s + hf * HALF_BYTES), &map_q, h * HD + hf * 64, q_begin + q0, q_full);
             int k_issued = 0, v_issued = 0;
             for (int j = 0; j < n_tiles; j++) {
-                const int st = j & 1;
-                const uint32_t prev_use = ((j >> 1) & 1) ^ 1;  // parity of the stage's use before this one
+                const int st = stage_of(j);
+                const uint32_t prev_use = use_of(j) ^ 1;       // parity of the stage's use before this one
                 const int key0 = (kt_lo + j) * BKV;
                 // A page is brought only if it holds a key that some row of the tile sees: the first page of the
                 // first tile may lie wholly before the window (a cache that keeps a window has given it back),
@@ -194,7 +200,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     break;
                 }
                 const uint32_t bytes = ((p0 >= 0 ? 1 : 0) + (p1 >= 0 ? 1 : 0)) * HALVES * PAGE_BYTES;
-                if (j >= 2 && !mbar_wait(s_full + 8 * st, prev_use)) {      // the scores of tile j-2 are done: its K is free
+                if (j >= NS && !mbar_wait(s_full + 8 * st, prev_use)) {     // the scores of tile j-NS are done: its K is free
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
                 }
@@ -206,7 +212,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (p1 >= 0) tma_load_2d(smem_u32(kd + hf * HALF_BYTES + PAGE_BYTES), &map_k, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, k_full + 8 * st);
                 }
                 k_issued = j + 1;
-                if (j >= 2 && !mbar_wait(v_free + 8 * st, prev_use)) {      // the second product of tile j-2 is done: its V is free
+                if (j >= NS && !mbar_wait(v_free + 8 * st, prev_use)) {     // the second product of tile j-NS is done: its V is free
                     atomicOr(status, MYNAH_ST_TIMEOUT);
                     break;
                 }
@@ -222,16 +228,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             griddep_launch_late();                             // all of this CTA's tiles have been asked for
             // whatever was started still lands in this CTA's shared memory: wait for it before leaving (bounded)
             mbar_wait(q_full, 0);
-            for (int j = max(0, k_issued - 2); j < k_issued; j++) mbar_wait(k_full + 8 * (j & 1), (j >> 1) & 1);
-            for (int j = max(0, v_issued - 2); j < v_issued; j++) mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1);
+            for (int j = max(0, k_issued - NS); j < k_issued; j++) mbar_wait(k_full + 8 * stage_of(j), use_of(j));
+            for (int j = max(0, v_issued - NS); j < v_issued; j++) mbar_wait(v_full + 8 * stage_of(j), use_of(j));
         }
     } else if (warp == 1) {
         if (lane == 0) {                                       // ---- MMA issuer
             constexpr uint32_t idesc_s = idesc(BKV, false), idesc_o = idesc(HD, true);
             const uint32_t t_o = tmem_base + O_COL;
             const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-            auto scores = [&](int j) {                         // S[j & 1] = Q . K_j^T
-                const int st = j & 1;
+            auto scores = [&](int j) {                         // S[stage of j] = Q . K_j^T
+                const int st = stage_of(j);
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t off = (k / 4) * HALF_BYTES + (k % 4) * 32;
@@ -245,28 +251,34 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 scores(0);
             }
             for (int j = 0; j < n_tiles && ok; j++) {
-                const int st = j & 1;
+                const int st = stage_of(j);
                 STAMP(j, 0);
-                if (j + 1 < n_tiles) {                         // the next tile's scores, while the softmax works on this one.
+                if (NS == 2 && j + 1 < n_tiles) {              // the next tile's scores, while the softmax works on this one.
                     // Their buffer held the probabilities of tile j-1; the product that read them was issued before.
-                    ok = mbar_wait(k_full + 8 * (st ^ 1), ((j + 1) >> 1) & 1);
+                    ok = mbar_wait(k_full + 8 * stage_of(j + 1), use_of(j + 1));
                     if (!ok) break;
                     tc_fence_after();
                     STAMP(j, 1);
                     scores(j + 1);
                 }
                 STAMP(j, 2);
-                ok = mbar_wait(p_full + 8 * st, (j >> 1) & 1) && mbar_wait(v_full + 8 * st, (j >> 1) & 1);
+                ok = mbar_wait(p_full + 8 * st, use_of(j)) && mbar_wait(v_full + 8 * st, use_of(j));
                 if (!ok) break;
                 tc_fence_after();
                 STAMP(j, 3);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++)             // 16 keys a step: 8 columns of packed probabilities, 16 rows of V
-                    tc_mma_ts(t_o, tmem_base + st * BKV + k * 8, desc_mn_major(v_addr + st * TILE_BYTES + k * 16 * 128, HALF_BYTES),
+                    tc_mma_ts(t_o, tmem_base + st * BKV + (NS == 2 ? k * 8 : (k / 4) * 64 + (k % 4) * 8), desc_mn_major(v_addr + st * TILE_BYTES + k * 16 * 128, HALF_BYTES),
                               idesc_o, (j | k) != 0);
                 tc_commit(v_free + 8 * st);
                 tc_commit(o_done);
                 STAMP(j, 4);
+                if (NS == 1 && j + 1 < n_tiles) {              // one score buffer: the next scores overwrite these probabilities,
+                    ok = mbar_wait(k_full, use_of(j + 1));     // so they are issued behind the product that reads them
+                    if (!ok) break;
+                    tc_fence_after();
+                    scores(j + 1);
+                }
             }
             if (!ok) atomicOr(status, MYNAH_ST_TIMEOUT);
         }
@@ -284,47 +296,73 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float m_ref = -INFINITY, l = 0.f;                      // the maximum that the sums are scaled by; the sum over this thread's keys
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
-            const int st = j & 1;
-            const uint32_t use = (j >> 1) & 1;
+            const int st = stage_of(j);
+            const uint32_t use = use_of(j);
+            const int xst = j & 1;                             // the exchange has two buffers whatever NS is
+            const uint32_t xuse = (j >> 1) & 1;
             const int key0 = (kt_lo + j) * BKV + grp * HALF_KEYS;     // this thread's first key
             const uint32_t t_s = t_row + st * BKV;
             STAMP(j, 0);
             if (!warp_wait(s_full + 8 * st, use)) { ok = false; break; }
             tc_fence_after();
             STAMP(j, 1);
-            float s[HALF_KEYS];
-#pragma unroll
-            for (int c = 0; c < HALF_KEYS / 32; c++) tc_ld32_nowait(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
-#pragma unroll
-            for (int c = 0; c < HALF_KEYS / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
-            STAMP(j, 2);
             // does any row of the tile have a key, among this group's, that it must not see?
             const bool need_mask = key0 + HALF_KEYS - 1 > past + q0 || key0 + HALF_KEYS > kvl ||
                                    (a.window > 0 && key0 < past + q0 + BQ - a.window);
-            if (need_mask) {                                   // a compare with a constant and a select per score
-                const int hi = min(qpos, kvl - 1) - key0;      // the last of this thread's scores that its row sees
-                if (a.window > 0) {
-                    const int lo = lo_r - key0;
+            const int hi = min(qpos, kvl - 1) - key0;          // the last of this thread's scores that its row sees
+            const int lo = a.window > 0 ? lo_r - key0 : -(1 << 30);
+            // 32 of the thread's scores (the c-th half of them), those that the row must not see set to -inf
+            auto fetch32 = [&](int c, float (&v)[32]) {
+                tc_ld32(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(v));
+                if (need_mask) {                               // a compare with a constant and a select per score
+                    if (a.window > 0) {
 #pragma unroll
-                    for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && e >= lo) ? s[e] : -INFINITY;
-                } else {
+                        for (int e = 0; e < 32; e++) v[e] = (c * 32 + e <= hi && c * 32 + e >= lo) ? v[e] : -INFINITY;
+                    } else {
 #pragma unroll
-                    for (int e = 0; e < HALF_KEYS; e++) s[e] = e <= hi ? s[e] : -INFINITY;
+                        for (int e = 0; e < 32; e++) v[e] = c * 32 + e <= hi ? v[e] : -INFINITY;
+                    }
                 }
-            }
+            };
+            float s[NS == 2 ? HALF_KEYS : 1];                  // NS == 2: a thread keeps its 64 scores; NS == 1: it fetches them twice
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if constexpr (NS == 2) {
 #pragma unroll
-            for (int e = 0; e < HALF_KEYS; e += 2) mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], s[e], s[e + 1]);
+                for (int c = 0; c < HALF_KEYS / 32; c++) tc_ld32_nowait(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+#pragma unroll
+                for (int c = 0; c < HALF_KEYS / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+                STAMP(j, 2);
+                if (need_mask) {
+                    if (a.window > 0) {
+#pragma unroll
+                        for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && e >= lo) ? s[e] : -INFINITY;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < HALF_KEYS; e++) s[e] = e <= hi ? s[e] : -INFINITY;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < HALF_KEYS; e += 2) mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], s[e], s[e + 1]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < HALF_KEYS / 32; c++) {
+                    float v[32];
+                    fetch32(c, v);
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) mx4[(e >> 1) & 3] = max3(mx4[(e >> 1) & 3], v[e], v[e + 1]);
+                }
+                STAMP(j, 2);
+            }
             const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the row's maximum over both groups, through shared memory (two buffers: a value is read before the
             // barrier of the next tile, and overwritten only after it)
-            xch[(st * 2 + grp) * BQ + row] = mx_own;
+            xch[(xst * 2 + grp) * BQ + row] = mx_own;
             __syncwarp();
             STAMP(j, 3);
-            if (lane == 0) mbar_arrive(x_full + 8 * st);
-            if (!warp_wait(x_full + 8 * st, use)) { ok = false; break; }
+            if (lane == 0) mbar_arrive(x_full + 8 * xst);
+            if (!warp_wait(x_full + 8 * xst, xuse)) { ok = false; break; }
             STAMP(j, 4);
-            const float m_new = fmaxf(mx_own, xch[(st * 2 + (grp ^ 1)) * BQ + row]) * a.scale_log2;
+            const float m_new = fmaxf(mx_own, xch[(xst * 2 + (grp ^ 1)) * BQ + row]) * a.scale_log2;
             // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
             // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
             // bf16 products carry without loss). Both threads of a row take the same decision.
@@ -351,18 +389,39 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_wait_st();
             }
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};              // two pairs of running sums
-            uint32_t pk[HALF_KEYS / 2];
+            if constexpr (NS == 2) {
+                uint32_t pk[HALF_KEYS / 2];
 #pragma unroll
-            for (int e = 0; e < HALF_KEYS; e += 2) {
-                float x0, x1;
-                fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
-                const float p0 = ex2(x0), p1 = ex2(x1);                           // 2^-inf = 0
-                add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
-                pk[e >> 1] = pack2(p0, p1);
+                for (int e = 0; e < HALF_KEYS; e += 2) {
+                    float x0, x1;
+                    fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
+                    const float p0 = ex2(x0), p1 = ex2(x1);                       // 2^-inf = 0
+                    add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
+                    pk[e >> 1] = pack2(p0, p1);
+                }
+                STAMP(j, 5);
+                // over the scores: both groups have theirs in registers since the exchange above
+                tc_st32(t_s + grp * (HALF_KEYS / 2), pk);
+            } else {
+                // The scores are fetched again, 32 at a time, and a group's probabilities go over its own scores
+                // (columns [64 g, 64 g + 32) of the buffer), behind the ones already fetched.
+#pragma unroll
+                for (int c = 0; c < HALF_KEYS / 32; c++) {
+                    float v[32];
+                    fetch32(c, v);
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        float x0, x1;
+                        fma2(x0, x1, v[e], v[e + 1], a.scale_log2, -m_use);
+                        const float p0 = ex2(x0), p1 = ex2(x1);
+                        add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
+                        pk[e >> 1] = pack2(p0, p1);
+                    }
+                    tc_st16(t_s + grp * HALF_KEYS + c * 16, pk);
+                }
+                STAMP(j, 5);
             }
-            STAMP(j, 5);
-            // over the scores: both groups have theirs in registers since the exchange above
-            tc_st32(t_s + grp * (HALF_KEYS / 2), pk);
             tc_wait_st();
             STAMP(j, 6);
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
@@ -429,11 +488,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #endif
 }
 
-template <int HD>
+template <int HD, int NS>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int n_tokens, int B, int max_q_len, const int* cu_q,
            const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
-    constexpr size_t smem = 5 * (size_t)(HD / 64) * HALF_BYTES + 128 + 2 * 2 * BQ * sizeof(float) + 1024;
-    auto kern = attn_prefill_tcgen05_kernel<HD>;
+    constexpr size_t smem = (1 + 2 * NS) * (size_t)(HD / 64) * HALF_BYTES + 128 + 2 * 2 * BQ * sizeof(float) + 1024;
+    auto kern = attn_prefill_tcgen05_kernel<HD, NS>;
     static bool opted = false;
     if (!opted) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -460,6 +519,22 @@ MYNAH_API int mynah_attn_prefill_spans(long long* out) {
 }
 #endif
 
+// 0: chosen by the number of CTAs (the default, or MYNAH_ATTN_PREFILL_STAGES), 1: one stage and two CTAs an SM, 2: two
+// stages and one CTA an SM. Both forms give the same bits.
+static int g_stages_mode = -1;
+static int stages_mode() {
+    if (g_stages_mode < 0) {
+        const char* e = getenv("MYNAH_ATTN_PREFILL_STAGES");
+        g_stages_mode = e != nullptr && (e[0] == '1' || e[0] == '2') ? e[0] - '0' : 0;
+    }
+    return g_stages_mode;
+}
+MYNAH_API int mynah_attn_prefill_tcgen05_stages(int mode) {
+    MYNAH_REQUIRE(mode >= 0 && mode <= 2, "attn_prefill_tcgen05_stages: mode %d is none of 0, 1, 2", mode);
+    g_stages_mode = mode;
+    return 0;
+}
+
 MYNAH_API int mynah_attn_prefill_tcgen05_supported(int H, int KV, int HD) {
     return (HD == 64 || HD == 128) && KV > 0 && H % KV == 0;
 }
@@ -484,6 +559,16 @@ MYNAH_API int mynah_attn_prefill_tcgen05(
     if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
     const PfArgs a{B, H, KV, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
-    if (HD == 128) return launch<128>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
-    return launch<64>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    // Two CTAs an SM pay once there are several waves of CTAs (64 prompts of 2,048 tokens and 32 heads: 2.97 against
+    // 3.34 ms; 4 prompts: 221 against 236 us); with one wave or two, the longest CTA's own chain sets the time and it
+    // is longer with one stage (one prompt of 16 heads: 39.7 against 28.0 us).
+    const int mode = stages_mode();
+    const long long ctas = (long long)H * (ceil_div(n_tokens, BQ) + B);
+    const int stages = mode != 0 ? mode : (ctas >= 8ll * mynah_sm_count() ? 1 : 2);
+    if (stages == 1) {
+        if (HD == 128) return launch<128, 1>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+        return launch<64, 1>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    }
+    if (HD == 128) return launch<128, 2>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    return launch<64, 2>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
 }

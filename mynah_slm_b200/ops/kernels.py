@@ -344,6 +344,12 @@ def attn_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, B: int, max_q_len
          ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, ptr(status), stream_ptr())
 
 
+def attn_prefill_tcgen05_stages(mode: int) -> None:
+    """0: the prompt attention chooses its form by the number of CTAs; 1: one stage of K, V and scores, two CTAs an
+    SM; 2: two stages, one CTA an SM. Both give the same bits."""
+    call("mynah_attn_prefill_tcgen05_stages", int(mode))
+
+
 def attn_decode_scratch_floats(B: int, H: int, HD: int, n_splits: int) -> int:
     return int(lib.load().mynah_attn_decode_scratch_floats(B, H, HD, n_splits))
 

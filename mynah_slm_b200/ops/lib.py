@@ -81,6 +81,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_decode_advance": [P, P, P, P, P, c_int, P],
     "mynah_sampler_accept": [P, c_int, P, P, P, c_int, P, P, P],
     "mynah_l2_prefetch": [P, P, c_int, P],
+    "mynah_attn_prefill_tcgen05_stages": [c_int],
     "mynah_wait_probe": [P, P, ctypes.c_ulonglong, P],
     "mynah_read_probe": [P, P, c_int, c_int, c_int, P, P, P],
     "mynah_randn_fill": [P, c_int, c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong, c_double, c_double, P],

@@ -828,12 +828,21 @@ def test_fused_decode_path_equals_the_unfused_one(tmp_path):
     assert rel_err(outs[1], outs[0]) < 1e-2
 
 
-@pytest.mark.parametrize("which", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("which", ["mma_sync", "tcgen05", "tcgen05_one_stage"])
 @pytest.mark.parametrize("H,KV,HD,window", [(16, 8, 128, 0), (4, 1, 64, 0), (6, 2, 128, 100), (8, 8, 64, 33), (2, 1, 128, 300)])
 def test_attn_prefill_tensor_cores(H, KV, HD, window, which):
     """The two tensor-core prompt kernels against the plain attention: a ragged
-    batch, prompts that continue earlier ones, a window, NaN in unused page tails."""
+    batch, prompts that continue earlier ones, a window, NaN in unused page tails. The tcgen05 kernel in both of
+    its forms (two stages and a CTA an SM; one stage and two CTAs an SM), which give the same bits."""
     k = _k()
+    k.attn_prefill_tcgen05_stages(1 if which == "tcgen05_one_stage" else 2)
+    try:
+        _attn_prefill_tensor_cores(k, H, KV, HD, window, which)
+    finally:
+        k.attn_prefill_tcgen05_stages(0)
+
+
+def _attn_prefill_tensor_cores(k, H, KV, HD, window, which):
     assert k.attn_prefill_tc_supported(torch.bfloat16, H, KV, HD) and not k.attn_prefill_tc_supported(torch.bfloat16, 4, 2, 48)
     assert k.attn_prefill_tcgen05_supported(torch.bfloat16, H, KV, HD) and not k.attn_prefill_tcgen05_supported(torch.float32, H, KV, HD)
     kernel = k.attn_prefill_tc if which == "mma_sync" else k.attn_prefill_tcgen05
@@ -864,6 +873,12 @@ def test_attn_prefill_tensor_cores(H, KV, HD, window, which):
     assert status.item() == 0
     got = out.float().cpu().numpy()
     assert np.isfinite(got).all()
+    if which == "tcgen05_one_stage":                                             # the other form: the same bits
+        k.attn_prefill_tcgen05_stages(2)
+        out2 = torch.zeros_like(out)
+        kernel(qkv, out2, len(seqs), max(lens_q), H, KV, HD, kc, vc, cu, kvl, pt, window, status)
+        k.attn_prefill_tcgen05_stages(1)
+        assert status.item() == 0 and torch.equal(out, out2)
     row = 0
     for (q, kk, vv), nq, p in zip(seqs, lens_q, past):
         ref = gqa_attention(q, kk, vv, window=window or None, q_pos=np.arange(p, p + nq), k_pos=np.arange(p + nq))
