@@ -187,6 +187,12 @@ def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
 
+# Prompt steps of more rows than this are never captured: their kernels run for so long that the launches hide
+# behind them (a 12,800-row step of the 4B shape: 85 ms on the device, about 2 ms of launches), while a captured step
+# keeps its activations' memory for as long as the graph lives and costs a second run to record.
+PROMPT_GRAPH_MAX_ROWS = int(os.environ.get("MYNAH_PROMPT_GRAPH_MAX_ROWS", "4096"))
+
+
 def _prompt_rows_bucket(T: int) -> int:
     """Rows of a prompt step, padded so that a few graphs serve many lengths and at most an eighth is padding."""
     if T <= 256:
@@ -400,6 +406,8 @@ class Engine:
             return None
         B = len(entries)
         T = sum(len(e.tokens) for e in entries)
+        if T > PROMPT_GRAPH_MAX_ROWS:
+            return None
         need_ids = [sum(self.cache.pages.n_held(e.slot, g) for e in entries) for g in range(self.n_groups)]
         key = (_prompt_rows_bucket(T), self._bucket(B), self._bucket(len(wants)),
                tuple(max(4, self._bucket(n)) for n in need_ids))
