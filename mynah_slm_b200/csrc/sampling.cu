@@ -106,7 +106,7 @@ template <int NC>
 __device__ Found radix_pass(const float* __restrict__ p, const RowShare<NC>& rs, unsigned int prefix_bits, unsigned int prefix_mask,
                             int shift, int n_bins, bool by_mass, unsigned int target_count,
                             unsigned long long target_mass, unsigned int carry_count, unsigned long long carry_mass,
-                            Shared& sh) {
+                            Shared& sh, float scale = 1.0f) {                // the elements are p[i] * scale (1: as stored)
     for (int i = threadIdx.x; i < BINS; i += THREADS) {
         sh.count[i] = 0;
         sh.mass_lo[i] = 0;
@@ -139,7 +139,7 @@ __device__ Found radix_pass(const float* __restrict__ p, const RowShare<NC>& rs,
             unsigned int d = 0xffffffffu;
             unsigned long long ms = 0;
             if (i < rs.end) {
-                const float v = vals[u];
+                const float v = vals[u] * scale;
                 const unsigned int bits = __float_as_uint(v);
                 if ((bits & prefix_mask) == prefix_bits) {
                     on = true;
@@ -638,7 +638,8 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
 // probabilities are found once (a search by count, then the id up to which entries equal to the k-th belong),
 // gathered into the leading CTA and sorted by (probability descending, id ascending), which is the order that
 // the general kernel walks. min-p, top-p, the kept mass and the drawn place are then prefixes of at most k
-// entries, walked by one thread in the same integer arithmetic: seven passes over the row instead of thirteen.
+// entries, walked by one thread in the same integer arithmetic: three passes over the row (exponentials and their
+// sum, the leading bits of the k-th largest, the gather) instead of thirteen; seven for a row with many equal logits.
 struct Candidates {
     unsigned long long key[MAX_CAND];      // probability bits above, ~id below: larger keys come first
     unsigned int n;
@@ -699,27 +700,41 @@ sample_top_k_kernel(float* __restrict__ logits, int V, int ld, const float* __re
     double sum = 0.0;
     for (int r = 0; r < NC; r++) sum += *rs.at(&sh.part_d, r);
     const float inv = (float)(1.0 / sum);
-    for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
-        float vals[LOADS];
-#pragma unroll
-        for (int u = 0; u < LOADS; u++) {
-            const int i = base0 + u * THREADS + (int)threadIdx.x;
-            vals[u] = i < rs.end ? row[i] : 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < LOADS; u++) {
-            const int i = base0 + u * THREADS + (int)threadIdx.x;
-            if (i < rs.end) row[i] = vals[u] * inv;
-        }
-    }
     if (threadIdx.x == 0) cand.n = 0;
     for (int i = threadIdx.x; i < MAX_CAND; i += THREADS) cand.key[i] = 0ull;
-    rs.sync();                                              // the row holds probabilities; the leading CTA's list is empty
-    const float p_best = __ldcg(row + best);
+    rs.sync();                                              // the row holds the exponentials; the leading CTA's list is empty
+    const float p_best = __ldcg(row + best) * inv;
 
-    // the k-th largest probability, and the last id among its equals that still belongs to the k
-    const Prefix topk = find_prefix<NC>(row, rs, false, (unsigned int)sp.top_k, 0, sh);
-    const int id_bound = nth_equal<NC>(row, rs, topk.value, topk.ties, sh);
+    // One pass over the probabilities (the stored exponentials times inv, as the reference forms them) finds the
+    // leading eleven bits of the k-th largest. Everything with those bits or larger ones holds the k largest; when
+    // that is a short list it is gathered and sorted, and its first k entries are the k largest in the order
+    // (probability descending, id ascending). Only a row that crowds more than MAX_CAND entries there (many equal
+    // logits) takes the long way: the row normalised in place, the k-th probability to the last bit and the id up
+    // to which its equals belong.
+    const Found lead = radix_pass<NC>(row, rs, 0u, 0u, 21, 2048, false, (unsigned int)sp.top_k, 0, 0, 0, sh, inv);
+    const bool short_list = lead.above + lead.count <= (unsigned int)MAX_CAND;      // the same in every CTA of the row
+    Prefix topk{0u, 0u, 0u, 0ull};
+    int id_bound = -1;
+    float gather_scale = inv;
+    if (!short_list) {
+        for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
+            float vals[LOADS];
+#pragma unroll
+            for (int u = 0; u < LOADS; u++) {
+                const int i = base0 + u * THREADS + (int)threadIdx.x;
+                vals[u] = i < rs.end ? row[i] : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < LOADS; u++) {
+                const int i = base0 + u * THREADS + (int)threadIdx.x;
+                if (i < rs.end) row[i] = vals[u] * inv;
+            }
+        }
+        rs.sync();                                          // the row holds probabilities
+        topk = find_prefix<NC>(row, rs, false, (unsigned int)sp.top_k, 0, sh);
+        id_bound = nth_equal<NC>(row, rs, topk.value, topk.ties, sh);
+        gather_scale = 1.0f;
+    }
     unsigned int* cnt = rs.at(&cand.n, 0);
     unsigned long long* keys = rs.at(&cand.key[0], 0);
     for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
@@ -732,8 +747,9 @@ sample_top_k_kernel(float* __restrict__ logits, int V, int ld, const float* __re
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            const unsigned int bits = __float_as_uint(vals[u]);     // probabilities are not negative: bits order as values
-            if (i < rs.end && (bits > topk.value || (bits == topk.value && i <= id_bound))) {
+            const unsigned int bits = __float_as_uint(vals[u] * gather_scale);    // probabilities are not negative: bits order as values
+            const bool take = short_list ? (bits >> 21) >= lead.digit : (bits > topk.value || (bits == topk.value && i <= id_bound));
+            if (i < rs.end && take) {
                 const unsigned int at = atomicAdd(cnt, 1u);
                 if (at < (unsigned int)MAX_CAND) keys[at] = ((unsigned long long)bits << 32) | (0xffffffffu - (unsigned int)i);
             }
@@ -757,7 +773,7 @@ sample_top_k_kernel(float* __restrict__ logits, int V, int ld, const float* __re
         }
     }
     if (threadIdx.x != 0) return;
-    const unsigned int n_c = min(cand.n, (unsigned int)MAX_CAND);      // top_k, unless the row has fewer entries
+    const unsigned int n_c = min(min(cand.n, (unsigned int)MAX_CAND), (unsigned int)sp.top_k);   // top_k, unless the row has fewer entries
     unsigned int n = n_c;
     if (sp.min_p > 0.f) {
         const float floor_p = sp.min_p * p_best;
