@@ -48,6 +48,7 @@ struct Shared {
     unsigned long long found_mass[2];
     unsigned int turn;                 // passes done so far (selects the set)
     double part_d;                     // this CTA's share of a sum over the row
+    unsigned long long part_m;         // this CTA's share of the row's mass
     unsigned int part_u;
     float red_f[32];
     int red_i[32];
@@ -568,6 +569,7 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     for (int r = 0; r < NC; r++) sum += *rs.at(&sh.part_d, r);       // in the CTAs' order: the same value in each of them
     const float inv = (float)(1.0 / sum);
     unsigned int n_floor = 0;
+    unsigned long long mass_part = 0;                       // the mass of this thread's probabilities (integers: any order)
     for (int base0 = rs.begin; base0 < rs.end; base0 += THREADS * LOADS) {
         float vals[LOADS];
 #pragma unroll
@@ -578,10 +580,25 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
 #pragma unroll
         for (int u = 0; u < LOADS; u++) {
             const int i = base0 + u * THREADS + (int)threadIdx.x;
-            if (i < rs.end) row[i] = vals[u] * inv;
+            if (i < rs.end) {
+                const float pr = vals[u] * inv;
+                row[i] = pr;
+                mass_part += mass_of(pr);
+            }
         }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mass_part += __shfl_xor_sync(0xffffffffu, mass_part, o);
+    if (lane == 0) sh.warp_mass[warp] = mass_part;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long mine = 0;
+        for (int w = 0; w < THREADS / 32; w++) mine += sh.warp_mass[w];
+        sh.part_m = mine;
+    }
     rs.sync();                                              // the whole row holds probabilities (and part_d has been read)
+    unsigned long long row_mass = 0;
+    for (int r = 0; r < NC; r++) row_mass += *rs.at(&sh.part_m, r);
     const float p_best = __ldcg(row + best);                // possibly written by another CTA of the row
 
     // the kept prefix: top-k, then min-p, then top-p (sampler.c:146-175)
@@ -614,7 +631,8 @@ sample_kernel(float* __restrict__ logits, int V, int ld, const float* __restrict
     }
     if (n < 1) n = 1;
     // mass of the kept prefix, then the draw r = U * total and the walk (sampler.c:178-186)
-    const Prefix kept = find_prefix<NC>(row, rs, false, n, 0, sh);
+    // (with nothing cut off that is the row's mass, which the pass above has added up: three passes fewer)
+    const Prefix kept = n == (unsigned int)V ? Prefix{0u, 0u, 0u, row_mass} : find_prefix<NC>(row, rs, false, n, 0, sh);
     unsigned long long state = rng[slot];                   // (rewritten by the leading CTA only after the last barrier)
     const double u = splitmix_uniform(&state);
     const double r = u * (double)kept.mass;
